@@ -1,0 +1,107 @@
+"""CPU: pin the oracle restatements to golden vectors produced by the reference's naive.py."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import hdla_oracle as orc
+from hdla_impl_b200.synthetic import make_inputs
+
+R = 2
+GRADS = ["dq", "dk", "dv", "da", "db", "dgk", "dh0"]
+
+
+def _small(golden_dir):
+    z = np.load(os.path.join(golden_dir, "naive_small.npz"))
+    x = {n[3:]: torch.from_numpy(z[n]) for n in z.files if n.startswith("in_")}
+    ref = {n[4:]: torch.from_numpy(z[n]) for n in z.files if n.startswith("out_")}
+    return x, ref
+
+
+def test_recurrence_matches_reference_naive(golden_dir):
+    x, ref = _small(golden_dir)
+    o, ht = orc.recurrent_ref(x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], R, 1.0, x["h0"])
+    assert orc.rel_err(o, ref["o"]) < 1e-12
+    assert orc.rel_err(ht, ref["ht"]) < 1e-12
+
+
+@pytest.mark.parametrize("chunk", [16, 64])
+def test_chunked_autograd_matches_reference_naive(golden_dir, chunk):
+    x, ref = _small(golden_dir)
+    fn = lambda q, k, v, a, b, gk, h0: orc.chunked_ref(q, k, v, a, b, gk, R, 1.0, h0, True, chunk)
+    o, ht, g = orc.autograd_ref(fn, x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], x["h0"], x["do"], x["dht"])
+    assert orc.rel_err(o, ref["o"]) < 1e-11
+    assert orc.rel_err(ht, ref["ht"]) < 1e-11
+    for n in GRADS:
+        assert orc.rel_err(g[n], ref[n]) < 1e-10, n
+
+
+@pytest.mark.parametrize("chunk", [16, 64])
+def test_staged_backward_matches_reference_naive(golden_dir, chunk):
+    x, ref = _small(golden_dir)
+    st = orc.staged_forward(x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], R, 1.0, x["h0"], chunk)
+    assert orc.rel_err(st["o_bthv"], ref["o"]) < 1e-11
+    assert orc.rel_err(st["ht"], ref["ht"]) < 1e-11
+    g = orc.staged_backward(st, x["do"], x["dht"])
+    for n in GRADS:
+        assert orc.rel_err(g[n], ref[n]) < 1e-10, n
+
+
+def test_recurrence_autograd_matches_reference_naive(golden_dir):
+    x, ref = _small(golden_dir)
+    fn = lambda q, k, v, a, b, gk, h0: orc.recurrent_ref(q, k, v, a, b, gk, R, 1.0, h0)
+    o, ht, g = orc.autograd_ref(fn, x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], x["h0"], x["do"], x["dht"])
+    for n in GRADS:
+        assert orc.rel_err(g[n], ref[n]) < 1e-10, n
+
+
+def test_cfg0_matches_reference_naive(golden_dir):
+    """CPU configuration B2 T256 H4 K=V=64 seed 0 against the subsampled reference output."""
+    z = np.load(os.path.join(golden_dir, "naive_cfg0.npz"))
+    x = make_inputs(2, 256, 4, 64, 64, R, seed=0, gk_div=16.0, with_dht=True)
+    for n in ("q", "k", "v", "a", "b", "gk", "do"):
+        s = z["insum_" + n]
+        assert abs(x[n].double().sum().item() - s[0]) <= 1e-6 * max(1.0, s[1]), f"input generator differs: {n}"
+    st = orc.staged_forward(x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], R, 1.0, None, 64)
+    g = orc.staged_backward(st, x["do"], None)
+    got = dict(o=st["o_bthv"], ht=st["ht"], **{n: g[n] for n in GRADS})
+    for n, t in got.items():
+        sub = torch.from_numpy(z["sub_" + n])
+        assert orc.rel_err(t.reshape(-1)[::13], sub) < 1e-10, n
+        assert abs(t.sum().item() - z["sum_" + n][0]) < 1e-8 * max(1.0, z["sum_" + n][1]), n
+
+
+def test_scale_and_partial_chunk_consistency():
+    """scale is applied to q; a ragged last chunk equals the recurrence."""
+    x = make_inputs(2, 83, 2, 16, 24, R, seed=3, gk_div=4.0, h0_std=0.5, with_dht=True)
+    fn_c = lambda q, k, v, a, b, gk, h0: orc.chunked_ref(q, k, v, a, b, gk, R, 0.37, h0, True, 32)
+    fn_r = lambda q, k, v, a, b, gk, h0: orc.recurrent_ref(q, k, v, a, b, gk, R, 0.37, h0)
+    args = [x[n] for n in ("q", "k", "v", "a", "b", "gk", "h0", "do", "dht")]
+    o1, h1, g1 = orc.autograd_ref(fn_c, *args)
+    o2, h2, g2 = orc.autograd_ref(fn_r, *args)
+    assert orc.rel_err(o1, o2) < 1e-11 and orc.rel_err(h1, h2) < 1e-11
+    for n in GRADS:
+        assert orc.rel_err(g1[n], g2[n]) < 1e-10, n
+    st = orc.staged_forward(*args[:6], R, 0.37, x["h0"], 32)
+    g3 = orc.staged_backward(st, x["do"], x["dht"])
+    for n in GRADS:
+        assert orc.rel_err(g3[n], g2[n]) < 1e-10, n
+
+
+def test_reverse_and_varlen_recurrence():
+    x = make_inputs(1, 40, 2, 16, 16, R, seed=5, gk_div=2.0)
+    cu = [0, 13, 40]
+    h0 = torch.randn(2, 2, 16, 16, generator=torch.Generator().manual_seed(1))
+    o, ht = orc.recurrent_ref(x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], R, None, h0, cu_seqlens=cu)
+    for i in range(2):
+        s, e = cu[i], cu[i + 1]
+        oi, hi = orc.recurrent_ref(x["q"][:, s:e], x["k"][:, s:e], x["v"][:, s:e], x["a"][:, 2 * s:2 * e],
+                                   x["b"][:, 2 * s:2 * e], x["gk"][:, s:e], R, None, h0[i:i + 1])
+        assert orc.rel_err(o[:, s:e], oi) < 1e-13 and orc.rel_err(ht[i:i + 1], hi) < 1e-13
+    # reverse == forward on the time-flipped sequence
+    flip2 = lambda t: t.view(1, 40, 2, 2, 16).flip(1).reshape(1, 80, 2, 16)
+    orv, hrv = orc.recurrent_ref(x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], R, None, None, reverse=True)
+    of, hf = orc.recurrent_ref(x["q"].flip(1), x["k"].flip(1), x["v"].flip(1), flip2(x["a"]), flip2(x["b"]),
+                               x["gk"].flip(1), R, None, None)
+    assert orc.rel_err(orv, of.flip(1)) < 1e-13 and orc.rel_err(hrv, hf) < 1e-13
