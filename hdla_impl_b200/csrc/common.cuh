@@ -1,0 +1,52 @@
+// Shared helpers for libhdla: error reporting, element-type access.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stddef.h>
+#include "../../include/hdla.h"
+
+namespace hdla {
+
+// Records a message for hdla_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...);
+
+#define HDLA_CHECK_LAUNCH(what)                                                       \
+    do {                                                                              \
+        cudaError_t e__ = cudaGetLastError();                                         \
+        if (e__ != cudaSuccess)                                                       \
+            return ::hdla::fail(HDLA_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e__)); \
+    } while (0)
+
+// Effective chunk size: min(C, max(next_pow2(T), 16)).
+static inline int effective_chunk(int T, int C) {
+    int p2 = 1;
+    while (p2 < T) p2 <<= 1;
+    int lo = p2 > 16 ? p2 : 16;
+    return C < lo ? C : lo;
+}
+
+// Runtime-typed element access (dt: HDLA_F32 | HDLA_BF16). The branch is warp-uniform.
+__device__ __forceinline__ float ld_elem(const void* p, size_t i, int dt) {
+    return dt == HDLA_F32 ? static_cast<const float*>(p)[i]
+                          : __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+}
+__device__ __forceinline__ void st_elem(void* p, size_t i, int dt, float x) {
+    if (dt == HDLA_F32) static_cast<float*>(p)[i] = x;
+    else static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(x);
+}
+
+// pipelines implemented in the other translation units
+int recurrent_fwd_launch(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a,
+                         const void* b, const void* gk, float scale, const float* h0, void* o, float* ht,
+                         const int64_t* cu_seqlens, int n_seqs, int reverse, cudaStream_t st);
+
+size_t simt_workspace_floats(const HdlaDims& d, int with_backward);
+int simt_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a, const void* b,
+                   const void* gk, float scale, const float* h0, void* o, float* ht, float* ws, bool need_o,
+                   cudaStream_t st);
+int simt_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a, const void* b,
+                   const void* gk, float scale, const float* h0, const void* d_o, const float* dht, void* dq,
+                   void* dk, void* dv, void* da, void* db, void* dgk, float* dh0, float* ws, cudaStream_t st);
+
+}  // namespace hdla

@@ -1,0 +1,129 @@
+/*
+ * hdla.h -- C ABI of libhdla: the HDLA rank-R diagonal-plus-low-rank delta-rule operator for
+ * NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers and sizes.  The caller owns all memory
+ * (inputs, outputs and the workspace whose size hdla_chunk_workspace_bytes() reports); the
+ * library never allocates, frees or synchronises, and enqueues all work on the stream it is
+ * given.  Functions return 0 on success and a negative HDLA_ERR_* code otherwise; they never
+ * throw, abort or trap.  hdla_last_error() returns a description of the calling thread's last
+ * failure.
+ *
+ * Tensor layouts (dense, row-major; identical to the reference operator's,
+ * HRDPLR/hrdplr.py:286-300 and HRDPLR/recurrent.py:227-241):
+ *     q, k, gk : [B, T,   H, K]
+ *     v, o     : [B, T,   H, V]
+ *     a, b     : [B, T*R, H, K]     row t*R + r  (time major, rank minor)
+ *     states   : [N, H, K, V] fp32  (N = B, or the number of sequences with cu_seqlens)
+ * gk is a LOG decay (<= 0).  R is the rank of the low-rank term (2 for HDLA).
+ */
+#ifndef HDLA_H_
+#define HDLA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HDLA_VERSION 100
+
+#if defined(__GNUC__)
+#define HDLA_API __attribute__((visibility("default")))
+#else
+#define HDLA_API
+#endif
+
+/* element types of q,k,v,a,b,o and their gradients (dtype) and of gk/dgk (gk_dtype) */
+#define HDLA_F32  0
+#define HDLA_BF16 1
+
+/* error codes */
+#define HDLA_OK                 0
+#define HDLA_ERR_INVALID       -1   /* null pointer, non-positive size, inconsistent shapes      */
+#define HDLA_ERR_UNSUPPORTED   -2   /* shape or dtype outside what the kernels are built for     */
+#define HDLA_ERR_WORKSPACE     -3   /* workspace pointer null/misaligned or too small            */
+#define HDLA_ERR_CUDA          -4   /* a CUDA runtime call or kernel launch reported an error    */
+
+/* flags of HdlaDims.flags */
+#define HDLA_FLAG_WS_HOLDS_FWD  1   /* hdla_chunk_bwd: the workspace still holds what hdla_chunk_fwd
+                                       left there for the same inputs -> skip the recomputation  */
+#define HDLA_FLAG_FORCE_SIMT    2   /* use the fp32 CUDA-core pipeline even for bf16 inputs       */
+
+typedef struct HdlaDims {
+    int32_t B;         /* batch (sequences)                                   */
+    int32_t T;         /* tokens per sequence                                 */
+    int32_t H;         /* heads                                               */
+    int32_t K;         /* key/query head dim                                  */
+    int32_t V;         /* value head dim                                      */
+    int32_t R;         /* rank of the a/b term                                */
+    int32_t C;         /* chunk size as passed by the caller; the effective chunk is
+                          min(C, max(next_pow2(T), 16))  (HRDPLR/hrdplr.py:42)  */
+    int32_t dtype;     /* HDLA_F32 | HDLA_BF16 for q,k,v,a,b,o,do and dq..db   */
+    int32_t gk_dtype;  /* HDLA_F32 | HDLA_BF16 for gk and dgk                  */
+    int32_t flags;     /* HDLA_FLAG_*                                          */
+} HdlaDims;
+
+/* Library version (HDLA_VERSION of the build). */
+HDLA_API int hdla_version(void);
+
+/* Text of the calling thread's most recent error ("" if none). The pointer stays valid until
+ * the same thread's next failing call. */
+HDLA_API const char* hdla_last_error(void);
+
+/* Bytes of device workspace hdla_chunk_fwd (with_backward = 0) or the pair hdla_chunk_fwd +
+ * hdla_chunk_bwd (with_backward = 1) needs for these dims; 0 if the dims are unsupported (see
+ * hdla_last_error).  Replaces the torch.empty(...) intermediates the reference's stage
+ * wrappers allocate: HRDPLR/fwd_func.py:40-43,69-72,131-132,198,243-245,296 and
+ * HRDPLR/bwd_func.py:33-36,84-86,139,181-185,238-241,300-309. */
+HDLA_API size_t hdla_chunk_workspace_bytes(const HdlaDims* dims, int with_backward);
+
+/* Chunked forward.  Replaces chunk_hrdplr_fwd (HRDPLR/hrdplr.py:25-99), i.e. the stage
+ * sequence cumsum -> intra-chunk A matrices -> (I-Aab)^-1 and w/u -> state scan -> output.
+ *   h0  : [B,H,K,V] fp32 initial state or NULL (zero state)
+ *   o   : [B,T,H,V] in dims->dtype
+ *   ht  : [B,H,K,V] fp32 final state or NULL
+ * The workspace must be 256-byte aligned.  With a workspace sized for backward the forward
+ * intermediates stay in it for hdla_chunk_bwd(HDLA_FLAG_WS_HOLDS_FWD). */
+HDLA_API int hdla_chunk_fwd(const HdlaDims* dims,
+                   const void* q, const void* k, const void* v, const void* a, const void* b,
+                   const void* gk, float scale, const float* h0,
+                   void* o, float* ht,
+                   void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/* Chunked backward.  Replaces ChunkDPLRDeltaRuleFunction.backward (HRDPLR/hrdplr.py:146-284):
+ * stages dAu, dhu (reverse state scan), dv, bwd_o, wy, intra and dgk.
+ *   d_o  : [B,T,H,V] gradient of o (dims->dtype);  dht: [B,H,K,V] fp32 gradient of the final
+ *          state or NULL
+ *   dq,dk,dv,da,db in dims->dtype, dgk in dims->gk_dtype, shaped like their inputs
+ *   dh0 : [B,H,K,V] fp32 or NULL
+ * Unless HDLA_FLAG_WS_HOLDS_FWD is set the forward intermediates are recomputed first (what
+ * the reference always does, HRDPLR/hrdplr.py:161-198). */
+HDLA_API int hdla_chunk_bwd(const HdlaDims* dims,
+                   const void* q, const void* k, const void* v, const void* a, const void* b,
+                   const void* gk, float scale, const float* h0,
+                   const void* d_o, const float* dht,
+                   void* dq, void* dk, void* dv, void* da, void* db, void* dgk, float* dh0,
+                   void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/* Fused recurrent forward (decode / short prefill).  Replaces
+ * fused_recurrent_dplr_delta_rule_fwd (HRDPLR/recurrent.py:121-177) and its kernel (:10-119).
+ *   dims->T : tokens per sequence (total tokens when cu_seqlens is given, in which case
+ *             dims->B must be 1); dims->C is ignored
+ *   h0      : [N,H,K,V] fp32 or NULL;  ht: [N,H,K,V] fp32 or NULL.  ht may alias h0 (in-place
+ *             state update).
+ *   cu_seqlens : device pointer to n_seqs+1 int64 offsets or NULL (then n_seqs is ignored)
+ *   reverse : process tokens from last to first (HRDPLR/recurrent.py:64,108)
+ * Needs no workspace. */
+HDLA_API int hdla_recurrent_fwd(const HdlaDims* dims,
+                       const void* q, const void* k, const void* v, const void* a, const void* b,
+                       const void* gk, float scale, const float* h0,
+                       void* o, float* ht,
+                       const int64_t* cu_seqlens, int32_t n_seqs, int32_t reverse,
+                       void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HDLA_H_ */

@@ -1,0 +1,222 @@
+"""GPU parity: the CUDA operator (through the public entry points, which call the C ABI) against
+the fp64 CPU oracle and the golden vectors of the reference's naive implementation.
+
+Tolerances (max|x-ref| / max|ref| per tensor): fp32 inputs 1e-4, bf16 inputs 2e-2.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import hdla_oracle as orc
+from hdla_impl_b200.synthetic import make_inputs
+
+pytestmark = pytest.mark.gpu
+
+R = 2
+TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2}
+GRADS = ["dq", "dk", "dv", "da", "db", "dgk"]
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def run_chunk(x, dev, scale, chunk, use_h0, use_dht, dtype):
+    import hdla_impl_b200 as H
+    names = ["q", "k", "v", "a", "b", "gk"]
+    leaves = [x[n].to(dev).to(dtype if n != "gk" else x[n].dtype).requires_grad_(True) for n in names]
+    h0 = x["h0"].to(dev).requires_grad_(True) if use_h0 else None
+    o, ht = H.chunk_hrdplr_delta_rule(*leaves, R, scale=scale, initial_state=h0, output_final_state=True,
+                                      chunk_size=chunk)
+    loss = (o.float() * x["do"].to(dev).float()).sum()
+    if use_dht:
+        loss = loss + (ht * x["dht"].to(dev)).sum()
+    ins = leaves + ([h0] if use_h0 else [])
+    grads = torch.autograd.grad(loss, ins)
+    out = dict(o=o, ht=ht)
+    out.update(dict(zip(GRADS + (["dh0"] if use_h0 else []), grads)))
+    return out
+
+
+def oracle_chunk(x, scale, use_h0, use_dht, dtype):
+    """fp64 oracle on the inputs as the device sees them (rounded to `dtype`)."""
+    rd = lambda n: x[n].to(dtype).double() if n != "gk" else x[n].double()
+    st = orc.staged_forward(rd("q"), rd("k"), rd("v"), rd("a"), rd("b"), rd("gk"), R, scale,
+                            x["h0"] if use_h0 else None, 64)
+    g = orc.staged_backward(st, x["do"].to(dtype).double(), x["dht"] if use_dht else None)
+    out = dict(o=st["o_bthv"], ht=st["ht"])
+    out.update({n: g[n] for n in GRADS + (["dh0"] if use_h0 else [])})
+    return out
+
+
+def assert_close(got, ref, tol, label=""):
+    bad = []
+    for n, r in ref.items():
+        e = orc.rel_err(got[n], r)
+        if not e < tol:
+            bad.append(f"{n}: {e:.3e}")
+    assert not bad, f"{label} exceeds {tol}: " + ", ".join(bad)
+
+
+@pytest.mark.parametrize("chunk", [64, 16])
+def test_chunk_cfg0_fp32(dev, chunk):
+    """B2 T256 H4 K=V=64 fp32 seed 0, zero initial state: o, final state and all gradients."""
+    x = make_inputs(2, 256, 4, 64, 64, R, seed=0, with_dht=True)
+    got = run_chunk(x, dev, 1.0, chunk, False, False, torch.float32)
+    ref = oracle_chunk(x, 1.0, False, False, torch.float32)
+    assert_close(got, ref, 1e-4, f"cfg0 chunk={chunk}")
+
+
+def test_chunk_cfg0_against_reference_golden(dev, golden_dir):
+    z = np.load(os.path.join(golden_dir, "naive_cfg0.npz"))
+    x = make_inputs(2, 256, 4, 64, 64, R, seed=0, with_dht=True)
+    got = run_chunk(x, dev, 1.0, 64, False, False, torch.float32)
+    for n in ["o", "ht"] + GRADS:
+        sub = torch.from_numpy(z["sub_" + n])
+        assert orc.rel_err(got[n].reshape(-1)[::13], sub) < 1e-4, n
+
+
+@pytest.mark.parametrize("chunk", [16, 32, 64])
+def test_chunk_small_golden_strong_decay(dev, golden_dir, chunk):
+    """Reference golden case: undivided logsigmoid decay, random h0 and dht, K=32, V=48."""
+    z = np.load(os.path.join(golden_dir, "naive_small.npz"))
+    x = {n[3:]: torch.from_numpy(z[n]) for n in z.files if n.startswith("in_")}
+    ref = {n[4:]: torch.from_numpy(z[n]) for n in z.files if n.startswith("out_")}
+    got = run_chunk(x, dev, 1.0, chunk, True, True, torch.float32)
+    assert_close(got, ref, 1e-4, f"golden small chunk={chunk}")
+
+
+def test_chunk_ragged_scale_h0(dev):
+    """T not a multiple of the chunk, K != V, non-unit scale, initial state and dht."""
+    x = make_inputs(2, 83, 3, 32, 64, R, seed=3, gk_div=4.0, h0_std=0.5, with_dht=True)
+    got = run_chunk(x, dev, 0.37, 32, True, True, torch.float32)
+    ref = oracle_chunk(x, 0.37, True, True, torch.float32)
+    assert_close(got, ref, 1e-4, "ragged")
+
+
+def test_chunk_short_sequence(dev):
+    """T < 16: the effective chunk is max(next_pow2(T), 16)."""
+    x = make_inputs(1, 5, 2, 16, 16, R, seed=4, gk_div=2.0, h0_std=1.0, with_dht=True)
+    got = run_chunk(x, dev, 0.25, 64, True, True, torch.float32)
+    ref = oracle_chunk(x, 0.25, True, True, torch.float32)
+    assert_close(got, ref, 1e-4, "short")
+
+
+def test_chunk_bf16(dev):
+    x = make_inputs(2, 256, 2, 128, 128, R, seed=1, dtype=torch.bfloat16, with_dht=True)
+    x["gk"] = x["gk"].float()
+    got = run_chunk(x, dev, 128 ** -0.5, 64, False, True, torch.bfloat16)
+    ref = oracle_chunk(x, 128 ** -0.5, False, True, torch.bfloat16)
+    assert_close(got, ref, 2e-2, "bf16")
+    assert got["o"].dtype == torch.bfloat16 and got["dq"].dtype == torch.bfloat16 and got["ht"].dtype == torch.float32
+
+
+def test_chunk_recompute_equals_saved(dev, monkeypatch):
+    x = make_inputs(1, 128, 2, 64, 64, R, seed=2, h0_std=0.1, with_dht=True)
+    a = run_chunk(x, dev, 1.0, 64, True, True, torch.float32)
+    monkeypatch.setenv("HDLA_RECOMPUTE", "1")
+    b = run_chunk(x, dev, 1.0, 64, True, True, torch.float32)
+    for n in a:
+        assert torch.equal(a[n], b[n]), n
+
+
+def test_chunk_forward_only_no_grad(dev):
+    import hdla_impl_b200 as H
+    x = make_inputs(1, 64, 2, 64, 64, R, seed=6)
+    with torch.no_grad():
+        o, ht = H.chunk_hrdplr_delta_rule(*[x[n].to(dev) for n in ("q", "k", "v", "a", "b", "gk")], R,
+                                          chunk_size=64)
+    assert ht is None
+    ref, _ = orc.recurrent_ref(x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], R, None, None)
+    assert orc.rel_err(o, ref) < 1e-4
+
+
+# ---------------------------------------------------------------------------------- recurrent
+def test_recurrent_cfg0_fp32(dev):
+    import hdla_impl_b200 as H
+    x = make_inputs(2, 256, 4, 64, 64, R, seed=0, h0_std=0.02)
+    o, ht = H.fused_recurrent_dplr_delta_rule(*[x[n].to(dev) for n in ("q", "k", "v", "a", "b", "gk")], R,
+                                              scale=1.0, initial_state=x["h0"].to(dev), output_final_state=True)
+    ro, rh = orc.recurrent_ref(x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], R, 1.0, x["h0"])
+    assert orc.rel_err(o, ro) < 1e-4 and orc.rel_err(ht, rh) < 1e-4
+
+
+def test_recurrent_matches_chunk(dev):
+    """The reference's test_recurrent.py: chunked and recurrent paths agree."""
+    import hdla_impl_b200 as H
+    x = make_inputs(2, 256, 4, 128, 64, R, seed=8, gk_div=1.0, h0_std=1.0)
+    args = [x[n].to(dev) for n in ("q", "k", "v", "a", "b", "gk")]
+    o1, h1 = H.chunk_hrdplr_delta_rule(*args, R, scale=1.0, initial_state=x["h0"].to(dev), output_final_state=True,
+                                       chunk_size=16)
+    o2, h2 = H.fused_recurrent_dplr_delta_rule(*args, R, 1.0, x["h0"].to(dev), True, False, None)
+    assert orc.rel_err(o1, o2) < 1e-4 and orc.rel_err(h1, h2) < 1e-4
+
+
+@pytest.mark.parametrize("K,V", [(32, 48), (96, 64), (128, 128), (16, 4)])
+def test_recurrent_shapes_bf16_decode(dev, K, V):
+    """One token per call for several calls with a carried fp32 state (the decode loop)."""
+    import hdla_impl_b200 as H
+    steps, B, Hh = 6, 3, 2
+    x = make_inputs(B, steps, Hh, K, V, R, seed=9, dtype=torch.bfloat16, h0_std=0.02)
+    S = x["h0"].to(dev)
+    outs = []
+    for t in range(steps):
+        sl = lambda n, r=1: x[n][:, t * r:(t + 1) * r].to(dev)
+        o, S = H.fused_recurrent_dplr_delta_rule(sl("q"), sl("k"), sl("v"), sl("a", R), sl("b", R), sl("gk"), R,
+                                                 initial_state=S, output_final_state=True)
+        outs.append(o)
+    o = torch.cat(outs, 1)
+    f = lambda n: x[n].double()
+    ro, rh = orc.recurrent_ref(f("q"), f("k"), f("v"), f("a"), f("b"), f("gk"), R, None, x["h0"])
+    assert orc.rel_err(o, ro) < 2e-2 and orc.rel_err(S, rh) < 1e-4
+
+
+def test_recurrent_inplace_state(dev):
+    import hdla_impl_b200 as H
+    x = make_inputs(4, 1, 2, 64, 64, R, seed=10, h0_std=0.5)
+    args = [x[n].to(dev) for n in ("q", "k", "v", "a", "b", "gk")]
+    S = x["h0"].to(dev).clone()
+    o1, h1 = H.fused_recurrent_dplr_delta_rule_fwd(*args, R, 0.125, x["h0"].to(dev), True)
+    o2, h2 = H.fused_recurrent_dplr_delta_rule_fwd(*args, R, 0.125, S, True, inplace_state=True)
+    assert h2.data_ptr() == S.data_ptr() and torch.equal(h1, S) and torch.equal(o1, o2)
+
+
+def test_recurrent_reverse_and_varlen(dev):
+    import hdla_impl_b200 as H
+    x = make_inputs(1, 40, 2, 64, 32, R, seed=5, gk_div=2.0)
+    args = [x[n].to(dev) for n in ("q", "k", "v", "a", "b", "gk")]
+    cu = torch.tensor([0, 13, 40], device=dev)
+    h0 = torch.randn(2, 2, 64, 32, generator=torch.Generator().manual_seed(1))
+    o, ht = H.fused_recurrent_dplr_delta_rule(*args, R, None, h0.to(dev), True, False, cu)
+    ro, rh = orc.recurrent_ref(x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], R, None, h0, cu_seqlens=[0, 13, 40])
+    assert orc.rel_err(o, ro) < 1e-4 and orc.rel_err(ht, rh) < 1e-4
+    o, ht = H.fused_recurrent_dplr_delta_rule(*args, R, None, None, True, True, None)
+    ro, rh = orc.recurrent_ref(x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], R, None, None, reverse=True)
+    assert orc.rel_err(o, ro) < 1e-4 and orc.rel_err(ht, rh) < 1e-4
+
+
+def test_recurrent_backward_raises(dev):
+    import hdla_impl_b200 as H
+    x = make_inputs(1, 4, 1, 16, 16, R, seed=11)
+    args = [x[n].to(dev).requires_grad_(True) for n in ("q", "k", "v", "a", "b", "gk")]
+    o, _ = H.fused_recurrent_dplr_delta_rule(*args, R)
+    with pytest.raises(NotImplementedError):
+        o.sum().backward()
+
+
+def test_error_paths(dev):
+    import hdla_impl_b200 as H
+    x = make_inputs(1, 32, 1, 16, 16, R, seed=12)
+    args = [x[n].to(dev) for n in ("q", "k", "v", "a", "b", "gk")]
+    with pytest.raises(RuntimeError, match="power of two"):
+        H.chunk_hrdplr_delta_rule(*args, R, chunk_size=24)
+    with pytest.raises(AssertionError):
+        H.chunk_hrdplr_delta_rule(*args, R, head_first=True)
+    with pytest.raises(ValueError):
+        H.chunk_hrdplr_delta_rule(args[0], args[1], args[2], args[3][:, :-1], args[4], args[5], R)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        H.chunk_hrdplr_delta_rule(*[x[n] for n in ("q", "k", "v", "a", "b", "gk")], R)

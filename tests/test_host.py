@@ -1,0 +1,74 @@
+"""CPU: the C-ABI library loads and exports every declared symbol; host-side validation."""
+import ctypes as C
+import os
+import re
+
+import pytest
+import torch
+
+from hdla_impl_b200 import _lib
+from hdla_impl_b200.synthetic import make_inputs
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    hdr = open(os.path.join(ROOT, "include", "hdla.h")).read()
+    declared = set(re.findall(r"HDLA_API[^;(]*?\b(hdla_\w+)\s*\(", hdr))
+    assert declared, "no declarations found in include/hdla.h"
+    lib = _lib.load()
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in hdla.h but not exported"
+    assert set(_lib.EXPORTS) == declared
+    assert lib.hdla_version() == int(re.search(r"#define HDLA_VERSION (\d+)", hdr).group(1))
+
+
+def test_workspace_query_and_error_text():
+    lib = _lib.load()
+    d = _lib.HdlaDims(2, 256, 4, 64, 64, 2, 64, 0, 0, 0)
+    fwd = lib.hdla_chunk_workspace_bytes(C.byref(d), 0)
+    both = lib.hdla_chunk_workspace_bytes(C.byref(d), 1)
+    assert 0 < fwd < both
+    d = _lib.HdlaDims(2, 256, 4, 64, 64, 2, 48, 0, 0, 0)
+    assert lib.hdla_chunk_workspace_bytes(C.byref(d), 0) == 0
+    assert "power of two" in _lib.last_error()
+    d = _lib.HdlaDims(2, 0, 4, 64, 64, 2, 64, 0, 0, 0)
+    assert lib.hdla_chunk_workspace_bytes(C.byref(d), 0) == 0
+    assert "non-positive" in _lib.last_error()
+
+
+def test_null_pointers_are_rejected_without_touching_a_gpu():
+    lib = _lib.load()
+    d = _lib.HdlaDims(1, 16, 1, 16, 16, 2, 16, 0, 0, 0)
+    rc = lib.hdla_chunk_fwd(C.byref(d), None, None, None, None, None, None, 1.0, None, None, None, None, 0, None)
+    assert rc == -1 and "null" in _lib.last_error()
+    rc = lib.hdla_recurrent_fwd(C.byref(d), None, None, None, None, None, None, 1.0, None, None, None, None, 0, 0, None)
+    assert rc == -1
+
+
+def test_no_cpu_fallback():
+    import hdla_impl_b200 as H
+    x = make_inputs(1, 16, 1, 16, 16, 2, seed=0)
+    args = [x[n] for n in ("q", "k", "v", "a", "b", "gk")]
+    with pytest.raises(RuntimeError, match="CUDA"):
+        H.chunk_hrdplr_delta_rule(*args, 2)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        H.fused_recurrent_dplr_delta_rule(*args, 2)
+
+
+def test_recurrent_argument_validation():
+    import hdla_impl_b200 as H
+    x = make_inputs(2, 8, 1, 16, 16, 2, seed=0)
+    args = [x[n] for n in ("q", "k", "v", "a", "b", "gk")]
+    with pytest.raises(ValueError, match="batch size"):
+        H.fused_recurrent_dplr_delta_rule(*args, 2, cu_seqlens=torch.tensor([0, 8]))
+    with pytest.raises(AssertionError):
+        H.fused_recurrent_dplr_delta_rule(*args, 3)
+    with pytest.raises(ValueError, match="4 dimensions"):
+        H.fused_recurrent_dplr_delta_rule(args[0], args[1], args[2], args[3][0], args[4], args[5], 2)
+
+
+def test_dtype_codes():
+    assert _lib.dtype_code(torch.float32) == 0 and _lib.dtype_code(torch.bfloat16) == 1
+    with pytest.raises(TypeError):
+        _lib.dtype_code(torch.float16)
