@@ -1,0 +1,329 @@
+#!/usr/bin/env python
+"""Benchmark of the chunked HDLA operator, forward + backward.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg1|cfg0|cfg3]
+
+One step = one forward + backward of the operator over one synthetic batch.  At N = 1 the
+workload is B8 T4096 H16 K=V=128, bf16 inputs, fp32 accumulation/state, chunk 64 ("cfg1").  At
+N > 1 (launched with torch.distributed.run, one rank per GPU) every rank processes its own cfg1
+batch -- the (batch, head) pairs are independent, so the job shards with no collective on the
+data path (weak scaling); ``--scaling strong`` shards the single cfg1 batch over the ranks instead.
+
+The printed JSON line carries
+  value / ms_per_step : tokens/s with the inputs resident in HBM, CUDA-event timed, max over ranks
+  e2e                 : the same through the public entry point with pinned HOST buffers, the
+                        host->device copies of all inputs and device->host copies of o and all
+                        gradients inside the timed region
+  roofline            : algorithmic FLOPs of one step / measured step time against the measured
+                        bf16 tensor peak (MEASURED_PEAKS.json), with the HBM view beside it
+  cpu_baseline        : the CPU oracle (a port of the reference algorithm) timed on this host
+  clocks              : SM clocks and throttle reasons sampled with nvidia-smi during the timed region
+
+``--impl reference`` times the reference algorithm's CPU implementation (the oracle port of
+HRDPLR/naive.py plus explicit backward; the reference itself ships Triton-only kernels and a
+torch "naive" path, and its checkout is not available on the GPU host) on all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "HDLA fwd+bwd tokens/s (B8 T4096 H16 D128 bf16)"
+WORKLOADS = {
+    # name: (B, T, H, K, V, C, dtype)
+    "cfg1": (8, 4096, 16, 128, 128, 64, "bf16"),
+    "cfg0": (2, 256, 4, 64, 64, 64, "f32"),
+    "cfg3": (1, 65536, 16, 128, 128, 64, "bf16"),
+}
+R = 2
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+# ------------------------------------------------------------------------------ work per unit
+def macs_per_chunk_head(C: int, D: int) -> float:
+    """Dense tile products of the algorithm per (chunk, head), no recompute, masked products dense."""
+    fwd = 9 * C * C * D + (2 * C) ** 3 / 3 + 4 * C ** 3 + 4 * C * C * D + 2 * C * C * D + 5 * C * D * D \
+        + (C * D * D + 3 * C * C * D)
+    bwd = 5 * C * C * D + 5 * C * D * D + (C * D * D + C * C * D) + 6 * C * D * D + (28 * C ** 3 + 12 * C * C * D) \
+        + 18 * C * C * D
+    return fwd + bwd
+
+
+def flops_per_token_head(C: int, D: int) -> float:
+    return 2.0 * macs_per_chunk_head(C, D) / C
+
+
+def bytes_per_token_head(C: int, D: int, elt: int) -> float:
+    """Minimal HBM traffic: fwd reads 8D writes D; bwd reads 9D writes 8D; state checkpoints
+    (K*V*2 bytes per chunk) written and read once each for S and dS."""
+    return (8 * D + D) * elt + (9 * D + 8 * D) * elt + 4 * (D * D * 2 / C)
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return d, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------ CPU oracle timing
+def time_cpu_port(T_sample: int, H: int, K: int, V: int, C: int, repeats: int = 1):
+    """Forward + explicit backward of the oracle port in fp32 on all host threads; tokens/s."""
+    from oracle import hdla_oracle as orc
+    from hdla_impl_b200.synthetic import make_inputs
+    torch.set_num_threads(os.cpu_count() or 1)
+    x = make_inputs(1, T_sample, H, K, V, R, seed=0)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        st = orc.staged_forward(x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], R, K ** -0.5, None, C,
+                                dtype=torch.float32)
+        orc.staged_backward(st, x["do"], None)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return T_sample / best, best
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    B, T, H, K, V, C, dt = WORKLOADS[args.workload]
+    T_s = min(T, 256)
+    times = []
+    for i in range(args.warmup + args.steps):
+        _, sec = time_cpu_port(T_s, H, K, V, C)
+        if i >= args.warmup:
+            times.append(sec)
+    total = sum(times)
+    val = T_s * args.steps / total
+    cores = os.cpu_count() or 1
+    sample = f"B=1 T={T_s} of {args.workload} (H={H} K={K} V={V} chunk {C}), fp32, per step"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "B": B, "T": T, "H": H, "K": K, "V": V, "chunk": C, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------ our arm
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    import hdla_impl_b200 as HD
+    from hdla_impl_b200 import _lib
+    from hdla_impl_b200.sharding import shard_batch_heads
+    from hdla_impl_b200.synthetic import make_inputs
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU arm")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, T, H, K, V, C, dt = WORKLOADS[args.workload]
+    dtype = torch.bfloat16 if dt == "bf16" else torch.float32
+    elt = 2 if dt == "bf16" else 4
+
+    # this rank's units
+    if args.scaling == "strong" and world > 1:
+        b_lo, b_hi, h_lo, h_hi = shard_batch_heads(B, H, rank, world)
+        Bl, Hl = b_hi - b_lo, h_hi - h_lo
+    else:
+        Bl, Hl = B, H
+    x = make_inputs(Bl, T, Hl, K, V, R, seed=rank, dtype=dtype)
+    names = ("q", "k", "v", "a", "b", "gk")
+    host = {n: x[n].pin_memory() for n in names + ("do",)}
+    dev_in = {n: host[n].to(dev) for n in host}
+    leaves = [dev_in[n].requires_grad_(True) for n in names]
+    scale = K ** -0.5
+
+    def step(lv, do):
+        o, _ = HD.chunk_hrdplr_delta_rule(*lv, R, scale=scale, chunk_size=C)
+        grads = torch.autograd.grad(o, lv, do)
+        return o, grads
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step(leaves, dev_in["do"])
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    l0 = _lib.kernel_launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step(leaves, dev_in["do"])
+    e1.record()
+    barrier()
+    launches = _lib.kernel_launches() - l0
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # end to end: pinned host buffers in, host buffers out
+    out_host = None
+    e2e_steps = args.steps
+
+    def e2e_step():
+        nonlocal out_host
+        lv = [host[n].to(dev, non_blocking=True).requires_grad_(True) for n in names]
+        do = host["do"].to(dev, non_blocking=True)
+        o, grads = step(lv, do)
+        outs = (o,) + tuple(grads)
+        if out_host is None:
+            out_host = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outs]
+        for hbuf, t in zip(out_host, outs):
+            hbuf.copy_(t, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+    h2d = sum(host[n].numel() * host[n].element_size() for n in host)
+    d2h = sum(t.numel() * t.element_size() for t in out_host)
+
+    if world > 1:
+        tt = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = tt.tolist()
+    tokens_step = B * T * (world if args.scaling == "weak" else 1)
+    ms_step = ms / args.steps
+    value = tokens_step / (ms_step / 1e3)
+    e2e_val = tokens_step / (ms_e2e / e2e_steps / 1e3)
+
+    if rank == 0:
+        peaks, how = load_peaks()
+        heads_tokens = tokens_step * H / world            # per-GPU token-heads per step
+        flops = heads_tokens * flops_per_token_head(C, K)
+        byts = heads_tokens * bytes_per_token_head(C, K, elt)
+        sec = ms_step / 1e3
+        tf = flops / sec / 1e12
+        gbs = byts / sec / 1e9
+        peak_tf = peaks.get("bf16_tflops_sustained") or peaks.get("bf16_tflops")
+        roof = {
+            "bound": "tensor", "kernel": "chunked fwd+bwd pipeline (all launches of one step)",
+            "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf, "traffic": None,
+            "peak_source": f"{how} (bf16 sustained)", "flops_per_launch": flops,
+            "hbm": {"achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                    "algorithmic_bytes": byts},
+        }
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            T_s = min(T, 1024)
+            val, sec_cpu = time_cpu_port(T_s, H, K, V, C)
+            cpu = {"value": val, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+                   "sample": f"B=1 T={T_s} of {args.workload} (H={H} K={K} V={V} chunk {C}) fp32, one pass, "
+                             f"{sec_cpu:.1f} s"}
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
+            "vs_baseline": None, "dtype": dt, "data": "synthetic",
+            "config": {"workload": args.workload, "B_per_step": B * (world if args.scaling == "weak" else 1), "T": T,
+                       "H": H, "K": K, "V": V, "R": R, "chunk": C, "sharding": "batch x head, no collective",
+                       "backward": "saved forward intermediates" if HD.hrdplr.save_workspace_default() else "recompute",
+                       "l2": "inputs (>1 GB per step) are larger than the 126 MB L2"},
+            "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

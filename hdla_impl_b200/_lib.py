@@ -18,7 +18,7 @@ FLAG_FORCE_SIMT = 2
 
 EXPORTS = (
     "hdla_version", "hdla_last_error", "hdla_chunk_workspace_bytes", "hdla_chunk_fwd", "hdla_chunk_bwd",
-    "hdla_recurrent_fwd",
+    "hdla_recurrent_fwd", "hdla_kernel_launches",
 )
 
 
@@ -53,6 +53,8 @@ def load() -> C.CDLL:
         lib.hdla_version.argtypes = []
         lib.hdla_last_error.restype = C.c_char_p
         lib.hdla_last_error.argtypes = []
+        lib.hdla_kernel_launches.restype = C.c_ulonglong
+        lib.hdla_kernel_launches.argtypes = []
         lib.hdla_chunk_workspace_bytes.restype = C.c_size_t
         lib.hdla_chunk_workspace_bytes.argtypes = [dp, C.c_int]
         lib.hdla_chunk_fwd.restype = C.c_int
@@ -65,6 +67,10 @@ def load() -> C.CDLL:
                                            vp, C.c_int32, C.c_int32, vp]
         _lib = lib
         return lib
+
+
+def kernel_launches() -> int:
+    return int(load().hdla_kernel_launches())
 
 
 def last_error() -> str:

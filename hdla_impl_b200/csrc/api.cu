@@ -4,9 +4,14 @@
 #include <cstdio>
 #include <cstring>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace hdla {
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 static thread_local char g_err[512] = "";
 
@@ -48,6 +53,8 @@ extern "C" {
 int hdla_version(void) { return HDLA_VERSION; }
 
 const char* hdla_last_error(void) { return g_err; }
+
+unsigned long long hdla_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
 size_t hdla_chunk_workspace_bytes(const HdlaDims* dims, int with_backward) {
     if (check_common(dims, true) != HDLA_OK) return 0;

@@ -11,8 +11,12 @@ namespace hdla {
 // Records a message for hdla_last_error() and returns `code`.
 int fail(int code, const char* fmt, ...);
 
+// Process-wide count of kernel launches (see hdla_kernel_launches()).
+void count_launch();
+
 #define HDLA_CHECK_LAUNCH(what)                                                       \
     do {                                                                              \
+        ::hdla::count_launch();                                                       \
         cudaError_t e__ = cudaGetLastError();                                         \
         if (e__ != cudaSuccess)                                                       \
             return ::hdla::fail(HDLA_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e__)); \

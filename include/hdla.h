@@ -72,6 +72,11 @@ HDLA_API int hdla_version(void);
  * the same thread's next failing call. */
 HDLA_API const char* hdla_last_error(void);
 
+/* Number of kernels this library has launched in the calling process so far (all threads).
+ * Instrumentation for benchmarks; it has no counterpart in the reference, whose launches are
+ * issued by the Triton runtime. */
+HDLA_API unsigned long long hdla_kernel_launches(void);
+
 /* Bytes of device workspace hdla_chunk_fwd (with_backward = 0) or the pair hdla_chunk_fwd +
  * hdla_chunk_bwd (with_backward = 1) needs for these dims; 0 if the dims are unsupported (see
  * hdla_last_error).  Replaces the torch.empty(...) intermediates the reference's stage
