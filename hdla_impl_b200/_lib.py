@@ -18,7 +18,7 @@ FLAG_FORCE_SIMT = 2
 
 EXPORTS = (
     "hdla_version", "hdla_last_error", "hdla_chunk_workspace_bytes", "hdla_chunk_fwd", "hdla_chunk_bwd",
-    "hdla_recurrent_fwd", "hdla_kernel_launches",
+    "hdla_recurrent_fwd", "hdla_kernel_launches", "hdla_debug_tc_buffer",
 )
 
 
@@ -55,6 +55,8 @@ def load() -> C.CDLL:
         lib.hdla_last_error.argtypes = []
         lib.hdla_kernel_launches.restype = C.c_ulonglong
         lib.hdla_kernel_launches.argtypes = []
+        lib.hdla_debug_tc_buffer.restype = C.c_int
+        lib.hdla_debug_tc_buffer.argtypes = [dp, vp, C.c_char_p, vp, vp]
         lib.hdla_chunk_workspace_bytes.restype = C.c_size_t
         lib.hdla_chunk_workspace_bytes.argtypes = [dp, C.c_int]
         lib.hdla_chunk_fwd.restype = C.c_int

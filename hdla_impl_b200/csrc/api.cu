@@ -56,9 +56,30 @@ const char* hdla_last_error(void) { return g_err; }
 
 unsigned long long hdla_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
+// Workspace layout: [tensor-core region (bf16 inputs only)] [fp32 CUDA-core region].
+static size_t tc_region_bytes(const HdlaDims& d, int with_backward) {
+    return tc_supported(d) ? tc_workspace_bytes(d, with_backward) : 0;
+}
+
 size_t hdla_chunk_workspace_bytes(const HdlaDims* dims, int with_backward) {
     if (check_common(dims, true) != HDLA_OK) return 0;
-    return simt_workspace_floats(*dims, with_backward) * sizeof(float);
+    const size_t simt = simt_workspace_floats(*dims, with_backward) * sizeof(float);
+    if (simt == 0) return 0;
+    if (tc_supported(*dims)) {
+        // forward runs on the tensor cores; backward still needs the fp32 region
+        return tc_region_bytes(*dims, with_backward) + (with_backward ? simt : 0);
+    }
+    return simt;
+}
+
+int hdla_debug_tc_buffer(const HdlaDims* dims, const void* workspace, const char* name, float* out,
+                         void* cuda_stream) {
+    int rc = check_common(dims, true);
+    if (rc != HDLA_OK) return rc;
+    if (!tc_supported(*dims)) return fail(HDLA_ERR_UNSUPPORTED, "no tensor-core workspace for these dims");
+    if (!workspace || !name || !out) return fail(HDLA_ERR_INVALID, "debug_tc_buffer: null argument");
+    return tc_debug_buffer(*dims, static_cast<const unsigned char*>(workspace), name, out,
+                           static_cast<cudaStream_t>(cuda_stream));
 }
 
 int hdla_chunk_fwd(const HdlaDims* dims, const void* q, const void* k, const void* v, const void* a, const void* b,
@@ -69,6 +90,9 @@ int hdla_chunk_fwd(const HdlaDims* dims, const void* q, const void* k, const voi
     if (!q || !k || !v || !a || !b || !gk || !o) return fail(HDLA_ERR_INVALID, "chunk_fwd: null tensor pointer");
     rc = check_ws(dims, workspace, workspace_bytes, 0);
     if (rc != HDLA_OK) return rc;
+    if (tc_supported(*dims))
+        return tc_chunk_fwd(*dims, q, k, v, a, b, gk, scale, h0, o, ht, static_cast<unsigned char*>(workspace), true,
+                            static_cast<cudaStream_t>(cuda_stream));
     return simt_chunk_fwd(*dims, q, k, v, a, b, gk, scale, h0, o, ht, static_cast<float*>(workspace), true,
                           static_cast<cudaStream_t>(cuda_stream));
 }
@@ -83,8 +107,15 @@ int hdla_chunk_bwd(const HdlaDims* dims, const void* q, const void* k, const voi
         return fail(HDLA_ERR_INVALID, "chunk_bwd: null tensor pointer");
     rc = check_ws(dims, workspace, workspace_bytes, 1);
     if (rc != HDLA_OK) return rc;
-    return simt_chunk_bwd(*dims, q, k, v, a, b, gk, scale, h0, d_o, dht, dq, dk, dv, da, db, dgk, dh0,
-                          static_cast<float*>(workspace), static_cast<cudaStream_t>(cuda_stream));
+    HdlaDims d = *dims;
+    unsigned char* ws = static_cast<unsigned char*>(workspace);
+    if (tc_supported(d)) {
+        // the fp32 region follows the tensor-core region and was not filled by the tensor-core forward
+        ws += tc_region_bytes(d, 1);
+        d.flags &= ~HDLA_FLAG_WS_HOLDS_FWD;
+    }
+    return simt_chunk_bwd(d, q, k, v, a, b, gk, scale, h0, d_o, dht, dq, dk, dv, da, db, dgk, dh0,
+                          reinterpret_cast<float*>(ws), static_cast<cudaStream_t>(cuda_stream));
 }
 
 int hdla_recurrent_fwd(const HdlaDims* dims, const void* q, const void* k, const void* v, const void* a,

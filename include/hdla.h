@@ -84,6 +84,13 @@ HDLA_API unsigned long long hdla_kernel_launches(void);
  * HRDPLR/bwd_func.py:33-36,84-86,139,181-185,238-241,300-309. */
 HDLA_API size_t hdla_chunk_workspace_bytes(const HdlaDims* dims, int with_backward);
 
+/* Debugging aid for tests: converts one named bf16 tile buffer of the tensor-core workspace
+ * ("Qh","Kh","Ah","Bh","Vc","Aqk","Aqb","Aak","Aab","M","W","P","U","Hs","V2") to fp32 row-major
+ * [B*H*NT][rows][cols] in `out` (device memory), or copies "E" / the 4-byte "status" word.  It has no
+ * counterpart in the reference, whose intermediates are ordinary torch tensors. */
+HDLA_API int hdla_debug_tc_buffer(const HdlaDims* dims, const void* workspace, const char* name, float* out,
+                                  void* cuda_stream);
+
 /* Chunked forward.  Replaces chunk_hrdplr_fwd (HRDPLR/hrdplr.py:25-99), i.e. the stage
  * sequence cumsum -> intra-chunk A matrices -> (I-Aab)^-1 and w/u -> state scan -> output.
  *   h0  : [B,H,K,V] fp32 initial state or NULL (zero state)
