@@ -56,7 +56,7 @@ const char* hdla_last_error(void) { return g_err; }
 
 unsigned long long hdla_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
-// Workspace layout: [tensor-core region (bf16 inputs only)] [fp32 CUDA-core region].
+// bf16 problems the tensor-core pipeline supports use its workspace plan, everything else the fp32 one.
 static size_t tc_region_bytes(const HdlaDims& d, int with_backward) {
     return tc_supported(d) ? tc_workspace_bytes(d, with_backward) : 0;
 }
@@ -65,10 +65,7 @@ size_t hdla_chunk_workspace_bytes(const HdlaDims* dims, int with_backward) {
     if (check_common(dims, true) != HDLA_OK) return 0;
     const size_t simt = simt_workspace_floats(*dims, with_backward) * sizeof(float);
     if (simt == 0) return 0;
-    if (tc_supported(*dims)) {
-        // forward runs on the tensor cores; backward still needs the fp32 region
-        return tc_region_bytes(*dims, with_backward) + (with_backward ? simt : 0);
-    }
+    if (tc_supported(*dims)) return tc_region_bytes(*dims, with_backward);
     return simt;
 }
 
@@ -107,15 +104,11 @@ int hdla_chunk_bwd(const HdlaDims* dims, const void* q, const void* k, const voi
         return fail(HDLA_ERR_INVALID, "chunk_bwd: null tensor pointer");
     rc = check_ws(dims, workspace, workspace_bytes, 1);
     if (rc != HDLA_OK) return rc;
-    HdlaDims d = *dims;
-    unsigned char* ws = static_cast<unsigned char*>(workspace);
-    if (tc_supported(d)) {
-        // the fp32 region follows the tensor-core region and was not filled by the tensor-core forward
-        ws += tc_region_bytes(d, 1);
-        d.flags &= ~HDLA_FLAG_WS_HOLDS_FWD;
-    }
-    return simt_chunk_bwd(d, q, k, v, a, b, gk, scale, h0, d_o, dht, dq, dk, dv, da, db, dgk, dh0,
-                          reinterpret_cast<float*>(ws), static_cast<cudaStream_t>(cuda_stream));
+    if (tc_supported(*dims))
+        return tc_chunk_bwd(*dims, q, k, v, a, b, gk, scale, h0, d_o, dht, dq, dk, dv, da, db, dgk, dh0,
+                            static_cast<unsigned char*>(workspace), static_cast<cudaStream_t>(cuda_stream));
+    return simt_chunk_bwd(*dims, q, k, v, a, b, gk, scale, h0, d_o, dht, dq, dk, dv, da, db, dgk, dh0,
+                          static_cast<float*>(workspace), static_cast<cudaStream_t>(cuda_stream));
 }
 
 int hdla_recurrent_fwd(const HdlaDims* dims, const void* q, const void* k, const void* v, const void* a,

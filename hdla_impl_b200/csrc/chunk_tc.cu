@@ -14,6 +14,7 @@
 // All matrices between kernels are bf16 in the C8 blocked layout (tc_tiles.cuh) and move with
 // bulk asynchronous copies; all products run on tcgen05.mma with fp32 accumulation in TMEM.
 #include <cstring>
+#include <initializer_list>
 
 #include "tc_tiles.cuh"
 
@@ -33,7 +34,8 @@ constexpr int CH128 = 16 * 128;    // chunks of a [128 x 128] tile
 struct TcPlan {
     int B, T, H, NT, BH;
     long long G;
-    size_t status, Qh, Kh, Ah, Bh, Vc, E, ghat, Aqk, Aqb, Aak, Aab, M, W, P, U, Hs, V2;
+    size_t status, Qh, Kh, Ah, Bh, Vc, E, ghat, Aqk, Aqb, Aak, Aab, M, W, P, U, Hs, V2, HT;
+    size_t dOc, dAqk, dAqb, DV2, DE, dgl, dW, dP, dAak, dM, tmp, dAab, dQh, dKh, dAh, dBh;
     size_t total_fwd, total;
 };
 
@@ -54,7 +56,12 @@ TcPlan make_tc_plan(const HdlaDims& d) {
     p.E = take(K * 4); p.ghat = take(C * K * 4);
     p.Aqk = take(8192); p.Aqb = take(16384); p.Aak = take(16384); p.Aab = take(32768); p.M = take(32768);
     p.W = take(32768); p.P = take(32768); p.U = take(32768); p.Hs = take(32768); p.V2 = take(32768);
+    p.HT = off; off += (((size_t)p.BH * K * V * 4 + 255) / 256) * 256;
     p.total_fwd = off;
+    p.dOc = take(16384); p.dAqk = take(8192); p.dAqb = take(16384); p.DV2 = take(32768); p.DE = take(32768);
+    p.dgl = take(K * 4); p.dW = take(32768); p.dP = take(32768); p.dAak = take(16384); p.dM = take(32768);
+    p.tmp = take(32768); p.dAab = take(32768); p.dQh = take(16384); p.dKh = take(16384); p.dAh = take(32768);
+    p.dBh = take(32768);
     p.total = off;
     return p;
 }
@@ -441,52 +448,66 @@ __global__ void __launch_bounds__(128) wu_tc_kernel(WuP p) {
 }
 
 // ------------------------------------------------------------------------------------------
-// K5: inter-chunk state scan   (HRDPLR/fwd_triton.py:795-968; HRDPLR/naive.py:232-255)
-//   per chunk:  St = E (.) S ;  v2 = Wh St + u ;  S <- E (.) (St + Kh^T v + Bh^T v2)
-// One CTA (8 warps) per (batch, head).  The fp32 state lives in registers: thread (k = lane of
-// warp%4, column half = warp/4) owns S[k, 64 columns].  The operands of the next chunk are
+// K5: inter-chunk state scans, forward and reverse, one kernel
+//   forward (HRDPLR/fwd_triton.py:795-968; HRDPLR/naive.py:232-255), per chunk n = 0..NT-1:
+//       St = E (.) S ;  v2 = Wh St + u ;  S <- E (.) (St + Kh^T v + Bh^T v2)
+//   reverse (HRDPLR/bwd_triton.py:110-222), per chunk n = NT-1..0, dS the gradient of the state
+//   leaving the chunk:
+//       dSt = E (.) dS ;  dv2 = Bh dSt + dv2_intra ;  dS <- E (.) (dSt + Qh^T dO + Wh^T dv2)
+//   and the gradient of the chunk-end log decay, dgl[k] = sum_v dS[k,v] S_{n+1}[k,v]
+//   (every term of S_{n+1} carries the factor e^{g_last}; HRDPLR/bwd_triton.py:400,442,457-459).
+// Both have the form  T = E(.)X ; Y = A1 T + ADD ; X <- E(.)(T + L1^T R1 + L2^T Y).
+// One CTA (8 warps) per (batch, head).  The fp32 state lives in registers: thread (row = lane of
+// warp%4, column half = warp/4) owns X[row, 64 columns].  The operands of the next chunk are
 // prefetched by bulk copies as soon as the product that reads their buffer has completed.
 // ------------------------------------------------------------------------------------------
 struct ScanTcP {
-    const uint4 *W, *U, *Kh, *Bh, *Vc;
+    const uint4 *A1, *ADD, *L1, *R1, *L2;   // fwd: Wh, u, Kh, v, Bh      rev: Bh, dv2_intra, Qh, dO, Wh
     const float* E;
-    const float* h0;
-    uint4 *Hs, *V2;
-    float* ht;
-    int NT;
+    const float* init;                       // fwd: h0, rev: dht (may be null)
+    uint4 *CK, *Y;                           // fwd: Hs (St checkpoints), v2     rev: dSt checkpoints, dv2
+    float* fin;                              // fwd: final state, rev: dh0 (may be null)
+    float* fin2;                             // second copy of the final value (workspace), may be null
+    const uint4* Hs;                         // rev only: forward checkpoints, for dgl
+    const float* HT;                         // rev only: forward final state
+    float* dgl;                              // rev only
+    int NT, reverse;
     int* status;
 };
 
-__global__ void __launch_bounds__(256) scan_fwd_tc_kernel(ScanTcP p) {
+__global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    uint4* sW = reinterpret_cast<uint4*>(smem);      // 32 KB
-    uint4* sU = sW + CH128;                          // 32 KB
-    uint4* sKh = sU + CH128;                         // 16 KB
-    uint4* sV = sKh + CH64;                          // 16 KB
-    uint4* sBh = sV + CH64;                          // 32 KB
-    uint4* sSt = sBh + CH128;                        // 32 KB  St [k x v]
-    uint4* sV2 = sSt + CH128;                        // 32 KB  v2 [128 x v]
+    uint4* sA1 = reinterpret_cast<uint4*>(smem);     // 32 KB
+    uint4* sADD = sA1 + CH128;                       // 32 KB
+    uint4* sL1 = sADD + CH128;                       // 16 KB
+    uint4* sR1 = sL1 + CH64;                         // 16 KB
+    uint4* sL2 = sR1 + CH64;                         // 32 KB
+    uint4* sT = sL2 + CH128;                         // 32 KB  T [k x v]
+    uint4* sY = sT + CH128;                          // 32 KB  Y [128 x v]
     __shared__ __align__(8) uint64_t ldA, ldB, barA, barB;
     __shared__ uint32_t tmem_s;
+    __shared__ float red[K];
     const int bh = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int row = (warp & 3) * 32 + lane;          // TMEM lane = k (state) or a/b row (v2)
-    const int half = warp >> 2;                      // which 64 columns
+    const int row = (warp & 3) * 32 + lane;
+    const int half = warp >> 2;
     if (warp == 0) { tmem_alloc(&tmem_s, 256); tmem_relinquish(); }
     const long long g0 = (long long)bh * p.NT;
+    const int n_first = p.reverse ? p.NT - 1 : 0, dn = p.reverse ? -1 : 1;
     if (tid == 0) {
+        const long long g = g0 + n_first;
         mbar_init(&ldA, 1); mbar_init(&ldB, 1); mbar_init(&barA, 1); mbar_init(&barB, 1); fence_mbar_init();
         mbar_expect_tx(&ldA, 65536);
-        bulk_g2s(sW, p.W + g0 * CH128, 32768, &ldA);
-        bulk_g2s(sU, p.U + g0 * CH128, 32768, &ldA);
+        bulk_g2s(sA1, p.A1 + g * CH128, 32768, &ldA);
+        bulk_g2s(sADD, p.ADD + g * CH128, 32768, &ldA);
         mbar_expect_tx(&ldB, 65536);
-        bulk_g2s(sKh, p.Kh + g0 * CH64, 16384, &ldB);
-        bulk_g2s(sV, p.Vc + g0 * CH64, 16384, &ldB);
-        bulk_g2s(sBh, p.Bh + g0 * CH128, 32768, &ldB);
+        bulk_g2s(sL1, p.L1 + g * CH64, 16384, &ldB);
+        bulk_g2s(sR1, p.R1 + g * CH64, 16384, &ldB);
+        bulk_g2s(sL2, p.L2 + g * CH128, 32768, &ldB);
     }
     float S[64];
-    if (p.h0) {
-        const float4* src = reinterpret_cast<const float4*>(p.h0 + ((size_t)bh * K + row) * V + half * 64);
+    if (p.init) {
+        const float4* src = reinterpret_cast<const float4*>(p.init + ((size_t)bh * K + row) * V + half * 64);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float4 x = src[j];
@@ -500,13 +521,37 @@ __global__ void __launch_bounds__(256) scan_fwd_tc_kernel(ScanTcP p) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_s;
-    const Tile tW = t8::tile(sW, 128), tKh = t8::tile(sKh, 64), tV = t8::tile(sV, 64), tBh = t8::tile(sBh, 128),
-               tSt = t8::tile(sSt, 128), tV2 = t8::tile(sV2, 128);
-    for (int n = 0; n < p.NT; ++n) {
+    const Tile tA1 = t8::tile(sA1, 128), tL1 = t8::tile(sL1, 64), tR1 = t8::tile(sR1, 64), tL2 = t8::tile(sL2, 128),
+               tT = t8::tile(sT, 128), tY = t8::tile(sY, 128);
+    for (int it = 0; it < p.NT; ++it) {
+        const int n = n_first + it * dn;
         const long long g = g0 + n;
-        const uint32_t ph = n & 1;
+        const uint32_t ph = it & 1;
+        const bool more = it + 1 < p.NT;
         const float e = p.E[(size_t)g * K + row];
-        // St = E (.) S  -> operand tile and checkpoint
+        float part = 0.f;
+        if (p.reverse) {                      // dgl = rowsum(dS (.) S_{n+1})
+            if (n + 1 < p.NT) {
+                const float inv = 1.f / p.E[(size_t)(g + 1) * K + row];
+#pragma unroll
+                for (int c8 = 0; c8 < 8; ++c8) {
+                    float f[8];
+                    t8::unpack8(p.Hs[(g + 1) * CH128 + (half * 8 + c8) * 128 + row], f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) part = fmaf(S[c8 * 8 + j], f[j] * inv, part);
+                }
+            } else {
+                const float4* src = reinterpret_cast<const float4*>(p.HT + ((size_t)bh * K + row) * V + half * 64);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float4 x = src[j];
+                    part = fmaf(S[4 * j], x.x, part); part = fmaf(S[4 * j + 1], x.y, part);
+                    part = fmaf(S[4 * j + 2], x.z, part); part = fmaf(S[4 * j + 3], x.w, part);
+                }
+            }
+            if (half == 1) red[row] = part;
+        }
+        // T = E (.) X  -> operand tile and checkpoint
 #pragma unroll
         for (int c8 = 0; c8 < 8; ++c8) {
             float f[8];
@@ -514,56 +559,57 @@ __global__ void __launch_bounds__(256) scan_fwd_tc_kernel(ScanTcP p) {
             for (int j = 0; j < 8; ++j) f[j] = e * S[c8 * 8 + j];
             const uint4 c = t8::pack8(f);
             const int cg = half * 8 + c8;
-            sSt[cg * 128 + row] = c;
-            p.Hs[g * CH128 + cg * 128 + row] = c;
+            sT[cg * 128 + row] = c;
+            p.CK[g * CH128 + cg * 128 + row] = c;
         }
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
+        if (p.reverse && half == 0) p.dgl[(size_t)g * K + row] = part + red[row];
         if (tid == 0) {
             wait_or_flag(&ldA, ph, p.status, 11);
             tc_fence_after();
-            t8::mma_chain<false, true>(tmem, tW, 0, 0, tSt, 0, 0, 128, 128, false);      // Wh St
+            t8::mma_chain<false, true>(tmem, tA1, 0, 0, tT, 0, 0, 128, 128, false);      // A1 T
             umma_commit(&barA);
         }
         wait_or_flag(&barA, ph, p.status, 12);
-        wait_or_flag(&ldA, ph, p.status, 13);         // u is read from shared memory below
+        wait_or_flag(&ldA, ph, p.status, 13);         // ADD is read from shared memory below
         tc_fence_after();
 #pragma unroll
         for (int c8 = 0; c8 < 8; ++c8) {
             const int cg = half * 8 + c8;
             uint32_t v[8]; float f[8], u[8];
             tmem_ld_x8(t8::taddr(tmem, warp, cg * 8), v);
-            t8::unpack8(sU[cg * 128 + row], u);
+            t8::unpack8(sADD[cg * 128 + row], u);
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]) + u[j];
             const uint4 c = t8::pack8(f);
-            sV2[cg * 128 + row] = c;
-            p.V2[g * CH128 + cg * 128 + row] = c;
+            sY[cg * 128 + row] = c;
+            p.Y[g * CH128 + cg * 128 + row] = c;
         }
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
         if (tid == 0) {
-            if (n + 1 < p.NT) {                        // W and u buffers are free: prefetch the next chunk's
+            if (more) {                                // A1 and ADD buffers are free: prefetch the next chunk's
                 mbar_expect_tx(&ldA, 65536);
-                bulk_g2s(sW, p.W + (g + 1) * CH128, 32768, &ldA);
-                bulk_g2s(sU, p.U + (g + 1) * CH128, 32768, &ldA);
+                bulk_g2s(sA1, p.A1 + (g + dn) * CH128, 32768, &ldA);
+                bulk_g2s(sADD, p.ADD + (g + dn) * CH128, 32768, &ldA);
             }
             wait_or_flag(&ldB, ph, p.status, 14);
             tc_fence_after();
-            t8::mma_chain<true, true>(tmem + 128, tKh, 0, 0, tV, 0, 0, 128, 64, false);  // Kh^T v
-            t8::mma_chain<true, true>(tmem + 128, tBh, 0, 0, tV2, 0, 0, 128, 128, true); // + Bh^T v2
+            t8::mma_chain<true, true>(tmem + 128, tL1, 0, 0, tR1, 0, 0, 128, 64, false);   // L1^T R1
+            t8::mma_chain<true, true>(tmem + 128, tL2, 0, 0, tY, 0, 0, 128, 128, true);    // + L2^T Y
             umma_commit(&barB);
         }
         wait_or_flag(&barB, ph, p.status, 15);
         tc_fence_after();
-        if (tid == 0 && n + 1 < p.NT) {
+        if (tid == 0 && more) {
             mbar_expect_tx(&ldB, 65536);
-            bulk_g2s(sKh, p.Kh + (g + 1) * CH64, 16384, &ldB);
-            bulk_g2s(sV, p.Vc + (g + 1) * CH64, 16384, &ldB);
-            bulk_g2s(sBh, p.Bh + (g + 1) * CH128, 32768, &ldB);
+            bulk_g2s(sL1, p.L1 + (g + dn) * CH64, 16384, &ldB);
+            bulk_g2s(sR1, p.R1 + (g + dn) * CH64, 16384, &ldB);
+            bulk_g2s(sL2, p.L2 + (g + dn) * CH128, 32768, &ldB);
         }
 #pragma unroll
         for (int c8 = 0; c8 < 8; ++c8) {
@@ -575,13 +621,197 @@ __global__ void __launch_bounds__(256) scan_fwd_tc_kernel(ScanTcP p) {
         }
         tc_fence_before();
     }
-    if (p.ht) {
-        float4* dst = reinterpret_cast<float4*>(p.ht + ((size_t)bh * K + row) * V + half * 64);
+    {
+        const size_t off = ((size_t)bh * K + row) * V + half * 64;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) dst[j] = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+        for (int j = 0; j < 16; ++j) {
+            const float4 x = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+            if (p.fin) reinterpret_cast<float4*>(p.fin + off)[j] = x;
+            if (p.fin2) reinterpret_cast<float4*>(p.fin2 + off)[j] = x;
+        }
     }
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+// ------------------------------------------------------------------------------------------
+// generic product over C8 tiles:  D[rows x N] = sum_c op(A_c) op(B_c)^T  (up to three chains),
+// optional causal mask, written as a C8 tile or as bf16 rows of a [B,T,H,N] tensor.
+// Used for every per-chunk product of the backward pass (HRDPLR/bwd_triton.py kernels dAu, dv,
+// bwd_o, wy, and the score-gradient applications of intra) with the operands chosen per call.
+// ------------------------------------------------------------------------------------------
+struct Opnd {
+    const uint4* p;
+    int rows, cols;       // tile shape
+    int mn;               // 0: contraction over the tile's columns, 1: over its rows
+};
+struct ChainP {
+    Opnd A[3], B[3];
+    int kdim[3];
+    int nchains;
+    int N;                // output columns (multiple of 16, <= 128)
+    int out_rows;         // 64 or 128
+    uint4* out;           // C8 tile output [out_rows x N] per chunk, or null
+    __nv_bfloat16* out_rows_bthn;   // else: rows t = n*64 + r of a [B,T,H,N] tensor
+    int mask, ri, rj;     // 0 none, 1 keep (r/ri) >= (c/rj), 2 keep (r/ri) > (c/rj)
+    int T, H, NT;
+    int* status;
+};
+
+__global__ void __launch_bounds__(128) chain_tc_kernel(ChainP p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ __align__(8) uint64_t ld_bar, mma_bar;
+    __shared__ uint32_t tmem_s;
+    const long long g = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    if (warp == 0) { tmem_alloc(&tmem_s, 128); tmem_relinquish(); }
+    Tile tA[3], tB[3];
+    {
+        uint32_t off = 0, total = 0;
+        for (int c = 0; c < p.nchains; ++c) total += (uint32_t)(p.A[c].rows * p.A[c].cols + p.B[c].rows * p.B[c].cols) * 2u;
+        if (tid == 0) {
+            mbar_init(&ld_bar, 1); mbar_init(&mma_bar, 1); fence_mbar_init();
+            mbar_expect_tx(&ld_bar, total);
+        }
+        for (int c = 0; c < p.nchains; ++c) {           // A tiles first: the ones read past their end (64-row A in an
+            const uint32_t bytes = (uint32_t)p.A[c].rows * p.A[c].cols * 2u;   // M=128 product) are followed by B tiles
+            tA[c] = t8::tile(smem + off, p.A[c].rows);
+            if (tid == 0) bulk_g2s(smem + off, p.A[c].p + g * (bytes / 16), bytes, &ld_bar);
+            off += bytes;
+        }
+        for (int c = 0; c < p.nchains; ++c) {
+            const uint32_t bytes = (uint32_t)p.B[c].rows * p.B[c].cols * 2u;
+            tB[c] = t8::tile(smem + off, p.B[c].rows);
+            if (tid == 0) bulk_g2s(smem + off, p.B[c].p + g * (bytes / 16), bytes, &ld_bar);
+            off += bytes;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_s;
+    wait_or_flag(&ld_bar, 0, p.status, 20);
+    if (tid == 0) {
+        for (int c = 0; c < p.nchains; ++c) {
+            const bool acc = c > 0;
+            if (!p.A[c].mn && !p.B[c].mn) t8::mma_chain<false, false>(tmem, tA[c], 0, 0, tB[c], 0, 0, p.N, p.kdim[c], acc);
+            else if (!p.A[c].mn && p.B[c].mn) t8::mma_chain<false, true>(tmem, tA[c], 0, 0, tB[c], 0, 0, p.N, p.kdim[c], acc);
+            else if (p.A[c].mn && !p.B[c].mn) t8::mma_chain<true, false>(tmem, tA[c], 0, 0, tB[c], 0, 0, p.N, p.kdim[c], acc);
+            else t8::mma_chain<true, true>(tmem, tA[c], 0, 0, tB[c], 0, 0, p.N, p.kdim[c], acc);
+        }
+        umma_commit(&mma_bar);
+    }
+    wait_or_flag(&mma_bar, 0, p.status, 21);
+    tc_fence_after();
+    if (warp * 32 < p.out_rows) {
+        const int r = tid;
+        uint4* dst_rows = nullptr;
+        bool row_ok = true;
+        if (!p.out) {
+            const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
+            const int b = bh / p.H, h = bh % p.H;
+            const int t = n * C + r;
+            row_ok = t < p.T;
+            dst_rows = reinterpret_cast<uint4*>(p.out_rows_bthn + (((size_t)b * p.T + (row_ok ? t : 0)) * p.H + h) * p.N);
+        }
+        for (int cg = 0; cg < p.N / 8; ++cg) {
+            uint32_t v[8]; float f[8];
+            tmem_ld_x8(t8::taddr(tmem, warp, cg * 8), v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int c = cg * 8 + j;
+                bool keep = true;
+                if (p.mask == 1) keep = (r / p.ri) >= (c / p.rj);
+                else if (p.mask == 2) keep = (r / p.ri) > (c / p.rj);
+                f[j] = keep ? __uint_as_float(v[j]) : 0.f;
+            }
+            const uint4 c = t8::pack8(f);
+            if (p.out) p.out[g * (long long)(p.out_rows * p.N / 8) + cg * p.out_rows + r] = c;
+            else if (row_ok) dst_rows[cg] = c;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 128);
+}
+
+// dO rows of the public [B,T,H,V] tensor -> C8 tile [64 x 128] per chunk
+__global__ void __launch_bounds__(128) rows_to_c8_kernel(const __nv_bfloat16* src, uint4* dst, int T, int H, int NT) {
+    const long long g = blockIdx.x;
+    const int bh = (int)(g / NT), n = (int)(g % NT);
+    const int b = bh / H, h = bh % H;
+    const int r = threadIdx.x & 63;
+    const int t = n * C + r;
+    for (int s = 0; s < 8; ++s) {
+        const int kc = (threadIdx.x >> 6) * 8 + s;
+        uint4 c = make_uint4(0, 0, 0, 0);
+        if (t < T) c = *reinterpret_cast<const uint4*>(src + (((size_t)b * T + t) * H + h) * V + kc * 8);
+        dst[g * CH64 + kc * 64 + r] = c;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// backward assembly (CUDA cores, streaming): from the gradients of the hat operands to the
+// public gradients and the log-decay gradient
+//   dq = scale e^{gi-half} dQh, dk = e^{half-gi} dKh, da = e^{ge-half} dAh, db = e^{half-gi} dBh
+//   dgk = revcumsum(Qh dQh - Kh dKh - sum_r Bh dBh + sum_r Ah dAh) - sum_r Ah dAh + dgl
+//   (HRDPLR/bwd_triton.py:854-880 and :944-946)
+// ------------------------------------------------------------------------------------------
+struct FinalP {
+    const uint4 *Qh, *Kh, *Ah, *Bh, *dQh, *dKh, *dAh, *dBh;
+    const float *ghat, *dgl;
+    __nv_bfloat16 *dq, *dk, *da, *db;
+    void* dgk;
+    float scale;
+    int T, H, NT, gdt;
+};
+
+__device__ __forceinline__ float c8g(const uint4* tile, int rows, int r, int c) {
+    const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(tile + (c >> 3) * rows + r);
+    return __bfloat162float(q[c & 7]);
+}
+
+__global__ void __launch_bounds__(128) bwd_final_kernel(FinalP p) {
+    const long long g = blockIdx.x;
+    const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
+    const int b = bh / p.H, h = bh % p.H;
+    const int k = threadIdx.x;
+    const uint4 *Qh = p.Qh + g * CH64, *Kh = p.Kh + g * CH64, *dQh = p.dQh + g * CH64, *dKh = p.dKh + g * CH64;
+    const uint4 *Ah = p.Ah + g * CH128, *Bh = p.Bh + g * CH128, *dAh = p.dAh + g * CH128, *dBh = p.dBh + g * CH128;
+    const float* gh = p.ghat + (size_t)g * C * K;
+    const float half = gh[(size_t)(C - 1) * K + k];
+    const float dgl = p.dgl[(size_t)g * K + k];
+    float run = 0.f;
+    for (int i = C - 1; i >= 0; --i) {
+        const float x = gh[(size_t)i * K + k];
+        const float xe = i > 0 ? gh[(size_t)(i - 1) * K + k] : -half;
+        const float ep = __expf(x), em = __expf(-x), ee = __expf(xe);
+        const float qh = c8g(Qh, 64, i, k), dqh = c8g(dQh, 64, i, k);
+        const float kh = c8g(Kh, 64, i, k), dkh = c8g(dKh, 64, i, k);
+        float d_gi = qh * dqh - kh * dkh, d_ge = 0.f;
+        const int t = n * C + i;
+        const bool ok = t < p.T;
+#pragma unroll
+        for (int rr = 0; rr < R; ++rr) {
+            const float ah = c8g(Ah, 128, i * R + rr, k), dah = c8g(dAh, 128, i * R + rr, k);
+            const float bhv = c8g(Bh, 128, i * R + rr, k), dbh = c8g(dBh, 128, i * R + rr, k);
+            d_ge = fmaf(ah, dah, d_ge);
+            d_gi = fmaf(-bhv, dbh, d_gi);
+            if (ok) {
+                const size_t oa = (((size_t)b * p.T * R + (size_t)t * R + rr) * p.H + h) * K + k;
+                p.da[oa] = __float2bfloat16_rn(ee * dah);
+                p.db[oa] = __float2bfloat16_rn(em * dbh);
+            }
+        }
+        run += d_gi + d_ge;
+        if (ok) {
+            const size_t o = (((size_t)b * p.T + t) * p.H + h) * K + k;
+            p.dq[o] = __float2bfloat16_rn(p.scale * ep * dqh);
+            p.dk[o] = __float2bfloat16_rn(em * dkh);
+            st_elem(p.dgk, o, p.gdt, run - d_ge + dgl);
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -662,6 +892,8 @@ __global__ void c8_to_rowmajor_kernel(const uint4* src, float* dst, int rows, in
     }
 }
 
+constexpr int kChainSmemMax = 6 * 32768 + 32768;   // six tiles plus slack for 64-row A operands read as 128 rows
+
 template <typename Kern>
 int set_smem(Kern kern, int bytes) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
@@ -694,8 +926,9 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         TRY(set_smem(gram_tc_kernel, 98304 + 1024));
         TRY(set_smem(inverse_tc_kernel, 98304));
         TRY(set_smem(wu_tc_kernel, 98304));
-        TRY(set_smem(scan_fwd_tc_kernel, 196608));
+        TRY(set_smem(scan_tc_kernel, 196608));
         TRY(set_smem(out_tc_kernel, 122880));
+        TRY(set_smem(chain_tc_kernel, kChainSmemMax));
         attr_dev = dev;
     }
     auto U4 = [&](size_t off) { return reinterpret_cast<uint4*>(ws + off); };
@@ -716,16 +949,116 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     WuP wp{U4(pl.M), U4(pl.Ah), U4(pl.Aak), U4(pl.Vc), U4(pl.P), U4(pl.U), U4(pl.W), status};
     wu_tc_kernel<<<G, 128, 98304, st>>>(wp);
     HDLA_CHECK_LAUNCH("wu_tc_kernel");
-    ScanTcP sp{U4(pl.W), U4(pl.U), U4(pl.Kh), U4(pl.Bh), U4(pl.Vc), F(pl.E), h0, U4(pl.Hs), U4(pl.V2), ht, pl.NT,
-               status};
-    scan_fwd_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
-    HDLA_CHECK_LAUNCH("scan_fwd_tc_kernel");
+    ScanTcP sp{U4(pl.W), U4(pl.U), U4(pl.Kh), U4(pl.Vc), U4(pl.Bh), F(pl.E), h0, U4(pl.Hs), U4(pl.V2), ht, F(pl.HT),
+               nullptr, nullptr, nullptr, pl.NT, 0, status};
+    scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
+    HDLA_CHECK_LAUNCH("scan_tc_kernel");
     if (need_o) {
         OutP op{U4(pl.Qh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Vc), U4(pl.Hs), U4(pl.V2), (__nv_bfloat16*)o, d.T, d.H,
                 pl.NT, status};
         out_tc_kernel<<<G, 128, 122880, st>>>(op);
         HDLA_CHECK_LAUNCH("out_tc_kernel");
     }
+    return HDLA_OK;
+}
+
+namespace {
+Opnd opnd(const unsigned char* ws, size_t off, int rows, int cols, int mn) {
+    return Opnd{reinterpret_cast<const uint4*>(ws + off), rows, cols, mn};
+}
+}  // namespace
+
+int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a, const void* b,
+                 const void* gk, float scale, const float* h0, const void* d_o, const float* dht, void* dq, void* dk,
+                 void* dv, void* da, void* db, void* dgk, float* dh0, unsigned char* ws, cudaStream_t st) {
+    if (!(d.flags & HDLA_FLAG_WS_HOLDS_FWD))
+        TRY(tc_chunk_fwd(d, q, k, v, a, b, gk, scale, h0, nullptr, nullptr, ws, false, st));
+    const TcPlan pl = make_tc_plan(d);
+    auto U4 = [&](size_t off) { return reinterpret_cast<uint4*>(ws + off); };
+    auto F = [&](size_t off) { return reinterpret_cast<float*>(ws + off); };
+    int* status = reinterpret_cast<int*>(ws + pl.status);
+    const unsigned G = (unsigned)pl.G;
+    typedef __nv_bfloat16* bp;
+
+    rows_to_c8_kernel<<<G, 128, 0, st>>>((const __nv_bfloat16*)d_o, U4(pl.dOc), d.T, d.H, pl.NT);
+    HDLA_CHECK_LAUNCH("rows_to_c8_kernel");
+
+    // one product: up to three chains into one accumulator
+    struct Ch { Opnd A, B; int kdim; };
+    auto run = [&](std::initializer_list<Ch> chains, int N, int out_rows, size_t out_off, bp rows_out, int mask,
+                   int ri, int rj) -> int {
+        ChainP cp{};
+        int c = 0;
+        size_t bytes = 0;
+        for (const Ch& ch : chains) {
+            cp.A[c] = ch.A; cp.B[c] = ch.B; cp.kdim[c] = ch.kdim;
+            bytes += (size_t)(ch.A.rows * ch.A.cols + ch.B.rows * ch.B.cols) * 2;
+            ++c;
+        }
+        cp.nchains = c; cp.N = N; cp.out_rows = out_rows;
+        cp.out = rows_out ? nullptr : U4(out_off);
+        cp.out_rows_bthn = rows_out;
+        cp.mask = mask; cp.ri = ri; cp.rj = rj; cp.T = d.T; cp.H = d.H; cp.NT = pl.NT; cp.status = status;
+        bytes += 32768;                               // slack: 64-row A tiles are read as 128 rows
+        if (bytes > (size_t)kChainSmemMax) return fail(HDLA_ERR_UNSUPPORTED, "chain: %zu bytes of shared memory", bytes);
+        chain_tc_kernel<<<G, 128, bytes, st>>>(cp);
+        HDLA_CHECK_LAUNCH("chain_tc_kernel");
+        return HDLA_OK;
+    };
+    const unsigned char* w = ws;
+    // tiles (rows, cols); last argument: 0 = contract over columns, 1 = contract over rows
+    auto dOc = [&](int mn) { return opnd(w, pl.dOc, 64, 128, mn); };
+    auto Vc = [&](int mn) { return opnd(w, pl.Vc, 64, 128, mn); };
+    auto V2 = [&](int mn) { return opnd(w, pl.V2, 128, 128, mn); };
+    auto DV2 = [&](int mn) { return opnd(w, pl.DV2, 128, 128, mn); };
+    auto Hs = [&](int mn) { return opnd(w, pl.Hs, 128, 128, mn); };
+    auto DE = [&](int mn) { return opnd(w, pl.DE, 128, 128, mn); };
+    auto Qh = [&](int mn) { return opnd(w, pl.Qh, 64, 128, mn); };
+    auto Kh = [&](int mn) { return opnd(w, pl.Kh, 64, 128, mn); };
+    auto Ah = [&](int mn) { return opnd(w, pl.Ah, 128, 128, mn); };
+    auto Bh = [&](int mn) { return opnd(w, pl.Bh, 128, 128, mn); };
+    auto Mm = [&](int mn) { return opnd(w, pl.M, 128, 128, mn); };
+    auto Pp = [&](int mn) { return opnd(w, pl.P, 128, 128, mn); };
+    auto Aqk = [&](int mn) { return opnd(w, pl.Aqk, 64, 64, mn); };
+    auto Aqb = [&](int mn) { return opnd(w, pl.Aqb, 64, 128, mn); };
+    auto Aak = [&](int mn) { return opnd(w, pl.Aak, 128, 64, mn); };
+    auto dAqk = [&](int mn) { return opnd(w, pl.dAqk, 64, 64, mn); };
+    auto dAqb = [&](int mn) { return opnd(w, pl.dAqb, 64, 128, mn); };
+    auto dAak = [&](int mn) { return opnd(w, pl.dAak, 128, 64, mn); };
+    auto dAab = [&](int mn) { return opnd(w, pl.dAab, 128, 128, mn); };
+    auto dW = [&](int mn) { return opnd(w, pl.dW, 128, 128, mn); };
+    auto dP = [&](int mn) { return opnd(w, pl.dP, 128, 128, mn); };
+    auto dM = [&](int mn) { return opnd(w, pl.dM, 128, 128, mn); };
+    auto Tmp = [&](int mn) { return opnd(w, pl.tmp, 128, 128, mn); };
+
+    // --- dAu (HRDPLR/bwd_triton.py:17-105): dAqk = tril(dO v^T), dAqb = mask(dO v2^T), dv2_intra = Aqb^T dO
+    TRY(run({{dOc(0), Vc(0), 128}}, 64, 64, pl.dAqk, nullptr, 1, 1, 1));
+    TRY(run({{dOc(0), V2(0), 128}}, 128, 64, pl.dAqb, nullptr, 1, 1, R));
+    TRY(run({{Aqb(1), dOc(1), 64}}, 128, 128, pl.DV2, nullptr, 0, 1, 1));
+    // --- dhu: reverse scan (dv2 is accumulated in place over dv2_intra)
+    ScanTcP sp{U4(pl.Bh), U4(pl.DV2), U4(pl.Qh), U4(pl.dOc), U4(pl.W), F(pl.E), dht, U4(pl.DE), U4(pl.DV2), dh0, nullptr,
+               U4(pl.Hs), F(pl.HT), F(pl.dgl), pl.NT, 1, status};
+    scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
+    HDLA_CHECK_LAUNCH("scan_tc_kernel");
+    // --- dv = Kh dSt + Aqk^T dO + Aak^T dP with dP = M^T dv2   (bwd_triton.py:227-290 and wy :489-612)
+    TRY(run({{Mm(1), DV2(1), 128}}, 128, 128, pl.dP, nullptr, 0, 1, 1));
+    TRY(run({{Kh(0), DE(1), 128}, {Aqk(1), dOc(1), 64}, {Aak(1), dP(1), 128}}, 128, 64, 0, (bp)dv, 0, 1, 1));
+    // --- wy: dWh = dv2 St^T ; dAak = mask(dP v^T) ; dM = dv2 P^T + dWh Ah^T ; dAab = mask(M^T dM M^T)
+    TRY(run({{DV2(0), Hs(0), 128}}, 128, 128, pl.dW, nullptr, 0, 1, 1));
+    TRY(run({{dP(0), Vc(0), 128}}, 64, 128, pl.dAak, nullptr, 2, R, 1));
+    TRY(run({{DV2(0), Pp(0), 128}, {dW(0), Ah(0), 128}}, 128, 128, pl.dM, nullptr, 0, 1, 1));
+    TRY(run({{Mm(1), dM(1), 128}}, 128, 128, pl.tmp, nullptr, 0, 1, 1));
+    TRY(run({{Tmp(0), Mm(0), 128}}, 128, 128, pl.dAab, nullptr, 2, R, R));
+    // --- gradients of the hat operands (bwd_o :295-487 and the score-gradient applications of intra :761-827)
+    TRY(run({{dOc(0), Hs(0), 128}, {dAqk(0), Kh(1), 64}, {dAqb(0), Bh(1), 128}}, 128, 64, pl.dQh, nullptr, 0, 1, 1));
+    TRY(run({{Vc(0), DE(0), 128}, {dAqk(1), Qh(1), 64}, {dAak(1), Ah(1), 128}}, 128, 64, pl.dKh, nullptr, 0, 1, 1));
+    TRY(run({{V2(0), DE(0), 128}, {dAqb(1), Qh(1), 64}, {dAab(1), Ah(1), 128}}, 128, 128, pl.dBh, nullptr, 0, 1, 1));
+    TRY(run({{Mm(1), dW(1), 128}, {dAak(0), Kh(1), 64}, {dAab(0), Bh(1), 128}}, 128, 128, pl.dAh, nullptr, 0, 1, 1));
+    // --- assembly
+    FinalP fp{U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.dQh), U4(pl.dKh), U4(pl.dAh), U4(pl.dBh), F(pl.ghat),
+              F(pl.dgl), (bp)dq, (bp)dk, (bp)da, (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype};
+    bwd_final_kernel<<<G, 128, 0, st>>>(fp);
+    HDLA_CHECK_LAUNCH("bwd_final_kernel");
     return HDLA_OK;
 }
 
@@ -737,7 +1070,12 @@ int tc_debug_buffer(const HdlaDims& d, const unsigned char* ws, const char* name
                        {"Vc", pl.Vc, 64, 128}, {"Aqk", pl.Aqk, 64, 64}, {"Aqb", pl.Aqb, 64, 128},
                        {"Aak", pl.Aak, 128, 64}, {"Aab", pl.Aab, 128, 128}, {"M", pl.M, 128, 128},
                        {"W", pl.W, 128, 128}, {"P", pl.P, 128, 128}, {"U", pl.U, 128, 128}, {"Hs", pl.Hs, 128, 128},
-                       {"V2", pl.V2, 128, 128}};
+                       {"V2", pl.V2, 128, 128},
+                       {"dOc", pl.dOc, 64, 128}, {"dAqk", pl.dAqk, 64, 64}, {"dAqb", pl.dAqb, 64, 128},
+                       {"DV2", pl.DV2, 128, 128}, {"DE", pl.DE, 128, 128}, {"dW", pl.dW, 128, 128},
+                       {"dP", pl.dP, 128, 128}, {"dAak", pl.dAak, 128, 64}, {"dM", pl.dM, 128, 128},
+                       {"tmp", pl.tmp, 128, 128}, {"dAab", pl.dAab, 128, 128}, {"dQh", pl.dQh, 64, 128},
+                       {"dKh", pl.dKh, 64, 128}, {"dAh", pl.dAh, 128, 128}, {"dBh", pl.dBh, 128, 128}};
     for (const Ent& e : tab)
         if (!strcmp(e.n, name)) {
             c8_to_rowmajor_kernel<<<(unsigned)pl.G, 128, 0, st>>>(reinterpret_cast<const uint4*>(ws + e.off), out,
@@ -747,6 +1085,10 @@ int tc_debug_buffer(const HdlaDims& d, const unsigned char* ws, const char* name
         }
     if (!strcmp(name, "E")) {
         cudaMemcpyAsync(out, ws + pl.E, (size_t)pl.G * K * 4, cudaMemcpyDeviceToDevice, st);
+        return HDLA_OK;
+    }
+    if (!strcmp(name, "dgl")) {
+        cudaMemcpyAsync(out, ws + pl.dgl, (size_t)pl.G * K * 4, cudaMemcpyDeviceToDevice, st);
         return HDLA_OK;
     }
     if (!strcmp(name, "status")) {

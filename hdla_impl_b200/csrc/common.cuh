@@ -59,6 +59,9 @@ size_t tc_workspace_bytes(const HdlaDims& d, int with_backward);
 int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a, const void* b,
                  const void* gk, float scale, const float* h0, void* o, float* ht, unsigned char* ws, bool need_o,
                  cudaStream_t st);
+int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a, const void* b,
+                 const void* gk, float scale, const float* h0, const void* d_o, const float* dht, void* dq, void* dk,
+                 void* dv, void* da, void* db, void* dgk, float* dh0, unsigned char* ws, cudaStream_t st);
 int tc_debug_buffer(const HdlaDims& d, const unsigned char* ws, const char* name, float* out, cudaStream_t st);
 
 }  // namespace hdla
