@@ -213,12 +213,12 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    for _ in range(max(args.warmup, 3)):
-        step(leaves, dev_in["do"])
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        step(leaves, dev_in["do"])
+    barrier()
     l0 = _lib.kernel_launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -229,6 +229,13 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     launches = _lib.kernel_launches() - l0
     ms = e0.elapsed_time(e1)
+    if rank == 0:
+        # the timed region can be shorter than nvidia-smi's sampling period: keep the same load running
+        # (untimed) until a few samples exist, so the clocks reported are clocks under this load
+        t_end = time.time() + 5.0
+        while len(sampler.rows) < 5 and time.time() < t_end:
+            step(leaves, dev_in["do"])
+            torch.cuda.synchronize(dev)
     clocks = sampler.stop() if rank == 0 else None
 
     # end to end: pinned host buffers in, host buffers out

@@ -89,59 +89,92 @@ struct PrepP {
 
 __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
     __shared__ float gis[C][K + 4];
-    __shared__ float halfs[K];
+    __shared__ float tot[4][K];
     const long long g = blockIdx.x;
     const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
     const int b = bh / p.H, h = bh % p.H;
     const int t0 = n * C;
     const int valid = min(C, p.T - t0);
-    const int tid = threadIdx.x;
-    {
-        float run = 0.f;
-        for (int i = 0; i < C; ++i) {
-            float gv = 0.f;
-            if (i < valid) gv = ld_elem(p.gk, (((size_t)b * p.T + t0 + i) * p.H + h) * K + tid, p.gdt);
-            run += gv;
-            gis[i][tid] = run;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    {   // two-level cumulative sum: warp w owns rows [16w, 16w+16), lane owns 4 columns
+        float4 x[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int r = warp * 16 + i;
+            x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < valid) {
+                const size_t src = (((size_t)b * p.T + t0 + r) * p.H + h) * K + lane * 4;
+                if (p.gdt == HDLA_F32) {
+                    x[i] = *reinterpret_cast<const float4*>(static_cast<const float*>(p.gk) + src);
+                } else {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.gk) + src);
+                    x[i] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                                       __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+                }
+            }
         }
-        halfs[tid] = 0.5f * run;
-        p.E[(size_t)g * K + tid] = __expf(0.5f * run);
+        float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            run.x += x[i].x; run.y += x[i].y; run.z += x[i].z; run.w += x[i].w;
+            x[i] = run;
+        }
+        *reinterpret_cast<float4*>(&tot[warp][lane * 4]) = run;
+        __syncthreads();
+        float4 off = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int w = 0; w < warp; ++w) {
+            const float4 t = *reinterpret_cast<const float4*>(&tot[w][lane * 4]);
+            off.x += t.x; off.y += t.y; off.z += t.z; off.w += t.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            *reinterpret_cast<float4*>(&gis[warp * 16 + i][lane * 4]) =
+                make_float4(x[i].x + off.x, x[i].y + off.y, x[i].z + off.z, x[i].w + off.w);
     }
     __syncthreads();
-    const int r = tid & 63;
-    const bool rowok = r < valid;
+    if (tid < K) p.E[(size_t)g * K + tid] = __expf(0.5f * gis[C - 1][tid]);
+    // hat operands: per instruction a warp covers 8 rows x 4 column groups, so every global access
+    // is a run of full 32-byte sectors (64 B per row in, 128 B per column group out)
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    for (int s = 0; s < 8; ++s) {
-        const int kc = (tid >> 6) * 8 + s;
+    for (int it = 0; it < 8; ++it) {
+        const int blk = warp * 8 + it;                 // 32 blocks of (8 rows x 4 column groups)
+        const int r = (blk >> 2) * 8 + (lane & 7);
+        const int kc = (blk & 3) * 4 + (lane >> 3);
+        const bool rowok = r < valid;
         float gi[8], ge[8], hf[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             gi[j] = gis[r][kc * 8 + j];
             ge[j] = r > 0 ? gis[r - 1][kc * 8 + j] : 0.f;
-            hf[j] = halfs[kc * 8 + j];
+            hf[j] = 0.5f * gis[C - 1][kc * 8 + j];
         }
         const size_t src = (((size_t)b * p.T + t0 + r) * p.H + h) * K + kc * 8;
-        float x[8], y[8];
+        float x[8], y[8], ep[8], em[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { ep[j] = __expf(gi[j] - hf[j]); em[j] = __expf(hf[j] - gi[j]); }
         t8::unpack8(rowok ? *reinterpret_cast<const uint4*>(p.q + src) : zero, x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = x[j] * p.scale * __expf(gi[j] - hf[j]);
+        for (int j = 0; j < 8; ++j) y[j] = x[j] * p.scale * ep[j];
         p.Qh[(size_t)g * CH64 + kc * 64 + r] = t8::pack8(y);
         t8::unpack8(rowok ? *reinterpret_cast<const uint4*>(p.k + src) : zero, x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = x[j] * __expf(hf[j] - gi[j]);
+        for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
         p.Kh[(size_t)g * CH64 + kc * 64 + r] = t8::pack8(y);
         p.Vc[(size_t)g * CH64 + kc * 64 + r] =
             rowok ? *reinterpret_cast<const uint4*>(p.v + (((size_t)b * p.T + t0 + r) * p.H + h) * V + kc * 8) : zero;
+        float ea[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ea[j] = __expf(ge[j] - hf[j]);
 #pragma unroll
         for (int rr = 0; rr < R; ++rr) {
             const size_t sa = (((size_t)b * p.T * R + (size_t)(t0 + r) * R + rr) * p.H + h) * K + kc * 8;
             t8::unpack8(rowok ? *reinterpret_cast<const uint4*>(p.a + sa) : zero, x);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) y[j] = x[j] * __expf(ge[j] - hf[j]);
+            for (int j = 0; j < 8; ++j) y[j] = x[j] * ea[j];
             p.Ah[(size_t)g * CH128 + kc * 128 + r * R + rr] = t8::pack8(y);
             t8::unpack8(rowok ? *reinterpret_cast<const uint4*>(p.b + sa) : zero, x);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) y[j] = x[j] * __expf(hf[j] - gi[j]);
+            for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
             p.Bh[(size_t)g * CH128 + kc * 128 + r * R + rr] = t8::pack8(y);
         }
         float4* gh = reinterpret_cast<float4*>(p.ghat + (size_t)g * C * K + (size_t)r * K + kc * 8);
