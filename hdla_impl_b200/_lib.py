@@ -18,7 +18,7 @@ FLAG_FORCE_SIMT = 2
 
 EXPORTS = (
     "hdla_version", "hdla_last_error", "hdla_chunk_workspace_bytes", "hdla_chunk_fwd", "hdla_chunk_bwd",
-    "hdla_recurrent_fwd", "hdla_kernel_launches", "hdla_debug_tc_buffer",
+    "hdla_recurrent_fwd", "hdla_kernel_launches", "hdla_debug_tc_buffer", "hdla_chunk_fwd_noalloc",
 )
 
 
@@ -61,6 +61,8 @@ def load() -> C.CDLL:
         lib.hdla_chunk_workspace_bytes.argtypes = [dp, C.c_int]
         lib.hdla_chunk_fwd.restype = C.c_int
         lib.hdla_chunk_fwd.argtypes = [dp, vp, vp, vp, vp, vp, vp, C.c_float, f32p, vp, f32p, vp, C.c_size_t, vp]
+        lib.hdla_chunk_fwd_noalloc.restype = C.c_int
+        lib.hdla_chunk_fwd_noalloc.argtypes = [dp, vp, vp, vp, vp, vp, vp, C.c_float, f32p, vp, f32p, vp]
         lib.hdla_chunk_bwd.restype = C.c_int
         lib.hdla_chunk_bwd.argtypes = [dp, vp, vp, vp, vp, vp, vp, C.c_float, f32p, vp, f32p,
                                        vp, vp, vp, vp, vp, vp, f32p, vp, C.c_size_t, vp]

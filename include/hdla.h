@@ -104,6 +104,26 @@ HDLA_API int hdla_chunk_fwd(const HdlaDims* dims,
                    void* o, float* ht,
                    void* workspace, size_t workspace_bytes, void* cuda_stream);
 
+/* Chunked forward without a caller workspace: same computation and arguments as hdla_chunk_fwd,
+ * but the scratch memory is a fixed array of HDLA_NOALLOC_SCRATCH_BYTES built into the library
+ * (resident on every GPU that loads the library, until the process exits).  It exists for callers
+ * that cannot allocate device memory when they need the operator -- plugins of a server that owns
+ * the device memory, serving loops with a no-allocation policy, code running where cudaMalloc is
+ * not allowed -- and performs no allocation of any kind.  It has no counterpart in the reference,
+ * whose wrappers allocate their intermediates with torch.empty.
+ *   - Problems whose workspace (hdla_chunk_workspace_bytes(dims, 0)) exceeds the built-in scratch are
+ *     rejected with HDLA_ERR_WORKSPACE and an explanatory hdla_last_error().
+ *   - The first call on each device resolves the array's device address; make that first call with
+ *     the device current and before starting any stream capture.
+ *   - All calls on a device share the one array, which keeps the previous call's contents: calls whose
+ *     GPU work can overlap (different streams, different threads) race with each other.  Issue them
+ *     on one stream, or order them yourself. */
+#define HDLA_NOALLOC_SCRATCH_BYTES (64u << 20)
+HDLA_API int hdla_chunk_fwd_noalloc(const HdlaDims* dims,
+                   const void* q, const void* k, const void* v, const void* a, const void* b,
+                   const void* gk, float scale, const float* h0,
+                   void* o, float* ht, void* cuda_stream);
+
 /* Chunked backward.  Replaces ChunkDPLRDeltaRuleFunction.backward (HRDPLR/hrdplr.py:146-284):
  * stages dAu, dhu (reverse state scan), dv, bwd_o, wy, intra and dgk.
  *   d_o  : [B,T,H,V] gradient of o (dims->dtype);  dht: [B,H,K,V] fp32 gradient of the final
