@@ -769,6 +769,165 @@ __global__ void __launch_bounds__(128) chain_tc_kernel(ChainP p) {
     if (warp == 0) tmem_dealloc(tmem, 128);
 }
 
+// ------------------------------------------------------------------------------------------
+// backward through the WY representation, one kernel per chunk   (HRDPLR/bwd_triton.py:489-612)
+//   dWh = dv2 St^T ; dP = M^T dv2 ; dAak = smask(dP v^T) ; dM = dv2 P^T + dWh Ah^T ;
+//   dAab = smask(M^T dM M^T)
+// Six operand tiles are loaded once (176 KB); dWh, dP, dM and M^T dM are produced as bf16 operand
+// tiles in shared memory (over buffers whose contents are no longer needed) and feed the next
+// product directly, so only dWh, dP, dAak and dAab go back to HBM.
+// ------------------------------------------------------------------------------------------
+struct WyBwdP {
+    const uint4 *M, *DV2, *Hs, *Vc, *P, *Ah;
+    uint4 *dW, *dP, *dAak, *dAab;
+    int* status;
+};
+
+// 64 accumulator columns of this thread's row -> registers (two 32-column loads, one wait)
+__device__ __forceinline__ void tmem_row64(uint32_t addr, float* f) {
+    uint32_t a[32], b[32];
+    tmem_ld_x32(addr, a);
+    tmem_ld_x32(addr + 32, b);
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { f[j] = __uint_as_float(a[j]); f[32 + j] = __uint_as_float(b[j]); }
+}
+
+__global__ void __launch_bounds__(128) wy_bwd_tc_kernel(WyBwdP p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint4* bM = reinterpret_cast<uint4*>(smem);      // M
+    uint4* bDV2 = bM + CH128;                        // dv2, later dM
+    uint4* bHs = bDV2 + CH128;                       // St, later dWh
+    uint4* bP = bHs + CH128;                         // P, later M^T dM
+    uint4* bAh = bP + CH128;                         // Ah
+    uint4* bdP = bAh + CH128;                        // dP
+    uint4* bVc = bdP + CH128;                        // v  [64 x 128]
+    __shared__ __align__(8) uint64_t ld1, ld2, mma_bar;
+    __shared__ uint32_t tmem_s;
+    const long long g = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    if (warp == 0) { tmem_alloc(&tmem_s, 256); tmem_relinquish(); }
+    if (tid == 0) {
+        mbar_init(&ld1, 1); mbar_init(&ld2, 1); mbar_init(&mma_bar, 1); fence_mbar_init();
+        mbar_expect_tx(&ld1, 98304);
+        bulk_g2s(bDV2, p.DV2 + g * CH128, 32768, &ld1);
+        bulk_g2s(bHs, p.Hs + g * CH128, 32768, &ld1);
+        bulk_g2s(bM, p.M + g * CH128, 32768, &ld1);
+        mbar_expect_tx(&ld2, 81920);
+        bulk_g2s(bVc, p.Vc + g * CH64, 16384, &ld2);
+        bulk_g2s(bP, p.P + g * CH128, 32768, &ld2);
+        bulk_g2s(bAh, p.Ah + g * CH128, 32768, &ld2);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_s;
+    const Tile tM = t8::tile(bM, 128), tDV2 = t8::tile(bDV2, 128), tHs = t8::tile(bHs, 128), tP = t8::tile(bP, 128),
+               tAh = t8::tile(bAh, 128), tdP = t8::tile(bdP, 128), tVc = t8::tile(bVc, 64);
+    const int r = tid;
+    float f[64];
+    // ---- phase 1: dWh = dv2 St^T (cols 0..127), dP = M^T dv2 (cols 128..255)
+    wait_or_flag(&ld1, 0, p.status, 30);
+    if (tid == 0) {
+        t8::mma_chain<false, false>(tmem, tDV2, 0, 0, tHs, 0, 0, 128, 128, false);
+        t8::mma_chain<true, true>(tmem + 128, tM, 0, 0, tDV2, 0, 0, 128, 128, false);
+        umma_commit(&mma_bar);
+    }
+    wait_or_flag(&mma_bar, 0, p.status, 31);
+    tc_fence_after();
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {
+        tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+            const uint4 c = t8::pack8(f + c8 * 8);
+            bHs[(hh * 8 + c8) * 128 + r] = c;                       // dWh replaces St
+            p.dW[g * CH128 + (hh * 8 + c8) * 128 + r] = c;
+        }
+        tmem_row64(t8::taddr(tmem, warp, 128 + hh * 64), f);
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+            const uint4 c = t8::pack8(f + c8 * 8);
+            bdP[(hh * 8 + c8) * 128 + r] = c;
+            p.dP[g * CH128 + (hh * 8 + c8) * 128 + r] = c;
+        }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    // ---- phase 2: dAak = dP v^T (cols 0..63), dM = dv2 P^T + dWh Ah^T (cols 128..255)
+    wait_or_flag(&ld2, 0, p.status, 32);
+    if (tid == 0) {
+        tc_fence_after();
+        t8::mma_chain<false, false>(tmem, tdP, 0, 0, tVc, 0, 0, 64, 128, false);
+        t8::mma_chain<false, false>(tmem + 128, tDV2, 0, 0, tP, 0, 0, 128, 128, false);
+        t8::mma_chain<false, false>(tmem + 128, tHs, 0, 0, tAh, 0, 0, 128, 128, true);
+        umma_commit(&mma_bar);
+    }
+    wait_or_flag(&mma_bar, 1, p.status, 33);
+    tc_fence_after();
+    {
+        const int i = r >> 1;
+        tmem_row64(t8::taddr(tmem, warp, 0), f);
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) if (!((c8 * 8 + j) < i)) f[c8 * 8 + j] = 0.f;
+            p.dAak[g * CH64 + c8 * 128 + r] = t8::pack8(f + c8 * 8);
+        }
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+            tmem_row64(t8::taddr(tmem, warp, 128 + hh * 64), f);
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) bDV2[(hh * 8 + c8) * 128 + r] = t8::pack8(f + c8 * 8);   // dM replaces dv2
+        }
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    // ---- phase 3: tmp = M^T dM
+    if (tid == 0) {
+        tc_fence_after();
+        t8::mma_chain<true, true>(tmem, tM, 0, 0, tDV2, 0, 0, 128, 128, false);
+        umma_commit(&mma_bar);
+    }
+    wait_or_flag(&mma_bar, 0, p.status, 34);
+    tc_fence_after();
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {
+        tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) bP[(hh * 8 + c8) * 128 + r] = t8::pack8(f + c8 * 8);         // tmp replaces P
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    // ---- phase 4: dAab = smask(tmp M^T)
+    if (tid == 0) {
+        tc_fence_after();
+        t8::mma_chain<false, false>(tmem + 128, tP, 0, 0, tM, 0, 0, 128, 128, false);
+        umma_commit(&mma_bar);
+    }
+    wait_or_flag(&mma_bar, 1, p.status, 35);
+    tc_fence_after();
+    {
+        const int i = r >> 1;
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+            tmem_row64(t8::taddr(tmem, warp, 128 + hh * 64), f);
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) if (!(((hh * 64 + c8 * 8 + j) >> 1) < i)) f[c8 * 8 + j] = 0.f;
+                p.dAab[g * CH128 + (hh * 8 + c8) * 128 + r] = t8::pack8(f + c8 * 8);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
 // dO rows of the public [B,T,H,V] tensor -> C8 tile [64 x 128] per chunk
 __global__ void __launch_bounds__(128) rows_to_c8_kernel(const __nv_bfloat16* src, uint4* dst, int T, int H, int NT) {
     const long long g = blockIdx.x;
@@ -925,6 +1084,7 @@ __global__ void c8_to_rowmajor_kernel(const uint4* src, float* dst, int rows, in
     }
 }
 
+constexpr int kWySmem = 6 * 32768 + 16384;
 constexpr int kChainSmemMax = 6 * 32768 + 32768;   // six tiles plus slack for 64-row A operands read as 128 rows
 
 template <typename Kern>
@@ -962,6 +1122,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         TRY(set_smem(scan_tc_kernel, 196608));
         TRY(set_smem(out_tc_kernel, 122880));
         TRY(set_smem(chain_tc_kernel, kChainSmemMax));
+        TRY(set_smem(wy_bwd_tc_kernel, kWySmem));
         attr_dev = dev;
     }
     auto U4 = [&](size_t off) { return reinterpret_cast<uint4*>(ws + off); };
@@ -1073,15 +1234,13 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
                U4(pl.Hs), F(pl.HT), F(pl.dgl), pl.NT, 1, status};
     scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
     HDLA_CHECK_LAUNCH("scan_tc_kernel");
-    // --- dv = Kh dSt + Aqk^T dO + Aak^T dP with dP = M^T dv2   (bwd_triton.py:227-290 and wy :489-612)
-    TRY(run({{Mm(1), DV2(1), 128}}, 128, 128, pl.dP, nullptr, 0, 1, 1));
+    // --- wy: dWh, dP, dAak, dAab in one kernel
+    WyBwdP wyp{U4(pl.M), U4(pl.DV2), U4(pl.Hs), U4(pl.Vc), U4(pl.P), U4(pl.Ah), U4(pl.dW), U4(pl.dP), U4(pl.dAak),
+               U4(pl.dAab), status};
+    wy_bwd_tc_kernel<<<G, 128, kWySmem, st>>>(wyp);
+    HDLA_CHECK_LAUNCH("wy_bwd_tc_kernel");
+    // --- dv = Kh dSt + Aqk^T dO + Aak^T dP   (bwd_triton.py:227-290 and the dv part of wy)
     TRY(run({{Kh(0), DE(1), 128}, {Aqk(1), dOc(1), 64}, {Aak(1), dP(1), 128}}, 128, 64, 0, (bp)dv, 0, 1, 1));
-    // --- wy: dWh = dv2 St^T ; dAak = mask(dP v^T) ; dM = dv2 P^T + dWh Ah^T ; dAab = mask(M^T dM M^T)
-    TRY(run({{DV2(0), Hs(0), 128}}, 128, 128, pl.dW, nullptr, 0, 1, 1));
-    TRY(run({{dP(0), Vc(0), 128}}, 64, 128, pl.dAak, nullptr, 2, R, 1));
-    TRY(run({{DV2(0), Pp(0), 128}, {dW(0), Ah(0), 128}}, 128, 128, pl.dM, nullptr, 0, 1, 1));
-    TRY(run({{Mm(1), dM(1), 128}}, 128, 128, pl.tmp, nullptr, 0, 1, 1));
-    TRY(run({{Tmp(0), Mm(0), 128}}, 128, 128, pl.dAab, nullptr, 2, R, R));
     // --- gradients of the hat operands (bwd_o :295-487 and the score-gradient applications of intra :761-827)
     TRY(run({{dOc(0), Hs(0), 128}, {dAqk(0), Kh(1), 64}, {dAqb(0), Bh(1), 128}}, 128, 64, pl.dQh, nullptr, 0, 1, 1));
     TRY(run({{Vc(0), DE(0), 128}, {dAqk(1), Qh(1), 64}, {dAak(1), Ah(1), 128}}, 128, 64, pl.dKh, nullptr, 0, 1, 1));
