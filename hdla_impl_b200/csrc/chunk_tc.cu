@@ -1084,6 +1084,200 @@ __global__ void c8_to_rowmajor_kernel(const uint4* src, float* dst, int rows, in
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// backward, last stage: gradients of the hat operands, dv, un-gating and dgk in one kernel
+//   (HRDPLR/bwd_triton.py: dv 227-290, bwd_o 295-487, score-gradient applications of intra 761-827,
+//    un-gating 854-880, dgk 885-947)
+// Five products, all evaluated transposed so that the accumulator lane is the channel k (or v):
+//   P1 dQh^T = St dO^T   + Kh^T dAqk^T + Bh^T dAqb^T        [k x 64 tokens]
+//   P2 dv^T  = dSt^T Kh^T + dO^T Aqk   + dP^T Aak           [v x 64 tokens]
+//   P3 dAh^T = dWh^T M   + Kh^T dAak^T + Bh^T dAab^T        [k x 128 rows]
+//   P4 dBh^T = dSt V2^T  + Qh^T dAqb   + Ah^T dAab          [k x 128 rows]
+//   P5 dKh^T = dSt v^T   + Qh^T dAqk   + Ah^T dAak          [k x 64 tokens]
+// They read 18 distinct tiles (416 KB) -- more than shared memory holds -- so the tiles go through
+// a fixed slot schedule: five 32 KB slots A..E, three 16 KB slots a..c, two 8 KB slots x, y; a tile
+// is loaded (bulk copy) as soon as the product that last read its slot has completed:
+//   L1: St->A Bh->B dO->a Kh->b dAqb->c dAqk->x      L2: dSt->C dP->D Aak->E Aqk->y
+//   P1 after L1, P2 after L2
+//   L3: dWh->A (after P1)  M->D dAab->E dAak->a (after P2);   P3 after L3
+//   L4: V2->A Ah->B Qh->D.lo v->D.hi (after P3);              P4, P5 after L4
+//   L5: Bh->A, ghat->C (after P4)
+// All five accumulators stay in TMEM (448 columns) until the end; then thread k walks the 64 tokens
+// backwards, un-gates (dq = scale e^{gi-half} dQh, ...), forms the running sum for dgk in registers
+// and writes every gradient in the public layout (a warp writes 32 adjacent channels of one token).
+// ------------------------------------------------------------------------------------------
+struct GradP {
+    const uint4 *Hs, *Bh, *dOc, *Kh, *dAqb, *dAqk, *DE, *dP, *Aak, *Aqk, *dW, *M, *dAab, *dAak, *V2, *Ah, *Qh, *Vc;
+    const float *ghat, *dgl;
+    __nv_bfloat16 *dq, *dk, *dv, *da, *db;
+    void* dgk;
+    float scale;
+    int T, H, NT, gdt;
+    int* status;
+};
+
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ void chain0(uint32_t tm, Tile A, Tile B, int N, int kdim, bool acc) {
+    t8::mma_chain<A_MN, B_MN>(tm, A, 0, 0, B, 0, 0, N, kdim, acc);
+}
+
+__device__ __forceinline__ float c8s(const uint4* tile, int rows, int r, int c) {      // element of a C8 tile in smem
+    const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(tile + (c >> 3) * rows + r);
+    return __bfloat162float(q[c & 7]);
+}
+
+__global__ void __launch_bounds__(128) grad_tc_kernel(GradP p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint4* sA = reinterpret_cast<uint4*>(smem);          // 32 KB slots
+    uint4* sB = sA + CH128;
+    uint4* sC = sB + CH128;
+    uint4* sD = sC + CH128;
+    uint4* sE = sD + CH128;
+    uint4* sa = sE + CH128;                              // 16 KB slots
+    uint4* sb = sa + CH64;
+    uint4* sc = sb + CH64;
+    uint4* sx = sc + CH64;                               // 8 KB slots
+    uint4* sy = sx + 512;
+    __shared__ __align__(8) uint64_t L1, L2, L3, L4, L5, m1, m2, m3, m4;
+    __shared__ uint32_t tmem_s;
+    const long long g = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    if (warp == 0) { tmem_alloc(&tmem_s, 512); tmem_relinquish(); }
+    if (tid == 0) {
+        mbar_init(&L1, 1); mbar_init(&L2, 1); mbar_init(&L3, 1); mbar_init(&L4, 1); mbar_init(&L5, 1);
+        mbar_init(&m1, 1); mbar_init(&m2, 1); mbar_init(&m3, 1); mbar_init(&m4, 1);
+        fence_mbar_init();
+        mbar_expect_tx(&L1, 32768 + 32768 + 16384 + 16384 + 16384 + 8192);
+        bulk_g2s(sA, p.Hs + g * CH128, 32768, &L1);
+        bulk_g2s(sB, p.Bh + g * CH128, 32768, &L1);
+        bulk_g2s(sa, p.dOc + g * CH64, 16384, &L1);
+        bulk_g2s(sb, p.Kh + g * CH64, 16384, &L1);
+        bulk_g2s(sc, p.dAqb + g * CH64, 16384, &L1);
+        bulk_g2s(sx, p.dAqk + g * 512, 8192, &L1);
+        mbar_expect_tx(&L2, 32768 + 32768 + 16384 + 8192);
+        bulk_g2s(sC, p.DE + g * CH128, 32768, &L2);
+        bulk_g2s(sD, p.dP + g * CH128, 32768, &L2);
+        bulk_g2s(sE, p.Aak + g * CH64, 16384, &L2);
+        bulk_g2s(sy, p.Aqk + g * 512, 8192, &L2);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_s;
+    // TMEM columns: dQh^T 0..63, dv^T 64..127, dAh^T 128..255, dBh^T 256..383, dKh^T 384..447
+    if (tid == 0) {
+        wait_or_flag(&L1, 0, p.status, 40);
+        chain0<false, false>(tmem, t8::tile(sA, 128), t8::tile(sa, 64), 64, 128, false);          // St dO^T
+        chain0<true, false>(tmem, t8::tile(sb, 64), t8::tile(sx, 64), 64, 64, true);              // Kh^T dAqk^T
+        chain0<true, false>(tmem, t8::tile(sB, 128), t8::tile(sc, 64), 64, 128, true);            // Bh^T dAqb^T
+        umma_commit(&m1);
+        wait_or_flag(&L2, 0, p.status, 41);
+        chain0<true, false>(tmem + 64, t8::tile(sC, 128), t8::tile(sb, 64), 64, 128, false);      // dSt^T Kh^T
+        chain0<true, true>(tmem + 64, t8::tile(sa, 64), t8::tile(sy, 64), 64, 64, true);          // dO^T Aqk
+        chain0<true, true>(tmem + 64, t8::tile(sD, 128), t8::tile(sE, 128), 64, 128, true);       // dP^T Aak
+        umma_commit(&m2);
+        wait_or_flag(&m1, 0, p.status, 42);
+        wait_or_flag(&m2, 0, p.status, 43);
+        mbar_expect_tx(&L3, 32768 + 32768 + 32768 + 16384);
+        bulk_g2s(sA, p.dW + g * CH128, 32768, &L3);
+        bulk_g2s(sD, p.M + g * CH128, 32768, &L3);
+        bulk_g2s(sE, p.dAab + g * CH128, 32768, &L3);
+        bulk_g2s(sa, p.dAak + g * CH64, 16384, &L3);
+        wait_or_flag(&L3, 0, p.status, 44);
+        chain0<true, true>(tmem + 128, t8::tile(sA, 128), t8::tile(sD, 128), 128, 128, false);    // dWh^T M
+        chain0<true, false>(tmem + 128, t8::tile(sb, 64), t8::tile(sa, 128), 128, 64, true);      // Kh^T dAak^T
+        chain0<true, false>(tmem + 128, t8::tile(sB, 128), t8::tile(sE, 128), 128, 128, true);    // Bh^T dAab^T
+        umma_commit(&m3);
+        wait_or_flag(&m3, 0, p.status, 45);
+        mbar_expect_tx(&L4, 32768 + 32768 + 16384 + 16384);
+        bulk_g2s(sA, p.V2 + g * CH128, 32768, &L4);
+        bulk_g2s(sB, p.Ah + g * CH128, 32768, &L4);
+        bulk_g2s(sD, p.Qh + g * CH64, 16384, &L4);
+        bulk_g2s(sD + CH64, p.Vc + g * CH64, 16384, &L4);
+        wait_or_flag(&L4, 0, p.status, 46);
+        chain0<false, false>(tmem + 256, t8::tile(sC, 128), t8::tile(sA, 128), 128, 128, false);  // dSt V2^T
+        chain0<true, true>(tmem + 256, t8::tile(sD, 64), t8::tile(sc, 64), 128, 64, true);        // Qh^T dAqb
+        chain0<true, true>(tmem + 256, t8::tile(sB, 128), t8::tile(sE, 128), 128, 128, true);     // Ah^T dAab
+        chain0<false, false>(tmem + 384, t8::tile(sC, 128), t8::tile(sD + CH64, 64), 64, 128, false);  // dSt v^T
+        chain0<true, true>(tmem + 384, t8::tile(sD, 64), t8::tile(sx, 64), 64, 64, true);         // Qh^T dAqk
+        chain0<true, true>(tmem + 384, t8::tile(sB, 128), t8::tile(sa, 128), 64, 128, true);      // Ah^T dAak
+        umma_commit(&m4);
+        wait_or_flag(&m4, 0, p.status, 47);
+        mbar_expect_tx(&L5, 65536);
+        bulk_g2s(sA, p.Bh + g * CH128, 32768, &L5);
+        bulk_g2s(sC, p.ghat + (size_t)g * C * K, 32768, &L5);      // fp32 [64][128] over the dSt slot
+    }
+    wait_or_flag(&m4, 0, p.status, 48);
+    wait_or_flag(&L5, 0, p.status, 49);
+    tc_fence_after();
+    {
+        const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
+        const int b = bh / p.H, h = bh % p.H;
+        const int k = tid;
+        const float* gh = reinterpret_cast<const float*>(sC);
+        const float half = gh[(size_t)(C - 1) * K + k];
+        const float dgl = p.dgl[(size_t)g * K + k];
+        const uint4 *tQh = sD, *tKh = sb, *tAh = sB, *tBh = sA;
+        float run = 0.f;
+        float x = half;                                   // ghat of token 63 is g_last - half = half
+#pragma unroll 1
+        for (int ib = 7; ib >= 0; --ib) {
+            uint32_t vq[8], vk[8], va[16], vb[16];
+            tmem_ld_x8(t8::taddr(tmem, warp, ib * 8), vq);
+            tmem_ld_x8(t8::taddr(tmem, warp, 384 + ib * 8), vk);
+            tmem_ld_x16(t8::taddr(tmem, warp, 128 + ib * 16), va);
+            tmem_ld_x16(t8::taddr(tmem, warp, 256 + ib * 16), vb);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 7; j >= 0; --j) {
+                const int i = ib * 8 + j;
+                const int t = n * C + i;
+                const bool ok = t < p.T;
+                const float xe = i > 0 ? gh[(size_t)(i - 1) * K + k] : -half;      // ge - half
+                const float ep = __expf(x), em = __expf(-x), ee = __expf(xe);
+                const float dqh = __uint_as_float(vq[j]), dkh = __uint_as_float(vk[j]);
+                float d_gi = c8s(tQh, 64, i, k) * dqh - c8s(tKh, 64, i, k) * dkh;
+                float d_ge = 0.f;
+#pragma unroll
+                for (int rr = 0; rr < R; ++rr) {
+                    const float dah = __uint_as_float(va[2 * j + rr]), dbh = __uint_as_float(vb[2 * j + rr]);
+                    d_ge = fmaf(c8s(tAh, 128, i * R + rr, k), dah, d_ge);
+                    d_gi = fmaf(-c8s(tBh, 128, i * R + rr, k), dbh, d_gi);
+                    if (ok) {
+                        const size_t oa = (((size_t)b * p.T * R + (size_t)t * R + rr) * p.H + h) * K + k;
+                        p.da[oa] = __float2bfloat16_rn(ee * dah);
+                        p.db[oa] = __float2bfloat16_rn(em * dbh);
+                    }
+                }
+                run += d_gi + d_ge;
+                if (ok) {
+                    const size_t o = (((size_t)b * p.T + t) * p.H + h) * K + k;
+                    p.dq[o] = __float2bfloat16_rn(p.scale * ep * dqh);
+                    p.dk[o] = __float2bfloat16_rn(em * dkh);
+                    st_elem(p.dgk, o, p.gdt, run - d_ge + dgl);
+                }
+                x = xe;                                   // ghat of token i-1
+            }
+        }
+        // dv: accumulator lane = value channel
+#pragma unroll 1
+        for (int cb = 0; cb < 2; ++cb) {
+            uint32_t v[32];
+            tmem_ld_x32(t8::taddr(tmem, warp, 64 + cb * 32), v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int t = n * C + cb * 32 + j;
+                if (t < p.T) p.dv[(((size_t)b * p.T + t) * p.H + h) * V + tid] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+constexpr int kGradSmem = 5 * 32768 + 3 * 16384 + 2 * 8192;
 constexpr int kWySmem = 6 * 32768 + 16384;
 constexpr int kChainSmemMax = 6 * 32768 + 32768;   // six tiles plus slack for 64-row A operands read as 128 rows
 
@@ -1123,6 +1317,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         TRY(set_smem(out_tc_kernel, 122880));
         TRY(set_smem(chain_tc_kernel, kChainSmemMax));
         TRY(set_smem(wy_bwd_tc_kernel, kWySmem));
+        TRY(set_smem(grad_tc_kernel, kGradSmem));
         attr_dev = dev;
     }
     auto U4 = [&](size_t off) { return reinterpret_cast<uint4*>(ws + off); };
@@ -1239,18 +1434,13 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
                U4(pl.dAab), status};
     wy_bwd_tc_kernel<<<G, 128, kWySmem, st>>>(wyp);
     HDLA_CHECK_LAUNCH("wy_bwd_tc_kernel");
-    // --- dv = Kh dSt + Aqk^T dO + Aak^T dP   (bwd_triton.py:227-290 and the dv part of wy)
-    TRY(run({{Kh(0), DE(1), 128}, {Aqk(1), dOc(1), 64}, {Aak(1), dP(1), 128}}, 128, 64, 0, (bp)dv, 0, 1, 1));
-    // --- gradients of the hat operands (bwd_o :295-487 and the score-gradient applications of intra :761-827)
-    TRY(run({{dOc(0), Hs(0), 128}, {dAqk(0), Kh(1), 64}, {dAqb(0), Bh(1), 128}}, 128, 64, pl.dQh, nullptr, 0, 1, 1));
-    TRY(run({{Vc(0), DE(0), 128}, {dAqk(1), Qh(1), 64}, {dAak(1), Ah(1), 128}}, 128, 64, pl.dKh, nullptr, 0, 1, 1));
-    TRY(run({{V2(0), DE(0), 128}, {dAqb(1), Qh(1), 64}, {dAab(1), Ah(1), 128}}, 128, 128, pl.dBh, nullptr, 0, 1, 1));
-    TRY(run({{Mm(1), dW(1), 128}, {dAak(0), Kh(1), 64}, {dAab(0), Bh(1), 128}}, 128, 128, pl.dAh, nullptr, 0, 1, 1));
-    // --- assembly
-    FinalP fp{U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.dQh), U4(pl.dKh), U4(pl.dAh), U4(pl.dBh), F(pl.ghat),
-              F(pl.dgl), (bp)dq, (bp)dk, (bp)da, (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype};
-    bwd_final_kernel<<<G, 128, 0, st>>>(fp);
-    HDLA_CHECK_LAUNCH("bwd_final_kernel");
+    // --- everything else: hat-operand gradients, dv, un-gating, dgk
+    GradP gp{U4(pl.Hs), U4(pl.Bh), U4(pl.dOc), U4(pl.Kh), U4(pl.dAqb), U4(pl.dAqk), U4(pl.DE), U4(pl.dP), U4(pl.Aak),
+             U4(pl.Aqk), U4(pl.dW), U4(pl.M), U4(pl.dAab), U4(pl.dAak), U4(pl.V2), U4(pl.Ah), U4(pl.Qh), U4(pl.Vc),
+             F(pl.ghat), F(pl.dgl), (bp)dq, (bp)dk, (bp)dv, (bp)da, (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype,
+             status};
+    grad_tc_kernel<<<G, 128, kGradSmem, st>>>(gp);
+    HDLA_CHECK_LAUNCH("grad_tc_kernel");
     return HDLA_OK;
 }
 
