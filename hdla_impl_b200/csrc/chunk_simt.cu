@@ -11,10 +11,8 @@
 // mask), so no operand is ever scaled by exp(-g) and nothing can overflow however strong the
 // decay is.  All dense products go through one batched tile-GEMM routine.
 #include "common.cuh"
-#include "tc_gemm.cuh"
 
 namespace hdla {
-int tc_bgemm_launch(const TcGemmP& p, long long G, cudaStream_t st);
 namespace {
 
 // ------------------------------------------------------------------------------------------
@@ -638,7 +636,6 @@ struct Ctx {
     Plan pl;
     float* ws;
     cudaStream_t st;
-    bool use_tc;            // dense products on the tensor cores (bf16 operands) instead of fp32 CUDA cores
     float* at(long long off) const { return ws + off; }
     Mat mat(long long off, long long per_chunk, long long rs, long long cs) const {
         return Mat{ws + off, per_chunk * pl.NT, per_chunk, rs, cs};
@@ -650,15 +647,6 @@ struct Ctx {
 
 int gemm(const Ctx& c, Mat A, Mat B, long long Coff, long long c_per_chunk, long long rsC, long long csC, int M,
          int N, int L, float alpha = 1.f, int accumulate = 0, int mask = 0, int ri = 1, int rj = 1) {
-    if (c.use_tc) {
-        TcGemmP t{};
-        t.A = TcOperand{A.p, A.sbh, A.sn, A.rs, A.cs, HDLA_F32};
-        t.B = TcOperand{B.p, B.sbh, B.sn, B.rs, B.cs, HDLA_F32};
-        t.C = c.ws + Coff; t.cbh = c_per_chunk * c.pl.NT; t.cn = c_per_chunk; t.rsC = rsC; t.csC = csC;
-        t.cdt = HDLA_F32; t.M = M; t.N = N; t.L = L; t.NT = c.pl.NT; t.alpha = alpha; t.accumulate = accumulate;
-        t.mask = mask; t.ri = ri; t.rj = rj; t.col_scale = nullptr; t.row_scale = nullptr; t.status = nullptr;
-        return tc_bgemm_launch(t, c.pl.G, c.st);
-    }
     GemmP p{A, B, c.ws + Coff, c_per_chunk * c.pl.NT, c_per_chunk, rsC, csC, M, N, L, c.pl.NT,
             alpha, accumulate, mask, ri, rj};
     dim3 grid((unsigned)c.pl.G, (N + TN - 1) / TN, (M + TM - 1) / TM);
@@ -668,9 +656,6 @@ int gemm(const Ctx& c, Mat A, Mat B, long long Coff, long long c_per_chunk, long
 }
 
 #define TRY(x) do { int rc__ = (x); if (rc__ != HDLA_OK) return rc__; } while (0)
-
-// bf16 inputs take the tensor-core products unless the caller forces the fp32 pipeline
-bool use_tensor_cores(const HdlaDims& d) { return d.dtype == HDLA_BF16 && !(d.flags & HDLA_FLAG_FORCE_SIMT); }
 
 int check_dims(const HdlaDims& d, const Plan& pl) {
     if (pl.m > 128) return fail(HDLA_ERR_UNSUPPORTED, "chunk: R*chunk = %d exceeds 128", pl.m);
@@ -690,7 +675,7 @@ size_t simt_workspace_floats(const HdlaDims& d, int with_backward) {
 int simt_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a, const void* b,
                    const void* gk, float scale, const float* h0, void* o, float* ht, float* ws, bool need_o,
                    cudaStream_t st) {
-    Ctx c{make_plan(d), ws, st, use_tensor_cores(d)};
+    Ctx c{make_plan(d), ws, st};
     const Plan& pl = c.pl;
     TRY(check_dims(d, pl));
     const int C = pl.C, m = pl.m, K = pl.K, V = pl.V, R = pl.R;
@@ -764,7 +749,7 @@ int simt_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* 
                    void* dk, void* dv, void* da, void* db, void* dgk, float* dh0, float* ws, cudaStream_t st) {
     if (!(d.flags & HDLA_FLAG_WS_HOLDS_FWD))
         TRY(simt_chunk_fwd(d, q, k, v, a, b, gk, scale, h0, nullptr, nullptr, ws, false, st));
-    Ctx c{make_plan(d), ws, st, use_tensor_cores(d)};
+    Ctx c{make_plan(d), ws, st};
     const Plan& pl = c.pl;
     TRY(check_dims(d, pl));
     const int C = pl.C, m = pl.m, K = pl.K, V = pl.V, R = pl.R;

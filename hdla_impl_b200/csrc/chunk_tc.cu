@@ -14,7 +14,6 @@
 // All matrices between kernels are bf16 in the C8 blocked layout (tc_tiles.cuh) and move with
 // bulk asynchronous copies; all products run on tcgen05.mma with fp32 accumulation in TMEM.
 #include <cstring>
-#include <initializer_list>
 
 #include "tc_tiles.cuh"
 
@@ -24,7 +23,7 @@ namespace {
 using namespace sm100;
 using t8::Tile;
 
-constexpr int C = 64, K = 128, V = 128, R = 2, m = 128;
+constexpr int C = 64, K = 128, V = 128, R = 2;
 constexpr int CH64 = 16 * 64;      // chunks (16 B) of a [64 x 128] tile
 constexpr int CH128 = 16 * 128;    // chunks of a [128 x 128] tile
 
@@ -69,6 +68,12 @@ TcPlan make_tc_plan(const HdlaDims& d) {
 // bounded wait on an mbarrier; records a failure in the device status word and carries on
 __device__ __forceinline__ void wait_or_flag(uint64_t* bar, uint32_t parity, int* status, int code) {
     if (!mbar_wait(bar, parity)) {
+        if (status) atomicExch(status, code);
+    }
+}
+
+__device__ __forceinline__ void wait_idle_or_flag(uint64_t* bar, uint32_t parity, int* status, int code) {
+    if (!mbar_wait_backoff(bar, parity)) {
         if (status) atomicExch(status, code);
     }
 }
@@ -142,16 +147,25 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
         const int kc = (blk & 3) * 4 + (lane >> 3);
         const bool rowok = r < valid;
         float gi[8], ge[8], hf[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            gi[j] = gis[r][kc * 8 + j];
-            ge[j] = r > 0 ? gis[r - 1][kc * 8 + j] : 0.f;
-            hf[j] = 0.5f * gis[C - 1][kc * 8 + j];
+        {
+            const float4 g0 = *reinterpret_cast<const float4*>(&gis[r][kc * 8]);
+            const float4 g1 = *reinterpret_cast<const float4*>(&gis[r][kc * 8 + 4]);
+            const float4 l0 = *reinterpret_cast<const float4*>(&gis[C - 1][kc * 8]);
+            const float4 l1 = *reinterpret_cast<const float4*>(&gis[C - 1][kc * 8 + 4]);
+            float4 e0 = make_float4(0.f, 0.f, 0.f, 0.f), e1 = e0;
+            if (r > 0) {
+                e0 = *reinterpret_cast<const float4*>(&gis[r - 1][kc * 8]);
+                e1 = *reinterpret_cast<const float4*>(&gis[r - 1][kc * 8 + 4]);
+            }
+            gi[0] = g0.x; gi[1] = g0.y; gi[2] = g0.z; gi[3] = g0.w; gi[4] = g1.x; gi[5] = g1.y; gi[6] = g1.z; gi[7] = g1.w;
+            ge[0] = e0.x; ge[1] = e0.y; ge[2] = e0.z; ge[3] = e0.w; ge[4] = e1.x; ge[5] = e1.y; ge[6] = e1.z; ge[7] = e1.w;
+            hf[0] = .5f * l0.x; hf[1] = .5f * l0.y; hf[2] = .5f * l0.z; hf[3] = .5f * l0.w;
+            hf[4] = .5f * l1.x; hf[5] = .5f * l1.y; hf[6] = .5f * l1.z; hf[7] = .5f * l1.w;
         }
         const size_t src = (((size_t)b * p.T + t0 + r) * p.H + h) * K + kc * 8;
         float x[8], y[8], ep[8], em[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { ep[j] = __expf(gi[j] - hf[j]); em[j] = __expf(hf[j] - gi[j]); }
+        for (int j = 0; j < 8; ++j) { ep[j] = __expf(gi[j] - hf[j]); em[j] = __frcp_rn(ep[j]); }
         t8::unpack8(rowok ? *reinterpret_cast<const uint4*>(p.q + src) : zero, x);
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = x[j] * p.scale * ep[j];
@@ -668,108 +682,6 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
 }
 
 // ------------------------------------------------------------------------------------------
-// generic product over C8 tiles:  D[rows x N] = sum_c op(A_c) op(B_c)^T  (up to three chains),
-// optional causal mask, written as a C8 tile or as bf16 rows of a [B,T,H,N] tensor.
-// Used for every per-chunk product of the backward pass (HRDPLR/bwd_triton.py kernels dAu, dv,
-// bwd_o, wy, and the score-gradient applications of intra) with the operands chosen per call.
-// ------------------------------------------------------------------------------------------
-struct Opnd {
-    const uint4* p;
-    int rows, cols;       // tile shape
-    int mn;               // 0: contraction over the tile's columns, 1: over its rows
-};
-struct ChainP {
-    Opnd A[3], B[3];
-    int kdim[3];
-    int nchains;
-    int N;                // output columns (multiple of 16, <= 128)
-    int out_rows;         // 64 or 128
-    uint4* out;           // C8 tile output [out_rows x N] per chunk, or null
-    __nv_bfloat16* out_rows_bthn;   // else: rows t = n*64 + r of a [B,T,H,N] tensor
-    int mask, ri, rj;     // 0 none, 1 keep (r/ri) >= (c/rj), 2 keep (r/ri) > (c/rj)
-    int T, H, NT;
-    int* status;
-};
-
-__global__ void __launch_bounds__(128) chain_tc_kernel(ChainP p) {
-    extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) uint64_t ld_bar, mma_bar;
-    __shared__ uint32_t tmem_s;
-    const long long g = blockIdx.x;
-    const int tid = threadIdx.x, warp = tid >> 5;
-    if (warp == 0) { tmem_alloc(&tmem_s, 128); tmem_relinquish(); }
-    Tile tA[3], tB[3];
-    {
-        uint32_t off = 0, total = 0;
-        for (int c = 0; c < p.nchains; ++c) total += (uint32_t)(p.A[c].rows * p.A[c].cols + p.B[c].rows * p.B[c].cols) * 2u;
-        if (tid == 0) {
-            mbar_init(&ld_bar, 1); mbar_init(&mma_bar, 1); fence_mbar_init();
-            mbar_expect_tx(&ld_bar, total);
-        }
-        for (int c = 0; c < p.nchains; ++c) {           // A tiles first: the ones read past their end (64-row A in an
-            const uint32_t bytes = (uint32_t)p.A[c].rows * p.A[c].cols * 2u;   // M=128 product) are followed by B tiles
-            tA[c] = t8::tile(smem + off, p.A[c].rows);
-            if (tid == 0) bulk_g2s(smem + off, p.A[c].p + g * (bytes / 16), bytes, &ld_bar);
-            off += bytes;
-        }
-        for (int c = 0; c < p.nchains; ++c) {
-            const uint32_t bytes = (uint32_t)p.B[c].rows * p.B[c].cols * 2u;
-            tB[c] = t8::tile(smem + off, p.B[c].rows);
-            if (tid == 0) bulk_g2s(smem + off, p.B[c].p + g * (bytes / 16), bytes, &ld_bar);
-            off += bytes;
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = tmem_s;
-    wait_or_flag(&ld_bar, 0, p.status, 20);
-    if (tid == 0) {
-        for (int c = 0; c < p.nchains; ++c) {
-            const bool acc = c > 0;
-            if (!p.A[c].mn && !p.B[c].mn) t8::mma_chain<false, false>(tmem, tA[c], 0, 0, tB[c], 0, 0, p.N, p.kdim[c], acc);
-            else if (!p.A[c].mn && p.B[c].mn) t8::mma_chain<false, true>(tmem, tA[c], 0, 0, tB[c], 0, 0, p.N, p.kdim[c], acc);
-            else if (p.A[c].mn && !p.B[c].mn) t8::mma_chain<true, false>(tmem, tA[c], 0, 0, tB[c], 0, 0, p.N, p.kdim[c], acc);
-            else t8::mma_chain<true, true>(tmem, tA[c], 0, 0, tB[c], 0, 0, p.N, p.kdim[c], acc);
-        }
-        umma_commit(&mma_bar);
-    }
-    wait_or_flag(&mma_bar, 0, p.status, 21);
-    tc_fence_after();
-    if (warp * 32 < p.out_rows) {
-        const int r = tid;
-        uint4* dst_rows = nullptr;
-        bool row_ok = true;
-        if (!p.out) {
-            const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
-            const int b = bh / p.H, h = bh % p.H;
-            const int t = n * C + r;
-            row_ok = t < p.T;
-            dst_rows = reinterpret_cast<uint4*>(p.out_rows_bthn + (((size_t)b * p.T + (row_ok ? t : 0)) * p.H + h) * p.N);
-        }
-        for (int cg = 0; cg < p.N / 8; ++cg) {
-            uint32_t v[8]; float f[8];
-            tmem_ld_x8(t8::taddr(tmem, warp, cg * 8), v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const int c = cg * 8 + j;
-                bool keep = true;
-                if (p.mask == 1) keep = (r / p.ri) >= (c / p.rj);
-                else if (p.mask == 2) keep = (r / p.ri) > (c / p.rj);
-                f[j] = keep ? __uint_as_float(v[j]) : 0.f;
-            }
-            const uint4 c = t8::pack8(f);
-            if (p.out) p.out[g * (long long)(p.out_rows * p.N / 8) + cg * p.out_rows + r] = c;
-            else if (row_ok) dst_rows[cg] = c;
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, 128);
-}
-
-// ------------------------------------------------------------------------------------------
 // backward through the WY representation, one kernel per chunk   (HRDPLR/bwd_triton.py:489-612)
 //   dWh = dv2 St^T ; dP = M^T dv2 ; dAak = smask(dP v^T) ; dM = dv2 P^T + dWh Ah^T ;
 //   dAab = smask(M^T dM M^T)
@@ -928,82 +840,103 @@ __global__ void __launch_bounds__(128) wy_bwd_tc_kernel(WyBwdP p) {
     if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
-// dO rows of the public [B,T,H,V] tensor -> C8 tile [64 x 128] per chunk
-__global__ void __launch_bounds__(128) rows_to_c8_kernel(const __nv_bfloat16* src, uint4* dst, int T, int H, int NT) {
-    const long long g = blockIdx.x;
-    const int bh = (int)(g / NT), n = (int)(g % NT);
-    const int b = bh / H, h = bh % H;
-    const int r = threadIdx.x & 63;
-    const int t = n * C + r;
-    for (int s = 0; s < 8; ++s) {
-        const int kc = (threadIdx.x >> 6) * 8 + s;
-        uint4 c = make_uint4(0, 0, 0, 0);
-        if (t < T) c = *reinterpret_cast<const uint4*>(src + (((size_t)b * T + t) * H + h) * V + kc * 8);
-        dst[g * CH64 + kc * 64 + r] = c;
-    }
-}
-
 // ------------------------------------------------------------------------------------------
-// backward assembly (CUDA cores, streaming): from the gradients of the hat operands to the
-// public gradients and the log-decay gradient
-//   dq = scale e^{gi-half} dQh, dk = e^{half-gi} dKh, da = e^{ge-half} dAh, db = e^{half-gi} dBh
-//   dgk = revcumsum(Qh dQh - Kh dKh - sum_r Bh dBh + sum_r Ah dAh) - sum_r Ah dAh + dgl
-//   (HRDPLR/bwd_triton.py:854-880 and :944-946)
+// backward, first stage (HRDPLR/bwd_triton.py:17-105), one kernel per chunk:
+//   dAqk = tril(dO v^T), dAqb = mask(dO v2^T), dv2_intra = Aqb^T dO
+// dO is read from the public [B,T,H,V] tensor, laid out as a C8 tile in shared memory (and stored
+// for the later stages); v, v2 and Aqb arrive by bulk copy.
 // ------------------------------------------------------------------------------------------
-struct FinalP {
-    const uint4 *Qh, *Kh, *Ah, *Bh, *dQh, *dKh, *dAh, *dBh;
-    const float *ghat, *dgl;
-    __nv_bfloat16 *dq, *dk, *da, *db;
-    void* dgk;
-    float scale;
-    int T, H, NT, gdt;
+struct DauP {
+    const __nv_bfloat16* d_o;
+    const uint4 *Vc, *V2, *Aqb;
+    uint4 *dOc, *dAqk, *dAqb, *DV2;
+    int T, H, NT;
+    int* status;
 };
 
-__device__ __forceinline__ float c8g(const uint4* tile, int rows, int r, int c) {
-    const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(tile + (c >> 3) * rows + r);
-    return __bfloat162float(q[c & 7]);
-}
-
-__global__ void __launch_bounds__(128) bwd_final_kernel(FinalP p) {
+__global__ void __launch_bounds__(128) dau_tc_kernel(DauP p) {
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint4* sdO = reinterpret_cast<uint4*>(smem);     // 16 KB [64 x 128]
+    uint4* sAqb = sdO + CH64;                        // 16 KB [64 x 128]
+    uint4* sVc = sAqb + CH64;                        // 16 KB [64 x 128]
+    uint4* sV2 = sVc + CH64;                         // 32 KB [128 x 128]
+    __shared__ __align__(8) uint64_t ld_bar, mma_bar;
+    __shared__ uint32_t tmem_s;
     const long long g = blockIdx.x;
-    const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
-    const int b = bh / p.H, h = bh % p.H;
-    const int k = threadIdx.x;
-    const uint4 *Qh = p.Qh + g * CH64, *Kh = p.Kh + g * CH64, *dQh = p.dQh + g * CH64, *dKh = p.dKh + g * CH64;
-    const uint4 *Ah = p.Ah + g * CH128, *Bh = p.Bh + g * CH128, *dAh = p.dAh + g * CH128, *dBh = p.dBh + g * CH128;
-    const float* gh = p.ghat + (size_t)g * C * K;
-    const float half = gh[(size_t)(C - 1) * K + k];
-    const float dgl = p.dgl[(size_t)g * K + k];
-    float run = 0.f;
-    for (int i = C - 1; i >= 0; --i) {
-        const float x = gh[(size_t)i * K + k];
-        const float xe = i > 0 ? gh[(size_t)(i - 1) * K + k] : -half;
-        const float ep = __expf(x), em = __expf(-x), ee = __expf(xe);
-        const float qh = c8g(Qh, 64, i, k), dqh = c8g(dQh, 64, i, k);
-        const float kh = c8g(Kh, 64, i, k), dkh = c8g(dKh, 64, i, k);
-        float d_gi = qh * dqh - kh * dkh, d_ge = 0.f;
-        const int t = n * C + i;
-        const bool ok = t < p.T;
-#pragma unroll
-        for (int rr = 0; rr < R; ++rr) {
-            const float ah = c8g(Ah, 128, i * R + rr, k), dah = c8g(dAh, 128, i * R + rr, k);
-            const float bhv = c8g(Bh, 128, i * R + rr, k), dbh = c8g(dBh, 128, i * R + rr, k);
-            d_ge = fmaf(ah, dah, d_ge);
-            d_gi = fmaf(-bhv, dbh, d_gi);
-            if (ok) {
-                const size_t oa = (((size_t)b * p.T * R + (size_t)t * R + rr) * p.H + h) * K + k;
-                p.da[oa] = __float2bfloat16_rn(ee * dah);
-                p.db[oa] = __float2bfloat16_rn(em * dbh);
-            }
-        }
-        run += d_gi + d_ge;
-        if (ok) {
-            const size_t o = (((size_t)b * p.T + t) * p.H + h) * K + k;
-            p.dq[o] = __float2bfloat16_rn(p.scale * ep * dqh);
-            p.dk[o] = __float2bfloat16_rn(em * dkh);
-            st_elem(p.dgk, o, p.gdt, run - d_ge + dgl);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (warp == 0) { tmem_alloc(&tmem_s, 256); tmem_relinquish(); }
+    if (tid == 0) {
+        mbar_init(&ld_bar, 1); mbar_init(&mma_bar, 1); fence_mbar_init();
+        mbar_expect_tx(&ld_bar, 65536);
+        bulk_g2s(sAqb, p.Aqb + g * CH64, 16384, &ld_bar);
+        bulk_g2s(sVc, p.Vc + g * CH64, 16384, &ld_bar);
+        bulk_g2s(sV2, p.V2 + g * CH128, 32768, &ld_bar);
+    }
+    {
+        const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
+        const int b = bh / p.H, h = bh % p.H;
+        for (int it = 0; it < 8; ++it) {
+            const int blk = warp * 8 + it;
+            const int r = (blk >> 2) * 8 + (lane & 7);
+            const int kc = (blk & 3) * 4 + (lane >> 3);
+            const int t = n * C + r;
+            uint4 c = make_uint4(0, 0, 0, 0);
+            if (t < p.T) c = *reinterpret_cast<const uint4*>(p.d_o + (((size_t)b * p.T + t) * p.H + h) * V + kc * 8);
+            sdO[kc * 64 + r] = c;
+            p.dOc[g * CH64 + kc * 64 + r] = c;
         }
     }
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_s;
+    const Tile tdO = t8::tile(sdO, 64), tAqb = t8::tile(sAqb, 64), tVc = t8::tile(sVc, 64), tV2 = t8::tile(sV2, 128);
+    wait_or_flag(&ld_bar, 0, p.status, 50);
+    if (tid == 0) {
+        t8::mma_chain<false, false>(tmem, tdO, 0, 0, tV2, 0, 0, 128, 128, false);        // dO v2^T
+        t8::mma_chain<true, true>(tmem + 128, tAqb, 0, 0, tdO, 0, 0, 128, 64, false);    // Aqb^T dO
+        umma_commit(&mma_bar);
+    }
+    wait_or_flag(&mma_bar, 0, p.status, 51);
+    tc_fence_after();
+    float f[64];
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {
+        if (warp < 2) {
+            tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) if (!(((hh * 64 + c8 * 8 + j) >> 1) <= tid)) f[c8 * 8 + j] = 0.f;
+                p.dAqb[g * CH64 + (hh * 8 + c8) * 64 + tid] = t8::pack8(f + c8 * 8);
+            }
+        }
+        tmem_row64(t8::taddr(tmem, warp, 128 + hh * 64), f);
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) p.DV2[g * CH128 + (hh * 8 + c8) * 128 + tid] = t8::pack8(f + c8 * 8);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+        tc_fence_after();
+        t8::mma_chain<false, false>(tmem, tdO, 0, 0, tVc, 0, 0, 64, 128, false);         // dO v^T
+        umma_commit(&mma_bar);
+    }
+    wait_or_flag(&mma_bar, 1, p.status, 52);
+    tc_fence_after();
+    if (warp < 2) {
+        tmem_row64(t8::taddr(tmem, warp, 0), f);
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) if (!((c8 * 8 + j) <= tid)) f[c8 * 8 + j] = 0.f;
+            p.dAqk[g * 512 + c8 * 64 + tid] = t8::pack8(f + c8 * 8);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1126,7 +1059,7 @@ __device__ __forceinline__ float c8s(const uint4* tile, int rows, int r, int c) 
     return __bfloat162float(q[c & 7]);
 }
 
-__global__ void __launch_bounds__(128) grad_tc_kernel(GradP p) {
+__global__ void __launch_bounds__(288) grad_tc_kernel(GradP p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint4* sA = reinterpret_cast<uint4*>(smem);          // 32 KB slots
     uint4* sB = sA + CH128;
@@ -1142,8 +1075,9 @@ __global__ void __launch_bounds__(128) grad_tc_kernel(GradP p) {
     __shared__ uint32_t tmem_s;
     const long long g = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5;
+    const bool producer = tid == 256;                   // lane 0 of the ninth warp loads tiles and issues MMAs
     if (warp == 0) { tmem_alloc(&tmem_s, 512); tmem_relinquish(); }
-    if (tid == 0) {
+    if (producer) {
         mbar_init(&L1, 1); mbar_init(&L2, 1); mbar_init(&L3, 1); mbar_init(&L4, 1); mbar_init(&L5, 1);
         mbar_init(&m1, 1); mbar_init(&m2, 1); mbar_init(&m3, 1); mbar_init(&m4, 1);
         fence_mbar_init();
@@ -1165,7 +1099,7 @@ __global__ void __launch_bounds__(128) grad_tc_kernel(GradP p) {
     tc_fence_after();
     const uint32_t tmem = tmem_s;
     // TMEM columns: dQh^T 0..63, dv^T 64..127, dAh^T 128..255, dBh^T 256..383, dKh^T 384..447
-    if (tid == 0) {
+    if (producer) {
         wait_or_flag(&L1, 0, p.status, 40);
         chain0<false, false>(tmem, t8::tile(sA, 128), t8::tile(sa, 64), 64, 128, false);          // St dO^T
         chain0<true, false>(tmem, t8::tile(sb, 64), t8::tile(sx, 64), 64, 64, true);              // Kh^T dAqk^T
@@ -1207,21 +1141,29 @@ __global__ void __launch_bounds__(128) grad_tc_kernel(GradP p) {
         bulk_g2s(sA, p.Bh + g * CH128, 32768, &L5);
         bulk_g2s(sC, p.ghat + (size_t)g * C * K, 32768, &L5);      // fp32 [64][128] over the dSt slot
     }
-    wait_or_flag(&m4, 0, p.status, 48);
-    wait_or_flag(&L5, 0, p.status, 49);
+    if (warp < 8) {
+        wait_idle_or_flag(&m4, 0, p.status, 48);
+        wait_idle_or_flag(&L5, 0, p.status, 49);
+    }
     tc_fence_after();
-    {
+    if (warp < 8) {
+        // two warpgroups share the token loop: group 0 walks tokens 63..32, group 1 tokens 31..0 and
+        // adds group 0's total to its running sums afterwards
+        __shared__ float upper_total[K];
         const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
         const int b = bh / p.H, h = bh % p.H;
-        const int k = tid;
+        const int k = tid & 127, wg = tid >> 7;
         const float* gh = reinterpret_cast<const float*>(sC);
         const float half = gh[(size_t)(C - 1) * K + k];
         const float dgl = p.dgl[(size_t)g * K + k];
         const uint4 *tQh = sD, *tKh = sb, *tAh = sB, *tBh = sA;
         float run = 0.f;
-        float x = half;                                   // ghat of token 63 is g_last - half = half
+        float* dgk_loc = reinterpret_cast<float*>(sE);    // [64][128] fp32 over the (consumed) dAab slot
+        const int i_hi = wg == 0 ? 63 : 31;
+        float ep = __expf(gh[(size_t)i_hi * K + k]);
 #pragma unroll 1
-        for (int ib = 7; ib >= 0; --ib) {
+        for (int ibl = 3; ibl >= 0; --ibl) {
+            const int ib = (wg == 0 ? 4 : 0) + ibl;
             uint32_t vq[8], vk[8], va[16], vb[16];
             tmem_ld_x8(t8::taddr(tmem, warp, ib * 8), vq);
             tmem_ld_x8(t8::taddr(tmem, warp, 384 + ib * 8), vk);
@@ -1234,7 +1176,8 @@ __global__ void __launch_bounds__(128) grad_tc_kernel(GradP p) {
                 const int t = n * C + i;
                 const bool ok = t < p.T;
                 const float xe = i > 0 ? gh[(size_t)(i - 1) * K + k] : -half;      // ge - half
-                const float ep = __expf(x), em = __expf(-x), ee = __expf(xe);
+                const float ee = __expf(xe);
+                const float em = __frcp_rn(ep);
                 const float dqh = __uint_as_float(vq[j]), dkh = __uint_as_float(vk[j]);
                 float d_gi = c8s(tQh, 64, i, k) * dqh - c8s(tKh, 64, i, k) * dkh;
                 float d_ge = 0.f;
@@ -1250,25 +1193,33 @@ __global__ void __launch_bounds__(128) grad_tc_kernel(GradP p) {
                     }
                 }
                 run += d_gi + d_ge;
+                dgk_loc[i * K + k] = run - d_ge + dgl;
                 if (ok) {
                     const size_t o = (((size_t)b * p.T + t) * p.H + h) * K + k;
                     p.dq[o] = __float2bfloat16_rn(p.scale * ep * dqh);
                     p.dk[o] = __float2bfloat16_rn(em * dkh);
-                    st_elem(p.dgk, o, p.gdt, run - d_ge + dgl);
                 }
-                x = xe;                                   // ghat of token i-1
+                ep = ee;                                  // e^{ghat} of token i-1
             }
         }
-        // dv: accumulator lane = value channel
-#pragma unroll 1
-        for (int cb = 0; cb < 2; ++cb) {
+        if (wg == 0) upper_total[k] = run;
+        asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight epilogue warps only
+        const float add = wg == 0 ? 0.f : upper_total[k];
+#pragma unroll 4
+        for (int jj = 0; jj < 32; ++jj) {
+            const int i = (wg == 0 ? 32 : 0) + jj;
+            const int t = n * C + i;
+            if (t < p.T) st_elem(p.dgk, (((size_t)b * p.T + t) * p.H + h) * K + k, p.gdt, dgk_loc[i * K + k] + add);
+        }
+        // dv: accumulator lane = value channel; each warpgroup writes 32 tokens
+        {
             uint32_t v[32];
-            tmem_ld_x32(t8::taddr(tmem, warp, 64 + cb * 32), v);
+            tmem_ld_x32(t8::taddr(tmem, warp, 64 + wg * 32), v);
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const int t = n * C + cb * 32 + j;
-                if (t < p.T) p.dv[(((size_t)b * p.T + t) * p.H + h) * V + tid] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                const int t = n * C + wg * 32 + j;
+                if (t < p.T) p.dv[(((size_t)b * p.T + t) * p.H + h) * V + k] = __float2bfloat16_rn(__uint_as_float(v[j]));
             }
         }
     }
@@ -1279,7 +1230,6 @@ __global__ void __launch_bounds__(128) grad_tc_kernel(GradP p) {
 
 constexpr int kGradSmem = 5 * 32768 + 3 * 16384 + 2 * 8192;
 constexpr int kWySmem = 6 * 32768 + 16384;
-constexpr int kChainSmemMax = 6 * 32768 + 32768;   // six tiles plus slack for 64-row A operands read as 128 rows
 
 template <typename Kern>
 int set_smem(Kern kern, int bytes) {
@@ -1315,9 +1265,9 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         TRY(set_smem(wu_tc_kernel, 98304));
         TRY(set_smem(scan_tc_kernel, 196608));
         TRY(set_smem(out_tc_kernel, 122880));
-        TRY(set_smem(chain_tc_kernel, kChainSmemMax));
         TRY(set_smem(wy_bwd_tc_kernel, kWySmem));
         TRY(set_smem(grad_tc_kernel, kGradSmem));
+        TRY(set_smem(dau_tc_kernel, 81920));
         attr_dev = dev;
     }
     auto U4 = [&](size_t off) { return reinterpret_cast<uint4*>(ws + off); };
@@ -1351,12 +1301,6 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     return HDLA_OK;
 }
 
-namespace {
-Opnd opnd(const unsigned char* ws, size_t off, int rows, int cols, int mn) {
-    return Opnd{reinterpret_cast<const uint4*>(ws + off), rows, cols, mn};
-}
-}  // namespace
-
 int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a, const void* b,
                  const void* gk, float scale, const float* h0, const void* d_o, const float* dht, void* dq, void* dk,
                  void* dv, void* da, void* db, void* dgk, float* dh0, unsigned char* ws, cudaStream_t st) {
@@ -1369,61 +1313,11 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     const unsigned G = (unsigned)pl.G;
     typedef __nv_bfloat16* bp;
 
-    rows_to_c8_kernel<<<G, 128, 0, st>>>((const __nv_bfloat16*)d_o, U4(pl.dOc), d.T, d.H, pl.NT);
-    HDLA_CHECK_LAUNCH("rows_to_c8_kernel");
+    DauP dp{(const __nv_bfloat16*)d_o, U4(pl.Vc), U4(pl.V2), U4(pl.Aqb), U4(pl.dOc), U4(pl.dAqk), U4(pl.dAqb), U4(pl.DV2),
+            d.T, d.H, pl.NT, status};
+    dau_tc_kernel<<<G, 128, 81920, st>>>(dp);
+    HDLA_CHECK_LAUNCH("dau_tc_kernel");
 
-    // one product: up to three chains into one accumulator
-    struct Ch { Opnd A, B; int kdim; };
-    auto run = [&](std::initializer_list<Ch> chains, int N, int out_rows, size_t out_off, bp rows_out, int mask,
-                   int ri, int rj) -> int {
-        ChainP cp{};
-        int c = 0;
-        size_t bytes = 0;
-        for (const Ch& ch : chains) {
-            cp.A[c] = ch.A; cp.B[c] = ch.B; cp.kdim[c] = ch.kdim;
-            bytes += (size_t)(ch.A.rows * ch.A.cols + ch.B.rows * ch.B.cols) * 2;
-            ++c;
-        }
-        cp.nchains = c; cp.N = N; cp.out_rows = out_rows;
-        cp.out = rows_out ? nullptr : U4(out_off);
-        cp.out_rows_bthn = rows_out;
-        cp.mask = mask; cp.ri = ri; cp.rj = rj; cp.T = d.T; cp.H = d.H; cp.NT = pl.NT; cp.status = status;
-        bytes += 32768;                               // slack: 64-row A tiles are read as 128 rows
-        if (bytes > (size_t)kChainSmemMax) return fail(HDLA_ERR_UNSUPPORTED, "chain: %zu bytes of shared memory", bytes);
-        chain_tc_kernel<<<G, 128, bytes, st>>>(cp);
-        HDLA_CHECK_LAUNCH("chain_tc_kernel");
-        return HDLA_OK;
-    };
-    const unsigned char* w = ws;
-    // tiles (rows, cols); last argument: 0 = contract over columns, 1 = contract over rows
-    auto dOc = [&](int mn) { return opnd(w, pl.dOc, 64, 128, mn); };
-    auto Vc = [&](int mn) { return opnd(w, pl.Vc, 64, 128, mn); };
-    auto V2 = [&](int mn) { return opnd(w, pl.V2, 128, 128, mn); };
-    auto DV2 = [&](int mn) { return opnd(w, pl.DV2, 128, 128, mn); };
-    auto Hs = [&](int mn) { return opnd(w, pl.Hs, 128, 128, mn); };
-    auto DE = [&](int mn) { return opnd(w, pl.DE, 128, 128, mn); };
-    auto Qh = [&](int mn) { return opnd(w, pl.Qh, 64, 128, mn); };
-    auto Kh = [&](int mn) { return opnd(w, pl.Kh, 64, 128, mn); };
-    auto Ah = [&](int mn) { return opnd(w, pl.Ah, 128, 128, mn); };
-    auto Bh = [&](int mn) { return opnd(w, pl.Bh, 128, 128, mn); };
-    auto Mm = [&](int mn) { return opnd(w, pl.M, 128, 128, mn); };
-    auto Pp = [&](int mn) { return opnd(w, pl.P, 128, 128, mn); };
-    auto Aqk = [&](int mn) { return opnd(w, pl.Aqk, 64, 64, mn); };
-    auto Aqb = [&](int mn) { return opnd(w, pl.Aqb, 64, 128, mn); };
-    auto Aak = [&](int mn) { return opnd(w, pl.Aak, 128, 64, mn); };
-    auto dAqk = [&](int mn) { return opnd(w, pl.dAqk, 64, 64, mn); };
-    auto dAqb = [&](int mn) { return opnd(w, pl.dAqb, 64, 128, mn); };
-    auto dAak = [&](int mn) { return opnd(w, pl.dAak, 128, 64, mn); };
-    auto dAab = [&](int mn) { return opnd(w, pl.dAab, 128, 128, mn); };
-    auto dW = [&](int mn) { return opnd(w, pl.dW, 128, 128, mn); };
-    auto dP = [&](int mn) { return opnd(w, pl.dP, 128, 128, mn); };
-    auto dM = [&](int mn) { return opnd(w, pl.dM, 128, 128, mn); };
-    auto Tmp = [&](int mn) { return opnd(w, pl.tmp, 128, 128, mn); };
-
-    // --- dAu (HRDPLR/bwd_triton.py:17-105): dAqk = tril(dO v^T), dAqb = mask(dO v2^T), dv2_intra = Aqb^T dO
-    TRY(run({{dOc(0), Vc(0), 128}}, 64, 64, pl.dAqk, nullptr, 1, 1, 1));
-    TRY(run({{dOc(0), V2(0), 128}}, 128, 64, pl.dAqb, nullptr, 1, 1, R));
-    TRY(run({{Aqb(1), dOc(1), 64}}, 128, 128, pl.DV2, nullptr, 0, 1, 1));
     // --- dhu: reverse scan (dv2 is accumulated in place over dv2_intra)
     ScanTcP sp{U4(pl.Bh), U4(pl.DV2), U4(pl.Qh), U4(pl.dOc), U4(pl.W), F(pl.E), dht, U4(pl.DE), U4(pl.DV2), dh0, nullptr,
                U4(pl.Hs), F(pl.HT), F(pl.dgl), pl.NT, 1, status};
@@ -1439,7 +1333,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
              U4(pl.Aqk), U4(pl.dW), U4(pl.M), U4(pl.dAab), U4(pl.dAak), U4(pl.V2), U4(pl.Ah), U4(pl.Qh), U4(pl.Vc),
              F(pl.ghat), F(pl.dgl), (bp)dq, (bp)dk, (bp)dv, (bp)da, (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype,
              status};
-    grad_tc_kernel<<<G, 128, kGradSmem, st>>>(gp);
+    grad_tc_kernel<<<G, 288, kGradSmem, st>>>(gp);
     HDLA_CHECK_LAUNCH("grad_tc_kernel");
     return HDLA_OK;
 }

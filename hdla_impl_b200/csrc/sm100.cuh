@@ -44,6 +44,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
     return false;
 }
 
+// Same, for long waits by threads that have nothing else to do: sleeps between polls so the
+// polling warps do not take issue slots from the warp that is producing what they wait for.
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, uint32_t limit = 1u << 22) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(200);
+    }
+    return false;
+}
+
 // ------------------------------------------------------------------------------ bulk async copy
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
