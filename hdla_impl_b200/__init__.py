@@ -6,7 +6,7 @@ Drop-in for the operator entry points of the reference package (``HRDPLR/__init_
 every kernel is hand-written CUDA inside ``libhdla.so`` behind the C ABI of ``include/hdla.h``.
 There is no CPU path and no fallback.
 """
-from .hrdplr import ChunkDPLRDeltaRuleFunction, chunk_hrdplr_delta_rule, chunk_hrdplr_fwd
+from .hrdplr import ChunkDPLRDeltaRuleFunction, check_status, chunk_hrdplr_delta_rule, chunk_hrdplr_fwd
 from .recurrent import (FusedRecurrentDPLRDeltaRuleFunction, fused_recurrent_dplr_delta_rule,
                         fused_recurrent_dplr_delta_rule_fwd)
 
@@ -16,5 +16,6 @@ __all__ = [
     "ChunkDPLRDeltaRuleFunction",
     "FusedRecurrentDPLRDeltaRuleFunction",
     "chunk_hrdplr_fwd",
+    "check_status",
     "fused_recurrent_dplr_delta_rule_fwd",
 ]

@@ -90,7 +90,12 @@ struct PrepP {
     float *E, *ghat;
     float scale;
     int T, H, NT, gdt;
+    int* status;
 };
+
+// The hat operands are scaled by up to e^{|g_last|/2}; beyond this total log decay per chunk and
+// channel they leave the bf16/fp32 exponent range and the caller must use the fp32 pipeline.
+constexpr float kMaxChunkDecay = 150.f;
 
 __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
     __shared__ float gis[C][K + 4];
@@ -137,7 +142,11 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
                 make_float4(x[i].x + off.x, x[i].y + off.y, x[i].z + off.z, x[i].w + off.w);
     }
     __syncthreads();
-    if (tid < K) p.E[(size_t)g * K + tid] = __expf(0.5f * gis[C - 1][tid]);
+    if (tid < K) {
+        const float gl = gis[C - 1][tid];
+        p.E[(size_t)g * K + tid] = __expf(0.5f * gl);
+        if (!(fabsf(gl) <= kMaxChunkDecay)) atomicExch(p.status + 1, 1);      // also catches NaN
+    }
     // hat operands: per instruction a warp covers 8 rows x 4 column groups, so every global access
     // is a run of full 32-byte sectors (64 B per row in, 128 B per column group out)
     const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -1276,7 +1285,11 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     const unsigned G = (unsigned)pl.G;
     typedef const __nv_bfloat16* bp;
     PrepP pp{(bp)q, (bp)k, (bp)v, (bp)a, (bp)b, gk, U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc), F(pl.E),
-             F(pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype};
+             F(pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status};
+    {
+        cudaError_t e = cudaMemsetAsync(ws + pl.status, 0, 256, st);
+        if (e != cudaSuccess) return fail(HDLA_ERR_CUDA, "status clear: %s", cudaGetErrorString(e));
+    }
     prep_hat_kernel<<<G, 128, 0, st>>>(pp);
     HDLA_CHECK_LAUNCH("prep_hat_kernel");
     GramP gp{U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Aak), U4(pl.Aab), status};

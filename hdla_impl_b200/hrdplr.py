@@ -59,6 +59,70 @@ def workspace_bytes(dims: _lib.HdlaDims, with_backward: bool) -> int:
     return n
 
 
+# ---- device status words ----------------------------------------------------------------------
+# The bf16 tensor-core kernels report two conditions in the first 8 bytes of the workspace (see
+# include/hdla.h).  They are copied to pinned host memory right after the forward launch, without
+# blocking, and inspected the next time this module is entered on that device (or at once with
+# HDLA_STRICT=1, which synchronises): a problem never stays silent, and the hot path never waits.
+_RING = 64
+_status = {}      # device index -> dict(host=pinned [RING,2] int32, events=[...], next=int, pending=[slots])
+
+
+def _status_state(dev):
+    st = _status.get(dev.index)
+    if st is None:
+        st = dict(host=torch.zeros(_RING, 2, dtype=torch.int32).pin_memory(),
+                  events=[torch.cuda.Event() for _ in range(_RING)], next=0, pending=[])
+        _status[dev.index] = st
+    return st
+
+
+def _raise_status(words):
+    if words[0]:
+        raise RuntimeError(f"libhdla: a device-side wait ran out (code {int(words[0])}); the results of that call are invalid")
+    if words[1]:
+        raise RuntimeError(
+            "libhdla: the total log decay of some chunk exceeds 150 in some channel, beyond what the bf16 "
+            "tensor-core pipeline represents; the results of that call are invalid. Set HDLA_FORCE_SIMT=1 to "
+            "use the fp32 pipeline, which has no such limit.")
+
+
+def check_status(dev=None, wait: bool = False) -> None:
+    """Raise if an earlier bf16 call on ``dev`` reported a problem. ``wait`` synchronises first."""
+    devs = list(_status) if dev is None else [dev.index if isinstance(dev, torch.device) else int(dev)]
+    for di in devs:
+        st = _status.get(di)
+        if st is None:
+            continue
+        keep = []
+        for slot in st["pending"]:
+            ev = st["events"][slot]
+            if wait:
+                ev.synchronize()
+            if ev.query():
+                words = st["host"][slot].tolist()
+                if words[0] or words[1]:
+                    st["pending"] = [s_ for s_ in st["pending"] if s_ != slot]
+                    _raise_status(words)
+            else:
+                keep.append(slot)
+        st["pending"] = keep
+
+
+def _post_status(ws: torch.Tensor, dev) -> None:
+    st = _status_state(dev)
+    slot = st["next"]
+    st["next"] = (slot + 1) % _RING
+    if slot in st["pending"]:                       # ring wrapped: that copy finished long ago
+        st["events"][slot].synchronize()
+        check_status(dev)
+    st["host"][slot].copy_(ws[:8].view(torch.int32), non_blocking=True)
+    st["events"][slot].record(torch.cuda.current_stream(dev))
+    st["pending"].append(slot)
+    if os.environ.get("HDLA_STRICT", "0") == "1":
+        check_status(dev, wait=True)
+
+
 def _alloc_ws(nbytes: int, device) -> torch.Tensor:
     return torch.empty(nbytes, dtype=torch.uint8, device=device)
 
@@ -76,6 +140,7 @@ def chunk_hrdplr_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state
     assert head_first is False, "head_first=True is not supported (as in the reference)"
     dev = _lib.require_cuda(q, k, v, a, b, gk, initial_state)
     _check_shapes(q, k, v, a, b, gk, RANK_AB, initial_state)
+    check_status(dev)
     lib = _lib.load()
     dims = _dims(q, v, a, gk, RANK_AB, chunk_size)
     B, T, H, K = q.shape
@@ -89,6 +154,9 @@ def chunk_hrdplr_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state
                                 _lib.ptr(gk), float(scale), _lib.ptr(h0), _lib.ptr(o), _lib.ptr(ht),
                                 _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
     _lib.check(rc, "hdla_chunk_fwd")
+    if q.dtype == torch.bfloat16 and not (dims.flags & _lib.FLAG_FORCE_SIMT):
+        with torch.cuda.device(dev):
+            _post_status(ws, dev)
     if _keep_ws:
         return o, ht, ws
     return o, ht
@@ -122,6 +190,7 @@ class ChunkDPLRDeltaRuleFunction(torch.autograd.Function):
     def backward(ctx, do, dht):
         q, k, v, a, b, gk, initial_state = ctx.saved_tensors
         dev = q.device
+        check_status(dev)
         lib = _lib.load()
         ws = ctx.ws
         ctx.ws = None

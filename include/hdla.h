@@ -91,6 +91,12 @@ HDLA_API size_t hdla_chunk_workspace_bytes(const HdlaDims* dims, int with_backwa
 HDLA_API int hdla_debug_tc_buffer(const HdlaDims* dims, const void* workspace, const char* name, float* out,
                                   void* cuda_stream);
 
+/* The first 8 bytes of a workspace used by the bf16 tensor-core pipeline are two int32 status words
+ * written by the kernels: word 0 is non-zero if a bounded device-side wait ran out (results invalid),
+ * word 1 is non-zero if some chunk's total log decay |sum_chunk gk| exceeded 150 in some channel, which
+ * the bf16 pipeline cannot represent (results invalid; rerun with HDLA_FLAG_FORCE_SIMT, whose fp32
+ * pipeline has no such limit).  Callers read them after the stream has finished the call. */
+
 /* Chunked forward.  Replaces chunk_hrdplr_fwd (HRDPLR/hrdplr.py:25-99), i.e. the stage
  * sequence cumsum -> intra-chunk A matrices -> (I-Aab)^-1 and w/u -> state scan -> output.
  *   h0  : [B,H,K,V] fp32 initial state or NULL (zero state)

@@ -220,3 +220,42 @@ def test_error_paths(dev):
         H.chunk_hrdplr_delta_rule(args[0], args[1], args[2], args[3][:, :-1], args[4], args[5], R)
     with pytest.raises(RuntimeError, match="CUDA"):
         H.chunk_hrdplr_delta_rule(*[x[n] for n in ("q", "k", "v", "a", "b", "gk")], R)
+
+
+def test_bf16_strong_decay_is_reported_and_fp32_pipeline_handles_it(dev, monkeypatch):
+    """A chunk whose total log decay exceeds what the bf16 pipeline represents must not pass silently;
+    the fp32 pipeline (HDLA_FORCE_SIMT) has no such limit and matches the oracle."""
+    import hdla_impl_b200 as H
+    x = make_inputs(1, 128, 1, 128, 128, R, seed=13, dtype=torch.bfloat16)
+    x["gk"] = torch.full_like(x["gk"].float(), -3.0)            # 64 * 3 = 192 > 150 per chunk
+    args = [x[n].to(dev) for n in ("q", "k", "v", "a", "b", "gk")]
+    monkeypatch.setenv("HDLA_STRICT", "1")
+    with pytest.raises(RuntimeError, match="log decay"):
+        H.chunk_hrdplr_delta_rule(*args, R, chunk_size=64)
+    monkeypatch.setenv("HDLA_FORCE_SIMT", "1")
+    o, ht = H.chunk_hrdplr_delta_rule(*args, R, chunk_size=64, output_final_state=True)
+    H.check_status(dev, wait=True)
+    f = lambda n: x[n].double()
+    ro, rh = orc.recurrent_ref(f("q"), f("k"), f("v"), f("a"), f("b"), f("gk"), R, None, None)
+    assert orc.rel_err(o, ro) < 2e-2 and orc.rel_err(ht, rh) < 1e-3
+
+
+def test_prefill_then_decode_state_handoff(dev):
+    """final_state of the chunked call seeds the recurrent calls (the reference layer's cache path,
+    HRDPLR/hdla_custom.py:295-337): prefill T0 tokens chunked, then decode token by token."""
+    import hdla_impl_b200 as H
+    T0, T1 = 192, 5
+    x = make_inputs(2, T0 + T1, 2, 128, 128, R, seed=14, dtype=torch.bfloat16)
+    names = ("q", "k", "v", "a", "b", "gk")
+    rr = lambda n: R if n in ("a", "b") else 1
+    pre = [x[n][:, :T0 * rr(n)].to(dev) for n in names]
+    o0, S = H.chunk_hrdplr_delta_rule(*pre, R, output_final_state=True, chunk_size=64)
+    outs = [o0]
+    for t in range(T0, T0 + T1):
+        cur = [x[n][:, t * rr(n):(t + 1) * rr(n)].to(dev) for n in names]
+        o, S = H.fused_recurrent_dplr_delta_rule(*cur, R, initial_state=S, output_final_state=True)
+        outs.append(o)
+    o = torch.cat(outs, 1)
+    f = lambda n: x[n].double()
+    ro, rh = orc.recurrent_ref(f("q"), f("k"), f("v"), f("a"), f("b"), f("gk"), R, None, None)
+    assert orc.rel_err(o, ro) < 2e-2 and orc.rel_err(S, rh) < 2e-2
