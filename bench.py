@@ -73,6 +73,23 @@ def bytes_per_token_head(C: int, D: int, elt: int) -> float:
     return (8 * D + D) * elt + (9 * D + 8 * D) * elt + 4 * (D * D * 2 / C)
 
 
+# Algorithmic HBM bytes per (chunk, head) of each kernel of the bf16 pipeline: every operand tile it
+# needs read once, every result written once (KiB; bf16 tiles, fp32 ghat/E; K = V = 128, chunk 64, R = 2).
+# scan_tc_kernel is launched twice per step (forward 192.5, reverse 225).
+KERNEL_KIB = {
+    "prep_hat_kernel": 272.5, "gram_tc_kernel": 168.0, "inverse_tc_kernel": 64.0, "wu_tc_kernel": 192.0,
+    "scan_tc_kernel": (192.5 + 225.0) / 2, "out_tc_kernel": 136.0, "dau_tc_kernel": 152.0,
+    "wy_bwd_tc_kernel": 288.0, "grad_tc_kernel": 576.5,
+}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch (GB) at cfg 1: one ncu capture at B=2 (a quarter of
+# cfg 1; traffic is proportional to the number of chunks), scaled by 4 -- see profiles/chunk_tc_pipeline_traffic.md
+KERNEL_NCU_TRAFFIC_GB = {
+    "prep_hat_kernel": 2.10, "gram_tc_kernel": 1.20, "inverse_tc_kernel": 0.35, "wu_tc_kernel": 1.39,
+    "scan_tc_kernel": (1.49 + 1.77) / 2, "out_tc_kernel": 1.09, "dau_tc_kernel": 1.08, "wy_bwd_tc_kernel": 2.24,
+    "grad_tc_kernel": 4.75,
+}
+
+
 def load_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -232,6 +249,15 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     launches = _lib.kernel_launches() - l0
     ms = e0.elapsed_time(e1)
+    # per-kernel durations, live: the library brackets every launch with CUDA events on its stream
+    ktimes = {}
+    if rank == 0:
+        _lib.timing_enable(True)
+        for _ in range(3):
+            step(leaves, dev_in["do"])
+        torch.cuda.synchronize(dev)
+        _lib.timing_enable(False)
+        ktimes = _lib.timing_report()
     if rank == 0:
         # the timed region can be shorter than nvidia-smi's sampling period: keep the same load running
         # (untimed) until a few samples exist, so the clocks reported are clocks under this load
@@ -293,6 +319,29 @@ def run_ours(args, rank, world, local_rank):
             "hbm": {"achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
                     "algorithmic_bytes": byts},
         }
+        if ktimes and dt == "bf16":
+            G = (B if args.scaling == "weak" else B // world) * H * ((T + C - 1) // C)
+            tot = sum(v[1] for v in ktimes.values())
+            table = {}
+            for name, (cnt, tms) in sorted(ktimes.items(), key=lambda kv: -kv[1][1]):
+                avg = tms / cnt
+                kib = KERNEL_KIB.get(name)
+                table[name] = {"launches_per_step": cnt // 3, "avg_ms": avg, "share": tms / tot,
+                               "algorithmic_GBps": (kib * 1024 * G / (avg / 1e3) / 1e9) if kib else None}
+            top = next(iter(table))
+            if KERNEL_KIB.get(top):
+                a = table[top]["algorithmic_GBps"]
+                roof = {
+                    "bound": "hbm", "kernel": top, "achieved": a, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": a / peaks["hbm_gbs"], "traffic": KERNEL_NCU_TRAFFIC_GB.get(top),
+                    "peak_source": f"{how} (copy)", "avg_launch_ms": table[top]["avg_ms"],
+                    "algorithmic_bytes_per_launch": KERNEL_KIB[top] * 1024 * G,
+                    "step": {"tensor": {"achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf,
+                                        "flops_per_step": flops},
+                             "hbm": {"achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                     "frac": gbs / peaks["hbm_gbs"], "algorithmic_bytes_per_step": byts}},
+                    "kernels": table,
+                }
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             T_s = min(T, 1024)

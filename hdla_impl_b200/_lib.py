@@ -18,7 +18,7 @@ FLAG_FORCE_SIMT = 2
 
 EXPORTS = (
     "hdla_version", "hdla_last_error", "hdla_chunk_workspace_bytes", "hdla_chunk_fwd", "hdla_chunk_bwd",
-    "hdla_recurrent_fwd", "hdla_kernel_launches", "hdla_debug_tc_buffer", "hdla_chunk_fwd_noalloc",
+    "hdla_recurrent_fwd", "hdla_kernel_launches", "hdla_debug_tc_buffer", "hdla_chunk_fwd_noalloc", "hdla_timing_enable", "hdla_timing_report",
 )
 
 
@@ -55,6 +55,10 @@ def load() -> C.CDLL:
         lib.hdla_last_error.argtypes = []
         lib.hdla_kernel_launches.restype = C.c_ulonglong
         lib.hdla_kernel_launches.argtypes = []
+        lib.hdla_timing_enable.restype = None
+        lib.hdla_timing_enable.argtypes = [C.c_int]
+        lib.hdla_timing_report.restype = C.c_size_t
+        lib.hdla_timing_report.argtypes = [C.c_char_p, C.c_size_t]
         lib.hdla_debug_tc_buffer.restype = C.c_int
         lib.hdla_debug_tc_buffer.argtypes = [dp, vp, C.c_char_p, vp, vp]
         lib.hdla_chunk_workspace_bytes.restype = C.c_size_t
@@ -75,6 +79,21 @@ def load() -> C.CDLL:
 
 def kernel_launches() -> int:
     return int(load().hdla_kernel_launches())
+
+
+def timing_enable(on: bool) -> None:
+    load().hdla_timing_enable(int(on))
+
+
+def timing_report() -> dict:
+    """{kernel name: (launches, total ms)} since timing was enabled; waits for the recorded events."""
+    buf = C.create_string_buffer(1 << 16)
+    load().hdla_timing_report(buf, len(buf))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, cnt, ms = line.rsplit(" ", 2)
+        out[name] = (int(cnt), float(ms))
+    return out
 
 
 def last_error() -> str:

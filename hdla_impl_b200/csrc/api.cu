@@ -5,13 +5,45 @@
 #include <cstring>
 
 #include <atomic>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
 
 #include "common.cuh"
 
 namespace hdla {
 
 static std::atomic<unsigned long long> g_launches{0};
-void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+// ---- optional per-kernel timing (benchmark instrumentation) -------------------------------------
+// With timing on, an event is recorded on the call's stream at entry and after every launch; the
+// time between consecutive events of one call is attributed to the kernel launched in between.
+namespace {
+struct Mark { const char* name; cudaEvent_t ev; };
+std::mutex g_tmu;
+bool g_timing = false;
+std::vector<Mark> g_marks;
+thread_local cudaStream_t g_cur_stream = nullptr;
+
+void timing_mark(const char* name) {
+    std::lock_guard<std::mutex> lock(g_tmu);
+    if (!g_timing || g_marks.size() > (1u << 20)) return;
+    cudaEvent_t ev;
+    if (cudaEventCreate(&ev) != cudaSuccess) return;
+    cudaEventRecord(ev, g_cur_stream);
+    g_marks.push_back(Mark{name, ev});
+}
+}  // namespace
+
+void count_launch(const char* what) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (g_timing) timing_mark(what);
+}
+static void begin_call(void* stream) {
+    g_cur_stream = static_cast<cudaStream_t>(stream);
+    if (g_timing) timing_mark(nullptr);
+}
 
 static thread_local char g_err[512] = "";
 
@@ -56,6 +88,41 @@ const char* hdla_last_error(void) { return g_err; }
 
 unsigned long long hdla_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
 
+void hdla_timing_enable(int on) {
+    std::lock_guard<std::mutex> lock(g_tmu);
+    g_timing = on != 0;
+}
+
+size_t hdla_timing_report(char* buf, size_t size) {
+    std::lock_guard<std::mutex> lock(g_tmu);
+    std::map<std::string, std::pair<long long, double>> acc;
+    for (size_t i = 0; i < g_marks.size(); ++i) {
+        cudaEventSynchronize(g_marks[i].ev);
+        if (g_marks[i].name && i > 0) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, g_marks[i - 1].ev, g_marks[i].ev) == cudaSuccess) {
+                auto& e = acc[g_marks[i].name];
+                e.first += 1;
+                e.second += ms;
+            }
+        }
+    }
+    for (auto& m : g_marks) cudaEventDestroy(m.ev);
+    g_marks.clear();
+    std::string out;
+    for (auto& kv : acc) {
+        char line[256];
+        snprintf(line, sizeof(line), "%s %lld %.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
+        out += line;
+    }
+    if (buf && size) {
+        const size_t n = out.size() < size - 1 ? out.size() : size - 1;
+        memcpy(buf, out.data(), n);
+        buf[n] = 0;
+    }
+    return out.size();
+}
+
 // bf16 problems the tensor-core pipeline supports use its workspace plan, everything else the fp32 one.
 static size_t tc_region_bytes(const HdlaDims& d, int with_backward) {
     return tc_supported(d) ? tc_workspace_bytes(d, with_backward) : 0;
@@ -84,6 +151,7 @@ int hdla_chunk_fwd(const HdlaDims* dims, const void* q, const void* k, const voi
                    size_t workspace_bytes, void* cuda_stream) {
     int rc = check_common(dims, true);
     if (rc != HDLA_OK) return rc;
+    begin_call(cuda_stream);
     if (!q || !k || !v || !a || !b || !gk || !o) return fail(HDLA_ERR_INVALID, "chunk_fwd: null tensor pointer");
     rc = check_ws(dims, workspace, workspace_bytes, 0);
     if (rc != HDLA_OK) return rc;
@@ -100,6 +168,7 @@ int hdla_chunk_bwd(const HdlaDims* dims, const void* q, const void* k, const voi
                    void* cuda_stream) {
     int rc = check_common(dims, true);
     if (rc != HDLA_OK) return rc;
+    begin_call(cuda_stream);
     if (!q || !k || !v || !a || !b || !gk || !d_o || !dq || !dk || !dv || !da || !db || !dgk)
         return fail(HDLA_ERR_INVALID, "chunk_bwd: null tensor pointer");
     rc = check_ws(dims, workspace, workspace_bytes, 1);
@@ -116,6 +185,7 @@ int hdla_recurrent_fwd(const HdlaDims* dims, const void* q, const void* k, const
                        const int64_t* cu_seqlens, int32_t n_seqs, int32_t reverse, void* cuda_stream) {
     int rc = check_common(dims, false);
     if (rc != HDLA_OK) return rc;
+    begin_call(cuda_stream);
     if (!q || !k || !v || !a || !b || !gk || !o) return fail(HDLA_ERR_INVALID, "recurrent_fwd: null tensor pointer");
     return recurrent_fwd_launch(*dims, q, k, v, a, b, gk, scale, h0, o, ht, cu_seqlens, n_seqs, reverse,
                                 static_cast<cudaStream_t>(cuda_stream));

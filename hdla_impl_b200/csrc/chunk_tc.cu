@@ -171,35 +171,50 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
             hf[0] = .5f * l0.x; hf[1] = .5f * l0.y; hf[2] = .5f * l0.z; hf[3] = .5f * l0.w;
             hf[4] = .5f * l1.x; hf[5] = .5f * l1.y; hf[6] = .5f * l1.z; hf[7] = .5f * l1.w;
         }
+        // all seven input chunks first (independent loads in flight together), then the arithmetic and stores
         const size_t src = (((size_t)b * p.T + t0 + r) * p.H + h) * K + kc * 8;
-        float x[8], y[8], ep[8], em[8];
+        const size_t sa0 = (((size_t)b * p.T * R + (size_t)(t0 + r) * R) * p.H + h) * K + kc * 8;
+        const size_t sa1 = sa0 + (size_t)p.H * K;
+        uint4 rq = zero, rk = zero, rv = zero, ra0 = zero, ra1 = zero, rb0 = zero, rb1 = zero;
+        if (rowok) {
+            rq = __ldg(reinterpret_cast<const uint4*>(p.q + src));
+            rk = __ldg(reinterpret_cast<const uint4*>(p.k + src));
+            rv = __ldg(reinterpret_cast<const uint4*>(p.v + (((size_t)b * p.T + t0 + r) * p.H + h) * V + kc * 8));
+            ra0 = __ldg(reinterpret_cast<const uint4*>(p.a + sa0));
+            ra1 = __ldg(reinterpret_cast<const uint4*>(p.a + sa1));
+            rb0 = __ldg(reinterpret_cast<const uint4*>(p.b + sa0));
+            rb1 = __ldg(reinterpret_cast<const uint4*>(p.b + sa1));
+        }
+        float x[8], y[8], ep[8], em[8], ea[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { ep[j] = __expf(gi[j] - hf[j]); em[j] = __frcp_rn(ep[j]); }
-        t8::unpack8(rowok ? *reinterpret_cast<const uint4*>(p.q + src) : zero, x);
+        for (int j = 0; j < 8; ++j) {
+            ep[j] = __expf(gi[j] - hf[j]); em[j] = __frcp_rn(ep[j]); ea[j] = __expf(ge[j] - hf[j]);
+        }
+        t8::unpack8(rq, x);
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = x[j] * p.scale * ep[j];
         p.Qh[(size_t)g * CH64 + kc * 64 + r] = t8::pack8(y);
-        t8::unpack8(rowok ? *reinterpret_cast<const uint4*>(p.k + src) : zero, x);
+        t8::unpack8(rk, x);
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
         p.Kh[(size_t)g * CH64 + kc * 64 + r] = t8::pack8(y);
-        p.Vc[(size_t)g * CH64 + kc * 64 + r] =
-            rowok ? *reinterpret_cast<const uint4*>(p.v + (((size_t)b * p.T + t0 + r) * p.H + h) * V + kc * 8) : zero;
-        float ea[8];
+        p.Vc[(size_t)g * CH64 + kc * 64 + r] = rv;
+        t8::unpack8(ra0, x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ea[j] = __expf(ge[j] - hf[j]);
+        for (int j = 0; j < 8; ++j) y[j] = x[j] * ea[j];
+        p.Ah[(size_t)g * CH128 + kc * 128 + r * R] = t8::pack8(y);
+        t8::unpack8(ra1, x);
 #pragma unroll
-        for (int rr = 0; rr < R; ++rr) {
-            const size_t sa = (((size_t)b * p.T * R + (size_t)(t0 + r) * R + rr) * p.H + h) * K + kc * 8;
-            t8::unpack8(rowok ? *reinterpret_cast<const uint4*>(p.a + sa) : zero, x);
+        for (int j = 0; j < 8; ++j) y[j] = x[j] * ea[j];
+        p.Ah[(size_t)g * CH128 + kc * 128 + r * R + 1] = t8::pack8(y);
+        t8::unpack8(rb0, x);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) y[j] = x[j] * ea[j];
-            p.Ah[(size_t)g * CH128 + kc * 128 + r * R + rr] = t8::pack8(y);
-            t8::unpack8(rowok ? *reinterpret_cast<const uint4*>(p.b + sa) : zero, x);
+        for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
+        p.Bh[(size_t)g * CH128 + kc * 128 + r * R] = t8::pack8(y);
+        t8::unpack8(rb1, x);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
-            p.Bh[(size_t)g * CH128 + kc * 128 + r * R + rr] = t8::pack8(y);
-        }
+        for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
+        p.Bh[(size_t)g * CH128 + kc * 128 + r * R + 1] = t8::pack8(y);
         float4* gh = reinterpret_cast<float4*>(p.ghat + (size_t)g * C * K + (size_t)r * K + kc * 8);
         gh[0] = make_float4(gi[0] - hf[0], gi[1] - hf[1], gi[2] - hf[2], gi[3] - hf[3]);
         gh[1] = make_float4(gi[4] - hf[4], gi[5] - hf[5], gi[6] - hf[6], gi[7] - hf[7]);
@@ -1165,11 +1180,19 @@ __global__ void __launch_bounds__(288) grad_tc_kernel(GradP p) {
         const float* gh = reinterpret_cast<const float*>(sC);
         const float half = gh[(size_t)(C - 1) * K + k];
         const float dgl = p.dgl[(size_t)g * K + k];
-        const uint4 *tQh = sD, *tKh = sb, *tAh = sB, *tBh = sA;
+        // per-thread element pointers into the four hat tiles (token i sits 16 bytes after token i-1)
+        const __nv_bfloat16* eq = reinterpret_cast<const __nv_bfloat16*>(sD + (k >> 3) * 64) + (k & 7);
+        const __nv_bfloat16* ek = reinterpret_cast<const __nv_bfloat16*>(sb + (k >> 3) * 64) + (k & 7);
+        const __nv_bfloat16* ea = reinterpret_cast<const __nv_bfloat16*>(sB + (k >> 3) * 128) + (k & 7);
+        const __nv_bfloat16* eb = reinterpret_cast<const __nv_bfloat16*>(sA + (k >> 3) * 128) + (k & 7);
+        const size_t tok_stride = (size_t)p.H * K;                    // elements between tokens in [B,T,H,K]
+        const size_t base_qk = (((size_t)b * p.T + (size_t)n * C) * p.H + h) * K + k;
+        const size_t base_ab = (((size_t)b * p.T + (size_t)n * C) * R * p.H + h) * K + k;
         float run = 0.f;
         float* dgk_loc = reinterpret_cast<float*>(sE);    // [64][128] fp32 over the (consumed) dAab slot
         const int i_hi = wg == 0 ? 63 : 31;
         float ep = __expf(gh[(size_t)i_hi * K + k]);
+        const int t_left = p.T - n * C;                               // tokens of this chunk that exist
 #pragma unroll 1
         for (int ibl = 3; ibl >= 0; --ibl) {
             const int ib = (wg == 0 ? 4 : 0) + ibl;
@@ -1179,34 +1202,36 @@ __global__ void __launch_bounds__(288) grad_tc_kernel(GradP p) {
             tmem_ld_x16(t8::taddr(tmem, warp, 128 + ib * 16), va);
             tmem_ld_x16(t8::taddr(tmem, warp, 256 + ib * 16), vb);
             tmem_wait_ld();
+            const int i0 = ib * 8;
+            const __nv_bfloat16 *bq = eq + i0 * 8, *bk = ek + i0 * 8, *ba = ea + i0 * 16, *bb = eb + i0 * 16;
+            const float* bg = gh + (size_t)i0 * K + k;
+            float* bd = dgk_loc + (size_t)i0 * K + k;
+            __nv_bfloat16 *oq = p.dq + base_qk + (size_t)i0 * tok_stride, *ok_ = p.dk + base_qk + (size_t)i0 * tok_stride;
+            __nv_bfloat16 *oa = p.da + base_ab + (size_t)i0 * R * tok_stride, *ob = p.db + base_ab + (size_t)i0 * R * tok_stride;
 #pragma unroll
             for (int j = 7; j >= 0; --j) {
-                const int i = ib * 8 + j;
-                const int t = n * C + i;
-                const bool ok = t < p.T;
-                const float xe = i > 0 ? gh[(size_t)(i - 1) * K + k] : -half;      // ge - half
+                const bool ok = i0 + j < t_left;
+                const float xe = (i0 + j) > 0 ? bg[(j - 1) * K] : -half;           // ge - half
                 const float ee = __expf(xe);
                 const float em = __frcp_rn(ep);
                 const float dqh = __uint_as_float(vq[j]), dkh = __uint_as_float(vk[j]);
-                float d_gi = c8s(tQh, 64, i, k) * dqh - c8s(tKh, 64, i, k) * dkh;
+                float d_gi = __bfloat162float(bq[j * 8]) * dqh - __bfloat162float(bk[j * 8]) * dkh;
                 float d_ge = 0.f;
 #pragma unroll
                 for (int rr = 0; rr < R; ++rr) {
                     const float dah = __uint_as_float(va[2 * j + rr]), dbh = __uint_as_float(vb[2 * j + rr]);
-                    d_ge = fmaf(c8s(tAh, 128, i * R + rr, k), dah, d_ge);
-                    d_gi = fmaf(-c8s(tBh, 128, i * R + rr, k), dbh, d_gi);
+                    d_ge = fmaf(__bfloat162float(ba[(2 * j + rr) * 8]), dah, d_ge);
+                    d_gi = fmaf(-__bfloat162float(bb[(2 * j + rr) * 8]), dbh, d_gi);
                     if (ok) {
-                        const size_t oa = (((size_t)b * p.T * R + (size_t)t * R + rr) * p.H + h) * K + k;
-                        p.da[oa] = __float2bfloat16_rn(ee * dah);
-                        p.db[oa] = __float2bfloat16_rn(em * dbh);
+                        oa[(size_t)(2 * j + rr) * tok_stride] = __float2bfloat16_rn(ee * dah);
+                        ob[(size_t)(2 * j + rr) * tok_stride] = __float2bfloat16_rn(em * dbh);
                     }
                 }
                 run += d_gi + d_ge;
-                dgk_loc[i * K + k] = run - d_ge + dgl;
+                bd[j * K] = run - d_ge + dgl;
                 if (ok) {
-                    const size_t o = (((size_t)b * p.T + t) * p.H + h) * K + k;
-                    p.dq[o] = __float2bfloat16_rn(p.scale * ep * dqh);
-                    p.dk[o] = __float2bfloat16_rn(em * dkh);
+                    oq[(size_t)j * tok_stride] = __float2bfloat16_rn(p.scale * ep * dqh);
+                    ok_[(size_t)j * tok_stride] = __float2bfloat16_rn(em * dkh);
                 }
                 ep = ee;                                  // e^{ghat} of token i-1
             }

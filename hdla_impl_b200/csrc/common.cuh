@@ -11,12 +11,13 @@ namespace hdla {
 // Records a message for hdla_last_error() and returns `code`.
 int fail(int code, const char* fmt, ...);
 
-// Process-wide count of kernel launches (see hdla_kernel_launches()).
-void count_launch();
+// Process-wide count of kernel launches (see hdla_kernel_launches()); when kernel timing is on
+// (hdla_timing_enable) it also records a CUDA event after the launch on the call's stream.
+void count_launch(const char* what);
 
 #define HDLA_CHECK_LAUNCH(what)                                                       \
     do {                                                                              \
-        ::hdla::count_launch();                                                       \
+        ::hdla::count_launch(what);                                                   \
         cudaError_t e__ = cudaGetLastError();                                         \
         if (e__ != cudaSuccess)                                                       \
             return ::hdla::fail(HDLA_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e__)); \

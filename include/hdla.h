@@ -77,6 +77,13 @@ HDLA_API const char* hdla_last_error(void);
  * issued by the Triton runtime. */
 HDLA_API unsigned long long hdla_kernel_launches(void);
 
+/* Per-kernel timing for benchmarks (no counterpart in the reference).  While enabled, every call
+ * records a CUDA event on its stream at entry and after each kernel launch.  hdla_timing_report()
+ * WAITS for those events, writes one line "kernel_name launches total_ms" per kernel into buf (at most
+ * size-1 characters, NUL terminated), forgets the events and returns the length of the full report. */
+HDLA_API void hdla_timing_enable(int on);
+HDLA_API size_t hdla_timing_report(char* buf, size_t size);
+
 /* Bytes of device workspace hdla_chunk_fwd (with_backward = 0) or the pair hdla_chunk_fwd +
  * hdla_chunk_bwd (with_backward = 1) needs for these dims; 0 if the dims are unsupported (see
  * hdla_last_error).  Replaces the torch.empty(...) intermediates the reference's stage
