@@ -211,20 +211,31 @@ def run_ours(args, rank, world, local_rank):
     elt = 2 if dt == "bf16" else 4
 
     # this rank's units
-    if args.scaling == "strong" and world > 1:
+    cp = args.workload == "cfg3" and world > 1           # long context: shard T, exchange boundary states
+    if cp:
+        args.scaling = "strong"
+    Tl = T // world if cp else T
+    if cp:
+        Bl, Hl = B, H
+    elif args.scaling == "strong" and world > 1:
         b_lo, b_hi, h_lo, h_hi = shard_batch_heads(B, H, rank, world)
         Bl, Hl = b_hi - b_lo, h_hi - h_lo
     else:
         Bl, Hl = B, H
-    x = make_inputs(Bl, T, Hl, K, V, R, seed=rank, dtype=dtype)
+    x = make_inputs(Bl, Tl, Hl, K, V, R, seed=rank, dtype=dtype)
     names = ("q", "k", "v", "a", "b", "gk")
     host = {n: x[n].pin_memory() for n in names + ("do",)}
     dev_in = {n: host[n].to(dev) for n in host}
     leaves = [dev_in[n].requires_grad_(True) for n in names]
     scale = K ** -0.5
 
+    from hdla_impl_b200.context_parallel import cp_chunk_hrdplr_delta_rule
+
     def step(lv, do):
-        o, _ = HD.chunk_hrdplr_delta_rule(*lv, R, scale=scale, chunk_size=C)
+        if cp:
+            o, _ = cp_chunk_hrdplr_delta_rule(*lv, R, scale=scale, chunk_size=C)
+        else:
+            o, _ = HD.chunk_hrdplr_delta_rule(*lv, R, scale=scale, chunk_size=C)
         grads = torch.autograd.grad(o, lv, do)
         return o, grads
 
@@ -251,20 +262,26 @@ def run_ours(args, rank, world, local_rank):
     ms = e0.elapsed_time(e1)
     # per-kernel durations, live: the library brackets every launch with CUDA events on its stream
     ktimes = {}
-    if rank == 0:
-        _lib.timing_enable(True)
+    if rank == 0 or cp:                                  # with context parallelism every step is collective
+        if rank == 0:
+            _lib.timing_enable(True)
         for _ in range(3):
             step(leaves, dev_in["do"])
         torch.cuda.synchronize(dev)
-        _lib.timing_enable(False)
-        ktimes = _lib.timing_report()
-    if rank == 0:
+        if rank == 0:
+            _lib.timing_enable(False)
+            ktimes = _lib.timing_report()
+    if rank == 0 and not cp:
         # the timed region can be shorter than nvidia-smi's sampling period: keep the same load running
         # (untimed) until a few samples exist, so the clocks reported are clocks under this load
         t_end = time.time() + 5.0
         while len(sampler.rows) < 5 and time.time() < t_end:
             step(leaves, dev_in["do"])
             torch.cuda.synchronize(dev)
+    elif cp:
+        for _ in range(20):                              # same number of collective steps on every rank
+            step(leaves, dev_in["do"])
+        torch.cuda.synchronize(dev)
     clocks = sampler.stop() if rank == 0 else None
 
     # end to end: pinned host buffers in, host buffers out
@@ -320,7 +337,7 @@ def run_ours(args, rank, world, local_rank):
                     "algorithmic_bytes": byts},
         }
         if ktimes and dt == "bf16":
-            G = (B if args.scaling == "weak" else B // world) * H * ((T + C - 1) // C)
+            G = (B if (args.scaling == "weak" or cp) else B // world) * H * ((Tl + C - 1) // C)
             tot = sum(v[1] for v in ktimes.values())
             table = {}
             for name, (cnt, tms) in sorted(ktimes.items(), key=lambda kv: -kv[1][1]):
@@ -350,11 +367,14 @@ def run_ours(args, rank, world, local_rank):
                    "sample": f"B=1 T={T_s} of {args.workload} (H={H} K={K} V={V} chunk {C}) fp32, one pass, "
                              f"{sec_cpu:.1f} s"}
         line = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
+            "metric": METRIC if args.workload == "cfg1" else
+            f"HDLA fwd+bwd tokens/s (B{B} T{T} H{H} D{K} {dt})", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": dt, "data": "synthetic",
             "config": {"workload": args.workload, "B_per_step": B * (world if args.scaling == "weak" else 1), "T": T,
-                       "H": H, "K": K, "V": V, "R": R, "chunk": C, "sharding": "batch x head, no collective",
+                       "H": H, "K": K, "V": V, "R": R, "chunk": C,
+                       "sharding": ("context parallel: T/N per rank, all-gather of affine state maps (NCCL)" if cp
+                                    else "batch x head, no collective"),
                        "backward": "saved forward intermediates" if HD.hrdplr.save_workspace_default() else "recompute",
                        "l2": "inputs (>1 GB per step) are larger than the 126 MB L2"},
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

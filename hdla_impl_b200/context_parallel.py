@@ -7,8 +7,10 @@ with ``initial_state = S`` and sends its final state to r+1; in backward the sta
 the other way.  The exchange is point-to-point (``torch.distributed`` send/recv: NCCL over NVLink
 on GPUs, gloo on CPU for tests); the received state lands in local memory before any kernel reads it.
 
-The pieces are autograd functions, so the local operator in between is the ordinary
-``chunk_hrdplr_delta_rule`` (or, in CPU tests, the oracle).
+Two forms are provided.  The generic one strings autograd send/recv functions around the ordinary
+local operator (any ``op``; used on CPU with the oracle): rank r waits for rank r-1.  The fused one
+(``_CPChunkFunction``, bf16 CUDA path) uses the library's phased calls so that all ranks scan at the
+same time and exchange one all-gather of affine state maps per direction.
 """
 from __future__ import annotations
 
@@ -79,6 +81,117 @@ class _Attach(torch.autograd.Function):
         return go, torch.zeros(ctx.shape, dtype=ctx.dtype, device=ctx.device)
 
 
+class _CPChunkFunction(torch.autograd.Function):
+    """Context-parallel chunked operator on the CUDA library, with the scans of all ranks running
+    concurrently.
+
+    The state leaving a rank is affine in the state entering it, ``S_out = T S_in + F``: ``T`` is the
+    product of the chunk transition matrices (one scan of a K x K identity, ``HDLA_PHASE_TRANSITION``)
+    and ``F`` the state reached from zero (``HDLA_PHASE_STATE``).  Every rank computes its ``(T, F)``
+    at the same time, one all-gather distributes them, each rank composes the state entering its slice
+    locally and only then runs the real scan (``HDLA_PHASE_POST``).  Backward is the mirror image with
+    ``T^T``.  Per rank the scan work is three passes over T/world chunks instead of one pass over T.
+    """
+
+    @staticmethod
+    def forward(ctx, q, k, v, a, b, gk, scale, initial_state, RANK_AB, chunk_size, group):
+        import ctypes as C
+        from . import _lib
+        from .hrdplr import _alloc_ws, _dims, _post_status, check_status, workspace_bytes
+        q, k, v, a, b, gk = (t.contiguous() for t in (q, k, v, a, b, gk))
+        dev = q.device
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        B, T, H, K = q.shape
+        V = v.shape[-1]
+        lib = _lib.load()
+        check_status(dev)
+        mk = lambda phase, extra=0: _dims(q, v, a, gk, RANK_AB, chunk_size, phase | extra)
+        ws = _alloc_ws(workspace_bytes(mk(0), True), dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+
+        def fwd(phase, h0, o, ht):
+            d = mk(phase)
+            rc = lib.hdla_chunk_fwd(C.byref(d), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(a), _lib.ptr(b),
+                                    _lib.ptr(gk), float(scale), _lib.ptr(h0), _lib.ptr(o), _lib.ptr(ht), _lib.ptr(ws),
+                                    ws.numel(), _lib.stream_ptr(dev))
+            _lib.check(rc, "hdla_chunk_fwd")
+
+        with torch.cuda.device(dev):
+            fwd(_lib.PHASE_PRE, None, None, None)
+            Tr = torch.empty(B, H, K, K, **f32)
+            Fr = torch.empty(B, H, K, V, **f32)
+            fwd(_lib.PHASE_TRANSITION, None, None, Tr)
+            fwd(_lib.PHASE_STATE, None, None, Fr)
+            Ts = [torch.empty_like(Tr) for _ in range(world)]
+            Fs = [torch.empty_like(Fr) for _ in range(world)]
+            dist.all_gather(Ts, Tr, group=group)
+            dist.all_gather(Fs, Fr, group=group)
+            S = torch.zeros(B, H, K, V, **f32) if initial_state is None else initial_state.to(torch.float32).clone()
+            src0 = dist.get_global_rank(group, 0) if group is not None else 0
+            if initial_state is not None or world > 1:
+                dist.broadcast(S, src=src0, group=group)           # the initial state lives on rank 0
+            for j in range(rank):
+                S = torch.matmul(Ts[j], S) + Fs[j]
+            o = torch.empty_like(v)
+            ht = torch.empty(B, H, K, V, **f32)
+            fwd(_lib.PHASE_POST, S, o, ht)
+            _post_status(ws, dev)
+        ctx.save_for_backward(q, k, v, a, b, gk, S, *Ts)
+        ctx.ws, ctx.scale, ctx.R, ctx.chunk, ctx.group = ws, scale, RANK_AB, chunk_size, group
+        ctx.has_h0 = initial_state is not None
+        return o, ht
+
+    @staticmethod
+    def backward(ctx, do, dht):
+        import ctypes as C
+        from . import _lib
+        from .hrdplr import _dims, check_status
+        q, k, v, a, b, gk, S_in, *Ts = ctx.saved_tensors
+        group = ctx.group
+        dev = q.device
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        B, T, H, K = q.shape
+        V = v.shape[-1]
+        lib = _lib.load()
+        check_status(dev)
+        ws = ctx.ws
+        ctx.ws = None
+        do = do.contiguous().to(q.dtype)
+        f32 = dict(dtype=torch.float32, device=dev)
+        grads = [torch.empty_like(t) for t in (q, k, v, a, b, gk)]
+
+        def bwd(phase, dht_, dh0_, with_grads):
+            d = _dims(q, v, a, gk, ctx.R, ctx.chunk, phase | _lib.FLAG_WS_HOLDS_FWD)
+            g = [_lib.ptr(t) for t in grads] if with_grads else [None] * 6
+            rc = lib.hdla_chunk_bwd(C.byref(d), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(a), _lib.ptr(b),
+                                    _lib.ptr(gk), float(ctx.scale), _lib.ptr(S_in), _lib.ptr(do), _lib.ptr(dht_),
+                                    *g, _lib.ptr(dh0_), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
+            _lib.check(rc, "hdla_chunk_bwd")
+
+        with torch.cuda.device(dev):
+            bwd(_lib.PHASE_PRE, None, None, False)
+            Gr = torch.empty(B, H, K, V, **f32)
+            bwd(_lib.PHASE_STATE, None, Gr, False)
+            Gs = [torch.empty_like(Gr) for _ in range(world)]
+            dist.all_gather(Gs, Gr, group=group)
+            D = torch.zeros(B, H, K, V, **f32)
+            if rank == world - 1 and dht is not None:
+                D = dht.to(torch.float32).contiguous().clone()
+            last = dist.get_global_rank(group, world - 1) if group is not None else world - 1
+            dist.broadcast(D, src=last, group=group)               # gradient of the sequence's final state
+            for j in range(world - 1, rank, -1):
+                D = torch.matmul(Ts[j].transpose(-1, -2), D) + Gs[j]
+            dh0 = torch.empty(B, H, K, V, **f32)
+            bwd(_lib.PHASE_POST, D, dh0, True)
+        dq, dk, dv, da, db, dgk = grads
+        return dq, dk, dv, da, db, dgk, None, (dh0 if ctx.has_h0 else None), None, None, None
+
+
+def _fused_supported(q, v, gk, RANK_AB, chunk_size) -> bool:
+    return (q.is_cuda and q.dtype == torch.bfloat16 and RANK_AB == 2 and q.shape[-1] == 128 and v.shape[-1] == 128
+            and chunk_size >= 64 and q.shape[1] >= 64)
+
+
 def cp_chunk_hrdplr_delta_rule(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, b: torch.Tensor, gk: torch.Tensor,
     RANK_AB: int, scale: Optional[float] = None, initial_state: Optional[torch.Tensor] = None,
@@ -92,6 +205,10 @@ def cp_chunk_hrdplr_delta_rule(
     ``final_state`` is the state after this rank's slice (the sequence's final state on the last
     rank).  ``op`` is the local operator with the signature of ``chunk_hrdplr_delta_rule``; it
     defaults to the CUDA operator of this package."""
+    if op is None and _fused_supported(q, v, gk, RANK_AB, chunk_size) and chunk_size == 64:
+        scale_ = q.shape[-1] ** -0.5 if scale is None else scale
+        o, ht = _CPChunkFunction.apply(q, k, v, a, b, gk, scale_, initial_state, RANK_AB, chunk_size, group)
+        return o, (ht if output_final_state else None)
     if op is None:
         from .hrdplr import chunk_hrdplr_delta_rule as op
     B, _, H, K = q.shape

@@ -152,9 +152,14 @@ int hdla_chunk_fwd(const HdlaDims* dims, const void* q, const void* k, const voi
     int rc = check_common(dims, true);
     if (rc != HDLA_OK) return rc;
     begin_call(cuda_stream);
-    if (!q || !k || !v || !a || !b || !gk || !o) return fail(HDLA_ERR_INVALID, "chunk_fwd: null tensor pointer");
-    rc = check_ws(dims, workspace, workspace_bytes, 0);
+    const int phase = dims->flags & HDLA_PHASE_MASK;
+    const bool needs_o = phase == HDLA_PHASE_ALL || phase == HDLA_PHASE_POST;
+    if (!q || !k || !v || !a || !b || !gk || (needs_o && !o))
+        return fail(HDLA_ERR_INVALID, "chunk_fwd: null tensor pointer");
+    rc = check_ws(dims, workspace, workspace_bytes, phase == HDLA_PHASE_ALL ? 0 : 1);
     if (rc != HDLA_OK) return rc;
+    if (phase != HDLA_PHASE_ALL && !tc_supported(*dims))
+        return fail(HDLA_ERR_UNSUPPORTED, "phased calls need the bf16 tensor-core pipeline (bf16, chunk 64, R=2, K=V=128)");
     if (tc_supported(*dims))
         return tc_chunk_fwd(*dims, q, k, v, a, b, gk, scale, h0, o, ht, static_cast<unsigned char*>(workspace), true,
                             static_cast<cudaStream_t>(cuda_stream));
@@ -169,10 +174,15 @@ int hdla_chunk_bwd(const HdlaDims* dims, const void* q, const void* k, const voi
     int rc = check_common(dims, true);
     if (rc != HDLA_OK) return rc;
     begin_call(cuda_stream);
-    if (!q || !k || !v || !a || !b || !gk || !d_o || !dq || !dk || !dv || !da || !db || !dgk)
+    const int phase = dims->flags & HDLA_PHASE_MASK;
+    const bool needs_grads = phase == HDLA_PHASE_ALL || phase == HDLA_PHASE_POST;
+    if (!q || !k || !v || !a || !b || !gk || (phase != HDLA_PHASE_STATE && !d_o) ||
+        (needs_grads && (!dq || !dk || !dv || !da || !db || !dgk)))
         return fail(HDLA_ERR_INVALID, "chunk_bwd: null tensor pointer");
     rc = check_ws(dims, workspace, workspace_bytes, 1);
     if (rc != HDLA_OK) return rc;
+    if (phase != HDLA_PHASE_ALL && !tc_supported(*dims))
+        return fail(HDLA_ERR_UNSUPPORTED, "phased calls need the bf16 tensor-core pipeline (bf16, chunk 64, R=2, K=V=128)");
     if (tc_supported(*dims))
         return tc_chunk_bwd(*dims, q, k, v, a, b, gk, scale, h0, d_o, dht, dq, dk, dv, da, db, dgk, dh0,
                             static_cast<unsigned char*>(workspace), static_cast<cudaStream_t>(cuda_stream));

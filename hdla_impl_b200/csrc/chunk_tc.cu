@@ -33,7 +33,7 @@ constexpr int CH128 = 16 * 128;    // chunks of a [128 x 128] tile
 struct TcPlan {
     int B, T, H, NT, BH;
     long long G;
-    size_t status, Qh, Kh, Ah, Bh, Vc, E, ghat, Aqk, Aqb, Aak, Aab, M, W, P, U, Hs, V2, HT;
+    size_t status, Qh, Kh, Ah, Bh, Vc, E, ghat, Aqk, Aqb, Aak, Aab, M, W, P, U, Hs, V2, HT, zero;
     size_t dOc, dAqk, dAqb, DV2, DE, dgl, dW, dP, dAak, dM, tmp, dAab, dQh, dKh, dAh, dBh;
     size_t total_fwd, total;
 };
@@ -56,6 +56,7 @@ TcPlan make_tc_plan(const HdlaDims& d) {
     p.Aqk = take(8192); p.Aqb = take(16384); p.Aak = take(16384); p.Aab = take(32768); p.M = take(32768);
     p.W = take(32768); p.P = take(32768); p.U = take(32768); p.Hs = take(32768); p.V2 = take(32768);
     p.HT = off; off += (((size_t)p.BH * K * V * 4 + 255) / 256) * 256;
+    p.zero = off; off += 32768;
     p.total_fwd = off;
     p.dOc = take(16384); p.dAqk = take(8192); p.dAqb = take(16384); p.DV2 = take(32768); p.DE = take(32768);
     p.dgl = take(K * 4); p.dW = take(32768); p.dP = take(32768); p.dAak = take(16384); p.dM = take(32768);
@@ -544,6 +545,9 @@ struct ScanTcP {
     float* dgl;                              // rev only
     int NT, reverse;
     int* status;
+    int add_stride, r1_stride;               // chunk strides of ADD / R1 in tiles: 1, or 0 for one shared (zero) tile
+    int no_store;                            // 1: do not write CK, Y, dgl (state-only passes)
+    int init_identity;                       // 1: start from the K x K identity (transition pass, needs K == V)
 };
 
 __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
@@ -570,14 +574,17 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         mbar_init(&ldA, 1); mbar_init(&ldB, 1); mbar_init(&barA, 1); mbar_init(&barB, 1); fence_mbar_init();
         mbar_expect_tx(&ldA, 65536);
         bulk_g2s(sA1, p.A1 + g * CH128, 32768, &ldA);
-        bulk_g2s(sADD, p.ADD + g * CH128, 32768, &ldA);
+        bulk_g2s(sADD, p.ADD + g * p.add_stride * CH128, 32768, &ldA);
         mbar_expect_tx(&ldB, 65536);
         bulk_g2s(sL1, p.L1 + g * CH64, 16384, &ldB);
-        bulk_g2s(sR1, p.R1 + g * CH64, 16384, &ldB);
+        bulk_g2s(sR1, p.R1 + g * p.r1_stride * CH64, 16384, &ldB);
         bulk_g2s(sL2, p.L2 + g * CH128, 32768, &ldB);
     }
     float S[64];
-    if (p.init) {
+    if (p.init_identity) {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) S[j] = (half * 64 + j == row) ? 1.f : 0.f;
+    } else if (p.init) {
         const float4* src = reinterpret_cast<const float4*>(p.init + ((size_t)bh * K + row) * V + half * 64);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -601,7 +608,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         const bool more = it + 1 < p.NT;
         const float e = p.E[(size_t)g * K + row];
         float part = 0.f;
-        if (p.reverse) {                      // dgl = rowsum(dS (.) S_{n+1})
+        if (p.reverse && !p.no_store) {       // dgl = rowsum(dS (.) S_{n+1})
             if (n + 1 < p.NT) {
                 const float inv = 1.f / p.E[(size_t)(g + 1) * K + row];
 #pragma unroll
@@ -631,12 +638,12 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
             const uint4 c = t8::pack8(f);
             const int cg = half * 8 + c8;
             sT[cg * 128 + row] = c;
-            p.CK[g * CH128 + cg * 128 + row] = c;
+            if (!p.no_store) p.CK[g * CH128 + cg * 128 + row] = c;
         }
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        if (p.reverse && half == 0) p.dgl[(size_t)g * K + row] = part + red[row];
+        if (p.reverse && !p.no_store && half == 0) p.dgl[(size_t)g * K + row] = part + red[row];
         if (tid == 0) {
             wait_or_flag(&ldA, ph, p.status, 11);
             tc_fence_after();
@@ -657,7 +664,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
             for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]) + u[j];
             const uint4 c = t8::pack8(f);
             sY[cg * 128 + row] = c;
-            p.Y[g * CH128 + cg * 128 + row] = c;
+            if (!p.no_store) p.Y[g * CH128 + cg * 128 + row] = c;
         }
         fence_proxy_async();
         tc_fence_before();
@@ -666,7 +673,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
             if (more) {                                // A1 and ADD buffers are free: prefetch the next chunk's
                 mbar_expect_tx(&ldA, 65536);
                 bulk_g2s(sA1, p.A1 + (g + dn) * CH128, 32768, &ldA);
-                bulk_g2s(sADD, p.ADD + (g + dn) * CH128, 32768, &ldA);
+                bulk_g2s(sADD, p.ADD + (g + dn) * p.add_stride * CH128, 32768, &ldA);
             }
             wait_or_flag(&ldB, ph, p.status, 14);
             tc_fence_after();
@@ -679,7 +686,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         if (tid == 0 && more) {
             mbar_expect_tx(&ldB, 65536);
             bulk_g2s(sL1, p.L1 + (g + dn) * CH64, 16384, &ldB);
-            bulk_g2s(sR1, p.R1 + (g + dn) * CH64, 16384, &ldB);
+            bulk_g2s(sR1, p.R1 + (g + dn) * p.r1_stride * CH64, 16384, &ldB);
             bulk_g2s(sL2, p.L2 + (g + dn) * CH128, 32768, &ldB);
         }
 #pragma unroll
@@ -1309,25 +1316,46 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     int* status = reinterpret_cast<int*>(ws + pl.status);
     const unsigned G = (unsigned)pl.G;
     typedef const __nv_bfloat16* bp;
-    PrepP pp{(bp)q, (bp)k, (bp)v, (bp)a, (bp)b, gk, U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc), F(pl.E),
-             F(pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status};
-    {
+    const int phase = d.flags & HDLA_PHASE_MASK;
+    if (phase == HDLA_PHASE_ALL || phase == HDLA_PHASE_PRE) {
         cudaError_t e = cudaMemsetAsync(ws + pl.status, 0, 256, st);
-        if (e != cudaSuccess) return fail(HDLA_ERR_CUDA, "status clear: %s", cudaGetErrorString(e));
+        if (e == cudaSuccess) e = cudaMemsetAsync(ws + pl.zero, 0, 32768, st);
+        if (e != cudaSuccess) return fail(HDLA_ERR_CUDA, "workspace clear: %s", cudaGetErrorString(e));
+        PrepP pp{(bp)q, (bp)k, (bp)v, (bp)a, (bp)b, gk, U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc),
+                 F(pl.E), F(pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status};
+        prep_hat_kernel<<<G, 128, 0, st>>>(pp);
+        HDLA_CHECK_LAUNCH("prep_hat_kernel");
+        GramP gp{U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Aak), U4(pl.Aab), status};
+        gram_tc_kernel<<<G, 128, 98304 + 1024, st>>>(gp);
+        HDLA_CHECK_LAUNCH("gram_tc_kernel");
+        InvP ivp{U4(pl.Aab), U4(pl.M), status};
+        inverse_tc_kernel<<<G, 128, 98304, st>>>(ivp);
+        HDLA_CHECK_LAUNCH("inverse_tc_kernel");
+        WuP wp{U4(pl.M), U4(pl.Ah), U4(pl.Aak), U4(pl.Vc), U4(pl.P), U4(pl.U), U4(pl.W), status};
+        wu_tc_kernel<<<G, 128, 98304, st>>>(wp);
+        HDLA_CHECK_LAUNCH("wu_tc_kernel");
+        if (phase == HDLA_PHASE_PRE) return HDLA_OK;
     }
-    prep_hat_kernel<<<G, 128, 0, st>>>(pp);
-    HDLA_CHECK_LAUNCH("prep_hat_kernel");
-    GramP gp{U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Aak), U4(pl.Aab), status};
-    gram_tc_kernel<<<G, 128, 98304 + 1024, st>>>(gp);
-    HDLA_CHECK_LAUNCH("gram_tc_kernel");
-    InvP ivp{U4(pl.Aab), U4(pl.M), status};
-    inverse_tc_kernel<<<G, 128, 98304, st>>>(ivp);
-    HDLA_CHECK_LAUNCH("inverse_tc_kernel");
-    WuP wp{U4(pl.M), U4(pl.Ah), U4(pl.Aak), U4(pl.Vc), U4(pl.P), U4(pl.U), U4(pl.W), status};
-    wu_tc_kernel<<<G, 128, 98304, st>>>(wp);
-    HDLA_CHECK_LAUNCH("wu_tc_kernel");
+    if (phase == HDLA_PHASE_TRANSITION) {
+        // chunk transition matrices composed over this call's chunks: state K x K from the identity,
+        // no inputs (u = 0, v = 0):  X <- E (.) (I + Bh^T Wh) (E (.) X)
+        if (!ht) return fail(HDLA_ERR_INVALID, "transition pass needs the output pointer (ht)");
+        ScanTcP sp{U4(pl.W), U4(pl.zero), U4(pl.Kh), U4(pl.zero), U4(pl.Bh), F(pl.E), nullptr, nullptr, nullptr, ht,
+                   nullptr, nullptr, nullptr, nullptr, pl.NT, 0, status, 0, 0, 1, 1};
+        scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+        return HDLA_OK;
+    }
+    if (phase == HDLA_PHASE_STATE) {
+        if (!ht) return fail(HDLA_ERR_INVALID, "state pass needs the output pointer (ht)");
+        ScanTcP sp{U4(pl.W), U4(pl.U), U4(pl.Kh), U4(pl.Vc), U4(pl.Bh), F(pl.E), h0, nullptr, nullptr, ht, nullptr,
+                   nullptr, nullptr, nullptr, pl.NT, 0, status, 1, 1, 1, 0};
+        scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+        return HDLA_OK;
+    }
     ScanTcP sp{U4(pl.W), U4(pl.U), U4(pl.Kh), U4(pl.Vc), U4(pl.Bh), F(pl.E), h0, U4(pl.Hs), U4(pl.V2), ht, F(pl.HT),
-               nullptr, nullptr, nullptr, pl.NT, 0, status};
+               nullptr, nullptr, nullptr, pl.NT, 0, status, 1, 1, 0, 0};
     scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
     HDLA_CHECK_LAUNCH("scan_tc_kernel");
     if (need_o) {
@@ -1342,8 +1370,14 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
 int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a, const void* b,
                  const void* gk, float scale, const float* h0, const void* d_o, const float* dht, void* dq, void* dk,
                  void* dv, void* da, void* db, void* dgk, float* dh0, unsigned char* ws, cudaStream_t st) {
-    if (!(d.flags & HDLA_FLAG_WS_HOLDS_FWD))
-        TRY(tc_chunk_fwd(d, q, k, v, a, b, gk, scale, h0, nullptr, nullptr, ws, false, st));
+    const int phase = d.flags & HDLA_PHASE_MASK;
+    if (phase != HDLA_PHASE_ALL && !(d.flags & HDLA_FLAG_WS_HOLDS_FWD))
+        return fail(HDLA_ERR_INVALID, "phased backward calls need HDLA_FLAG_WS_HOLDS_FWD");
+    if (!(d.flags & HDLA_FLAG_WS_HOLDS_FWD)) {
+        HdlaDims df = d;
+        df.flags &= ~HDLA_PHASE_MASK;
+        TRY(tc_chunk_fwd(df, q, k, v, a, b, gk, scale, h0, nullptr, nullptr, ws, false, st));
+    }
     const TcPlan pl = make_tc_plan(d);
     auto U4 = [&](size_t off) { return reinterpret_cast<uint4*>(ws + off); };
     auto F = [&](size_t off) { return reinterpret_cast<float*>(ws + off); };
@@ -1351,14 +1385,26 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     const unsigned G = (unsigned)pl.G;
     typedef __nv_bfloat16* bp;
 
-    DauP dp{(const __nv_bfloat16*)d_o, U4(pl.Vc), U4(pl.V2), U4(pl.Aqb), U4(pl.dOc), U4(pl.dAqk), U4(pl.dAqb), U4(pl.DV2),
-            d.T, d.H, pl.NT, status};
-    dau_tc_kernel<<<G, 128, 81920, st>>>(dp);
-    HDLA_CHECK_LAUNCH("dau_tc_kernel");
-
+    if (phase == HDLA_PHASE_ALL || phase == HDLA_PHASE_PRE) {
+        DauP dp{(const __nv_bfloat16*)d_o, U4(pl.Vc), U4(pl.V2), U4(pl.Aqb), U4(pl.dOc), U4(pl.dAqk), U4(pl.dAqb),
+                U4(pl.DV2), d.T, d.H, pl.NT, status};
+        dau_tc_kernel<<<G, 128, 81920, st>>>(dp);
+        HDLA_CHECK_LAUNCH("dau_tc_kernel");
+        if (phase == HDLA_PHASE_PRE) return HDLA_OK;
+    }
+    if (phase == HDLA_PHASE_TRANSITION) return fail(HDLA_ERR_INVALID, "the transition pass belongs to the forward call");
+    if (phase == HDLA_PHASE_STATE) {
+        // state gradient leaving this call's first chunk for the given incoming dht; nothing is stored
+        if (!dh0) return fail(HDLA_ERR_INVALID, "state pass needs the output pointer (dh0)");
+        ScanTcP sp{U4(pl.Bh), U4(pl.DV2), U4(pl.Qh), U4(pl.dOc), U4(pl.W), F(pl.E), dht, nullptr, nullptr, dh0, nullptr,
+                   U4(pl.Hs), F(pl.HT), nullptr, pl.NT, 1, status, 1, 1, 1, 0};
+        scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+        return HDLA_OK;
+    }
     // --- dhu: reverse scan (dv2 is accumulated in place over dv2_intra)
     ScanTcP sp{U4(pl.Bh), U4(pl.DV2), U4(pl.Qh), U4(pl.dOc), U4(pl.W), F(pl.E), dht, U4(pl.DE), U4(pl.DV2), dh0, nullptr,
-               U4(pl.Hs), F(pl.HT), F(pl.dgl), pl.NT, 1, status};
+               U4(pl.Hs), F(pl.HT), F(pl.dgl), pl.NT, 1, status, 1, 1, 0, 0};
     scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
     HDLA_CHECK_LAUNCH("scan_tc_kernel");
     // --- wy: dWh, dP, dAak, dAab in one kernel

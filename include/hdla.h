@@ -51,6 +51,26 @@ extern "C" {
                                        left there for the same inputs -> skip the recomputation  */
 #define HDLA_FLAG_FORCE_SIMT    2   /* use the fp32 CUDA-core pipeline even for bf16 inputs       */
 
+/* Phase selector (bits 4..7 of HdlaDims.flags), for callers that split a sequence over devices
+ * (context parallelism).  Only the inter-chunk scan depends on the incoming state, so a call can be cut:
+ *   PHASE_ALL         the whole forward / backward (default)
+ *   PHASE_PRE         forward: everything before the scan;  backward: the stage before the reverse scan
+ *   PHASE_TRANSITION  forward only: ht <- product of the chunk transition matrices [B,H,K,K] (needs K == V);
+ *                     the state after this call is  ht_transition * S_in + (state pass from S_in = 0),
+ *                     the state gradient before it  ht_transition^T * dS_out + (state pass from dS_out = 0)
+ *   PHASE_STATE       forward: ht <- state after this call's chunks from h0, nothing else written;
+ *                     backward: dh0 <- state gradient entering this call's first chunk from dht
+ *   PHASE_POST        forward: scan + output;  backward: reverse scan + all gradients
+ * Phased calls use one workspace (sized with_backward = 1) across all phases; backward phases need
+ * HDLA_FLAG_WS_HOLDS_FWD.  The bf16 tensor-core pipeline implements them; other problems report
+ * HDLA_ERR_UNSUPPORTED. */
+#define HDLA_PHASE_MASK        0xF0
+#define HDLA_PHASE_ALL         0x00
+#define HDLA_PHASE_PRE         0x10
+#define HDLA_PHASE_TRANSITION  0x20
+#define HDLA_PHASE_STATE       0x30
+#define HDLA_PHASE_POST        0x40
+
 typedef struct HdlaDims {
     int32_t B;         /* batch (sequences)                                   */
     int32_t T;         /* tokens per sequence                                 */
