@@ -653,18 +653,20 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         wait_or_flag(&barA, ph, p.status, 12);
         wait_or_flag(&ldA, ph, p.status, 13);         // ADD is read from shared memory below
         tc_fence_after();
+        {
+            float acc[64];
+            tmem_row64(t8::taddr(tmem, warp, half * 64), acc);
 #pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-            const int cg = half * 8 + c8;
-            uint32_t v[8]; float f[8], u[8];
-            tmem_ld_x8(t8::taddr(tmem, warp, cg * 8), v);
-            t8::unpack8(sADD[cg * 128 + row], u);
-            tmem_wait_ld();
+            for (int c8 = 0; c8 < 8; ++c8) {
+                const int cg = half * 8 + c8;
+                float u[8];
+                t8::unpack8(sADD[cg * 128 + row], u);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]) + u[j];
-            const uint4 c = t8::pack8(f);
-            sY[cg * 128 + row] = c;
-            if (!p.no_store) p.Y[g * CH128 + cg * 128 + row] = c;
+                for (int j = 0; j < 8; ++j) u[j] += acc[c8 * 8 + j];
+                const uint4 c = t8::pack8(u);
+                sY[cg * 128 + row] = c;
+                if (!p.no_store) p.Y[g * CH128 + cg * 128 + row] = c;
+            }
         }
         fence_proxy_async();
         tc_fence_before();
@@ -689,13 +691,11 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
             bulk_g2s(sR1, p.R1 + (g + dn) * p.r1_stride * CH64, 16384, &ldB);
             bulk_g2s(sL2, p.L2 + (g + dn) * CH128, 32768, &ldB);
         }
+        {
+            float acc[64];
+            tmem_row64(t8::taddr(tmem, warp, 128 + half * 64), acc);
 #pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-            uint32_t v[8];
-            tmem_ld_x8(t8::taddr(tmem, warp, 128 + (half * 8 + c8) * 8), v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 8; ++j) S[c8 * 8 + j] = e * fmaf(e, S[c8 * 8 + j], __uint_as_float(v[j]));
+            for (int j = 0; j < 64; ++j) S[j] = e * fmaf(e, S[j], acc[j]);
         }
         tc_fence_before();
     }
@@ -725,16 +725,6 @@ struct WyBwdP {
     uint4 *dW, *dP, *dAak, *dAab;
     int* status;
 };
-
-// 64 accumulator columns of this thread's row -> registers (two 32-column loads, one wait)
-__device__ __forceinline__ void tmem_row64(uint32_t addr, float* f) {
-    uint32_t a[32], b[32];
-    tmem_ld_x32(addr, a);
-    tmem_ld_x32(addr + 32, b);
-    tmem_wait_ld();
-#pragma unroll
-    for (int j = 0; j < 32; ++j) { f[j] = __uint_as_float(a[j]); f[32 + j] = __uint_as_float(b[j]); }
-}
 
 __global__ void __launch_bounds__(128) wy_bwd_tc_kernel(WyBwdP p) {
     extern __shared__ __align__(1024) unsigned char smem[];

@@ -69,4 +69,15 @@ __device__ __forceinline__ uint32_t taddr(uint32_t base, int warp, int col) {
 }
 
 }  // namespace t8
+
+// 64 accumulator columns of this thread's row -> registers (two 32-column loads, one wait)
+__device__ __forceinline__ void tmem_row64(uint32_t addr, float* f) {
+    uint32_t a[32], b[32];
+    sm100::tmem_ld_x32(addr, a);
+    sm100::tmem_ld_x32(addr + 32, b);
+    sm100::tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { f[j] = __uint_as_float(a[j]); f[32 + j] = __uint_as_float(b[j]); }
+}
+
 }  // namespace hdla
