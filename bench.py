@@ -45,6 +45,8 @@ WORKLOADS = {
     "cfg1": (8, 4096, 16, 128, 128, 64, "bf16"),
     "cfg0": (2, 256, 4, 64, 64, 64, "f32"),
     "cfg3": (1, 65536, 16, 128, 128, 64, "bf16"),
+    # one layer of the 24-layer stack of cfg 4 (B32 sharded over the GPUs by batch): operator only
+    "cfg4": (32, 4096, 16, 128, 128, 64, "bf16"),
     # decode: B sequences, one token per step, carried fp32 state [B,H,K,V]; T is unused
     "cfg2": (256, 1, 32, 128, 128, 0, "bf16"),
 }
@@ -212,6 +214,8 @@ def run_ours(args, rank, world, local_rank):
 
     # this rank's units
     cp = args.workload == "cfg3" and world > 1           # long context: shard T, exchange boundary states
+    if args.workload == "cfg4":
+        args.scaling = "strong"                          # one B32 batch, sharded by batch over the ranks
     if cp:
         args.scaling = "strong"
     Tl = T // world if cp else T
