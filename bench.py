@@ -288,20 +288,24 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize(dev)
     clocks = sampler.stop() if rank == 0 else None
 
-    # end to end: pinned host buffers in, host buffers out
-    out_host = None
+    # end to end: pinned host buffers in, host buffers out, through the package's host-tensor entry point
+    # (slices of the batch pipelined over copy-in / compute / copy-out streams)
+    from hdla_impl_b200.host import chunk_fwd_bwd_from_host
+    out_host = {}
     e2e_steps = args.steps
 
     def e2e_step():
-        nonlocal out_host
-        lv = [host[n].to(dev, non_blocking=True).requires_grad_(True) for n in names]
-        do = host["do"].to(dev, non_blocking=True)
-        o, grads = step(lv, do)
-        outs = (o,) + tuple(grads)
-        if out_host is None:
-            out_host = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outs]
-        for hbuf, t in zip(out_host, outs):
-            hbuf.copy_(t, non_blocking=True)
+        if cp:                                           # sequence-sharded: one slice, collective step
+            lv = [host[n].to(dev, non_blocking=True).requires_grad_(True) for n in names]
+            do = host["do"].to(dev, non_blocking=True)
+            o, grads = step(lv, do)
+            outs = (o,) + tuple(grads)
+            for i, t in enumerate(outs):
+                if i not in out_host:
+                    out_host[i] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+                out_host[i].copy_(t, non_blocking=True)
+        else:
+            chunk_fwd_bwd_from_host(host, out_host, R, dev, scale=scale, chunk_size=C, slice_batch=1)
 
     e2e_step()
     barrier()
@@ -313,7 +317,7 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     ms_e2e = f0.elapsed_time(f1)
     h2d = sum(host[n].numel() * host[n].element_size() for n in host)
-    d2h = sum(t.numel() * t.element_size() for t in out_host)
+    d2h = sum(t.numel() * t.element_size() for t in out_host.values())
 
     if world > 1:
         tt = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)

@@ -1,0 +1,76 @@
+"""Forward + backward of the chunked operator on HOST-resident tensors.
+
+For callers whose activations live in pinned host memory (offloaded training, a data-loader side
+process): the batch is cut into slices along B -- (batch, head) pairs are independent -- and the
+slices are pipelined over three streams, so the host->device copies of slice i+1, the kernels of
+slice i and the device->host copies of slice i-1 overlap.  The result is bound by the slower PCIe
+direction rather than by the sum of copies and compute.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .hrdplr import chunk_hrdplr_delta_rule
+
+_IN = ("q", "k", "v", "a", "b", "gk")
+_OUT = ("o", "dq", "dk", "dv", "da", "db", "dgk")
+
+
+def chunk_fwd_bwd_from_host(host_in: Dict[str, torch.Tensor], host_out: Optional[Dict[str, torch.Tensor]],
+                            RANK_AB: int, device, scale: Optional[float] = None, chunk_size: int = 64,
+                            slice_batch: int = 1) -> Dict[str, torch.Tensor]:
+    """``host_in``: pinned CPU tensors q,k,v,a,b,gk and ``do`` (gradient of o), layouts as in
+    ``chunk_hrdplr_delta_rule``.  Returns (and fills, if given) ``host_out`` with pinned CPU tensors
+    o,dq,dk,dv,da,db,dgk.  Synchronises the device before returning."""
+    dev = torch.device(device)
+    B = host_in["q"].shape[0]
+    if host_out is None:
+        host_out = {}
+    names_in = _IN + ("do",)
+    for n in names_in:
+        if not host_in[n].is_pinned():
+            raise ValueError(f"host tensor '{n}' must be in pinned memory")
+    ref = dict(o="v", dq="q", dk="k", dv="v", da="a", db="b", dgk="gk")
+    for n in _OUT:
+        if n not in host_out:
+            src = host_in[ref[n]]
+            host_out[n] = torch.empty(src.shape, dtype=src.dtype, pin_memory=True)
+    cur = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    s_in.wait_stream(cur)
+    bounds = [(i, min(i + slice_batch, B)) for i in range(0, B, slice_batch)]
+    stage = [None, None]                      # two sets of device input buffers
+    done_compute = [None, None]
+    with torch.cuda.device(dev):
+        for idx, (lo, hi) in enumerate(bounds):
+            slot = idx & 1
+            with torch.cuda.stream(s_in):
+                if done_compute[slot] is not None:
+                    s_in.wait_event(done_compute[slot])        # the buffers of slice idx-2 are free again
+                if stage[slot] is None or stage[slot]["q"].shape[0] != hi - lo:
+                    stage[slot] = {n: torch.empty((hi - lo,) + tuple(host_in[n].shape[1:]), dtype=host_in[n].dtype,
+                                                  device=dev) for n in names_in}
+                for n in names_in:
+                    stage[slot][n].copy_(host_in[n][lo:hi], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            cur.wait_event(ready)
+            lv = [stage[slot][n].requires_grad_(True) for n in _IN]
+            o, _ = chunk_hrdplr_delta_rule(*lv, RANK_AB, scale=scale, chunk_size=chunk_size)
+            grads = torch.autograd.grad(o, lv, stage[slot]["do"])
+            ev = torch.cuda.Event()
+            ev.record(cur)
+            done_compute[slot] = ev
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev)
+                for n, t in zip(_OUT, (o.detach(),) + tuple(grads)):
+                    t.record_stream(s_out)
+                    host_out[n][lo:hi].copy_(t, non_blocking=True)
+            for n in _IN:
+                stage[slot][n].requires_grad_(False)
+        cur.wait_stream(s_out)
+        cur.wait_stream(s_in)
+    torch.cuda.synchronize(dev)
+    return host_out

@@ -259,3 +259,18 @@ def test_prefill_then_decode_state_handoff(dev):
     f = lambda n: x[n].double()
     ro, rh = orc.recurrent_ref(f("q"), f("k"), f("v"), f("a"), f("b"), f("gk"), R, None, None)
     assert orc.rel_err(o, ro) < 2e-2 and orc.rel_err(S, rh) < 2e-2
+
+
+def test_host_pipeline_matches_device_call(dev):
+    """chunk_fwd_bwd_from_host (pinned host tensors, sliced and pipelined over streams) equals one device call."""
+    import hdla_impl_b200 as H
+    from hdla_impl_b200.host import chunk_fwd_bwd_from_host
+    x = make_inputs(3, 128, 2, 128, 128, R, seed=15, dtype=torch.bfloat16)
+    names = ("q", "k", "v", "a", "b", "gk")
+    host = {n: x[n].pin_memory() for n in names + ("do",)}
+    out = chunk_fwd_bwd_from_host(host, None, R, dev, chunk_size=64, slice_batch=1)
+    lv = [x[n].to(dev).requires_grad_(True) for n in names]
+    o, _ = H.chunk_hrdplr_delta_rule(*lv, R, chunk_size=64)
+    g = torch.autograd.grad(o, lv, x["do"].to(dev))
+    for n, t in zip(("o", "dq", "dk", "dv", "da", "db", "dgk"), (o,) + tuple(g)):
+        assert torch.equal(out[n], t.detach().cpu()), n
