@@ -201,4 +201,26 @@ int hdla_recurrent_fwd(const HdlaDims* dims, const void* q, const void* k, const
                                 static_cast<cudaStream_t>(cuda_stream));
 }
 
+int hdla_param_ab_fwd(const void* beta, const void* k, const void* log_f, void* a, void* b, int32_t B, int32_t T,
+                      int32_t H, int32_t K, int32_t dtype, void* cuda_stream) {
+    if (!beta || !k || !log_f || !a || !b) return fail(HDLA_ERR_INVALID, "param_ab_fwd: null tensor pointer");
+    if (B <= 0 || T <= 0 || H <= 0 || K <= 0) return fail(HDLA_ERR_INVALID, "param_ab_fwd: non-positive dimension");
+    if (dtype != HDLA_F32 && dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", dtype);
+    begin_call(cuda_stream);
+    return param_ab_launch(false, beta, k, log_f, a, b, nullptr, nullptr, nullptr, B, T, H, K, dtype,
+                           static_cast<cudaStream_t>(cuda_stream));
+}
+
+int hdla_param_ab_bwd(const void* beta, const void* k, const void* log_f, const void* da, const void* db, void* dbeta,
+                      void* dk, void* dlog_f, int32_t B, int32_t T, int32_t H, int32_t K, int32_t dtype,
+                      void* cuda_stream) {
+    if (!beta || !k || !log_f || !da || !db || !dbeta || !dk || !dlog_f)
+        return fail(HDLA_ERR_INVALID, "param_ab_bwd: null tensor pointer");
+    if (B <= 0 || T <= 0 || H <= 0 || K <= 0) return fail(HDLA_ERR_INVALID, "param_ab_bwd: non-positive dimension");
+    if (dtype != HDLA_F32 && dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", dtype);
+    begin_call(cuda_stream);
+    return param_ab_launch(true, beta, k, log_f, const_cast<void*>(da), const_cast<void*>(db), dbeta, dk, dlog_f, B, T,
+                           H, K, dtype, static_cast<cudaStream_t>(cuda_stream));
+}
+
 }  // extern "C"

@@ -54,6 +54,9 @@ int simt_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* 
                    const void* gk, float scale, const float* h0, const void* d_o, const float* dht, void* dq,
                    void* dk, void* dv, void* da, void* db, void* dgk, float* dh0, float* ws, cudaStream_t st);
 
+int param_ab_launch(bool backward, const void* beta, const void* k, const void* log_f, void* a, void* b, void* dbeta,
+                    void* dk, void* dlog_f, int B, int T, int H, int K, int dt, cudaStream_t st);
+
 // tensor-core (bf16) pipeline, chunk_tc.cu
 bool tc_supported(const HdlaDims& d);
 size_t tc_workspace_bytes(const HdlaDims& d, int with_backward);

@@ -188,6 +188,17 @@ HDLA_API int hdla_recurrent_fwd(const HdlaDims* dims,
                        const int64_t* cu_seqlens, int32_t n_seqs, int32_t reverse,
                        void* cuda_stream);
 
+/* a/b parametrisation of the HDLA layer, forward and backward.  Replaces parameterize_a_b
+ * (HRDPLR/hdla_custom.py:19-43; as shipped that function builds a and b but has no return statement):
+ *   a1 = -beta k, a2 = -beta e^{log_f} k + a1 * sum_K(k * (-beta e^{log_f} k)), b1 = e^{log_f} k, b2 = k
+ *   beta [B,T,H,1], k and log_f [B,T,H,K]  ->  a, b [B, 2T, H, K] (row 2t + r), all in `dtype`.
+ * Backward takes da, db and writes dbeta [B,T,H,1], dk, dlog_f. */
+HDLA_API int hdla_param_ab_fwd(const void* beta, const void* k, const void* log_f, void* a, void* b,
+                               int32_t B, int32_t T, int32_t H, int32_t K, int32_t dtype, void* cuda_stream);
+HDLA_API int hdla_param_ab_bwd(const void* beta, const void* k, const void* log_f, const void* da, const void* db,
+                               void* dbeta, void* dk, void* dlog_f,
+                               int32_t B, int32_t T, int32_t H, int32_t K, int32_t dtype, void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

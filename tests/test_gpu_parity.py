@@ -274,3 +274,37 @@ def test_host_pipeline_matches_device_call(dev):
     g = torch.autograd.grad(o, lv, x["do"].to(dev))
     for n, t in zip(("o", "dq", "dk", "dv", "da", "db", "dgk"), (o,) + tuple(g)):
         assert torch.equal(out[n], t.detach().cpu()), n
+
+
+def _param_ab_torch(beta, k, log_f):
+    """Restatement of the reference's parameterize_a_b (HRDPLR/hdla_custom.py:19-43) with the missing return."""
+    a_t1 = -beta * k
+    a_t2 = -beta * torch.exp(log_f) * k
+    a_2 = a_t2 + a_t1 * torch.sum(k * a_t2, dim=-1, keepdim=True)
+    b_1 = torch.exp(log_f) * k
+    B, T, H, K = k.shape
+    a = torch.stack([a_t1, a_2], dim=2).reshape(B, 2 * T, H, K)
+    b = torch.stack([b_1, k], dim=2).reshape(B, 2 * T, H, K)
+    return a, b
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_parameterize_a_b_forward_backward(dev, dtype, tol):
+    from hdla_impl_b200.layer_ops import parameterize_a_b
+    g = torch.Generator().manual_seed(3)
+    B, T, H, K = 2, 33, 3, 96
+    k = torch.nn.functional.normalize(torch.randn(B, T, H, K, generator=g), dim=-1)
+    beta = 2 * torch.sigmoid(torch.randn(B, T, H, 1, generator=g))
+    log_f = torch.nn.functional.logsigmoid(torch.randn(B, T, H, K, generator=g))
+    ga, gb = torch.randn(B, 2 * T, H, K, generator=g), torch.randn(B, 2 * T, H, K, generator=g)
+    rd = lambda t: t.to(dtype).double().requires_grad_(True)
+    rb, rk, rf = rd(beta), rd(k), rd(log_f)
+    ra, rbb = _param_ab_torch(rb, rk, rf)
+    rg = torch.autograd.grad((ra * ga.to(dtype).double()).sum() + (rbb * gb.to(dtype).double()).sum(), [rb, rk, rf])
+    xb, xk, xf = (t.to(dtype).to(dev).requires_grad_(True) for t in (beta, k, log_f))
+    a, b = parameterize_a_b(xb, xk, xf)
+    gg = torch.autograd.grad((a.float() * ga.to(dtype).to(dev).float()).sum() + (b.float() * gb.to(dtype).to(dev).float()).sum(),
+                             [xb, xk, xf])
+    assert orc.rel_err(a, ra) < tol and orc.rel_err(b, rbb) < tol
+    for got, ref, n in zip(gg, rg, ("dbeta", "dk", "dlog_f")):
+        assert orc.rel_err(got, ref) < tol, n
