@@ -308,3 +308,19 @@ def test_parameterize_a_b_forward_backward(dev, dtype, tol):
     assert orc.rel_err(a, ra) < tol and orc.rel_err(b, rbb) < tol
     for got, ref, n in zip(gg, rg, ("dbeta", "dk", "dlog_f")):
         assert orc.rel_err(got, ref) < tol, n
+
+
+def test_bf16_recompute_and_forward_only(dev, monkeypatch):
+    """Tensor-core path: backward that recomputes the forward (HDLA_RECOMPUTE=1, the reference's behaviour) gives
+    the same gradients as backward on the saved workspace; a no-grad forward uses the forward-only workspace."""
+    import hdla_impl_b200 as H
+    x = make_inputs(1, 256, 2, 128, 128, R, seed=16, dtype=torch.bfloat16, h0_std=0.1, with_dht=True)
+    a = run_chunk(x, dev, 0.1, 64, True, True, torch.bfloat16)
+    monkeypatch.setenv("HDLA_RECOMPUTE", "1")
+    b = run_chunk(x, dev, 0.1, 64, True, True, torch.bfloat16)
+    for n in a:
+        assert torch.equal(a[n], b[n]), n
+    with torch.no_grad():
+        o, ht = H.chunk_hrdplr_delta_rule(*[x[n].to(dev) for n in ("q", "k", "v", "a", "b", "gk")], R, scale=0.1,
+                                          initial_state=x["h0"].to(dev), output_final_state=True, chunk_size=64)
+    assert torch.equal(o, a["o"]) and torch.equal(ht, a["ht"])
