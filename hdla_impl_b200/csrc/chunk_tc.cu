@@ -1080,7 +1080,7 @@ __device__ __forceinline__ float c8s(const uint4* tile, int rows, int r, int c) 
     return __bfloat162float(q[c & 7]);
 }
 
-__global__ void __launch_bounds__(288) grad_tc_kernel(GradP p) {
+__global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint4* sA = reinterpret_cast<uint4*>(smem);          // 32 KB slots
     uint4* sB = sA + CH128;
@@ -1096,7 +1096,7 @@ __global__ void __launch_bounds__(288) grad_tc_kernel(GradP p) {
     __shared__ uint32_t tmem_s;
     const long long g = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5;
-    const bool producer = tid == 256;                   // lane 0 of the ninth warp loads tiles and issues MMAs
+    const bool producer = tid == 512;                   // lane 0 of the seventeenth warp loads tiles and issues MMAs
     if (warp == 0) { tmem_alloc(&tmem_s, 512); tmem_relinquish(); }
     if (producer) {
         mbar_init(&L1, 1); mbar_init(&L2, 1); mbar_init(&L3, 1); mbar_init(&L4, 1); mbar_init(&L5, 1);
@@ -1162,15 +1162,15 @@ __global__ void __launch_bounds__(288) grad_tc_kernel(GradP p) {
         bulk_g2s(sA, p.Bh + g * CH128, 32768, &L5);
         bulk_g2s(sC, p.ghat + (size_t)g * C * K, 32768, &L5);      // fp32 [64][128] over the dSt slot
     }
-    if (warp < 8) {
+    if (warp < 16) {
         wait_idle_or_flag(&m4, 0, p.status, 48);
         wait_idle_or_flag(&L5, 0, p.status, 49);
     }
     tc_fence_after();
-    if (warp < 8) {
-        // two warpgroups share the token loop: group 0 walks tokens 63..32, group 1 tokens 31..0 and
-        // adds group 0's total to its running sums afterwards
-        __shared__ float upper_total[K];
+    if (warp < 16) {
+        // four warpgroups share the token loop (the work is latency bound): group w walks tokens
+        // 63-16w .. 48-16w and adds the totals of the groups above it to its running sums afterwards
+        float (*group_total)[K] = reinterpret_cast<float (*)[K]>(sy);      // 2 KB in the (consumed) Aqk slot
         const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
         const int b = bh / p.H, h = bh % p.H;
         const int k = tid & 127, wg = tid >> 7;
@@ -1187,12 +1187,12 @@ __global__ void __launch_bounds__(288) grad_tc_kernel(GradP p) {
         const size_t base_ab = (((size_t)b * p.T + (size_t)n * C) * R * p.H + h) * K + k;
         float run = 0.f;
         float* dgk_loc = reinterpret_cast<float*>(sE);    // [64][128] fp32 over the (consumed) dAab slot
-        const int i_hi = wg == 0 ? 63 : 31;
+        const int i_hi = 63 - 16 * wg;
         float ep = __expf(gh[(size_t)i_hi * K + k]);
         const int t_left = p.T - n * C;                               // tokens of this chunk that exist
 #pragma unroll 1
-        for (int ibl = 3; ibl >= 0; --ibl) {
-            const int ib = (wg == 0 ? 4 : 0) + ibl;
+        for (int ibl = 1; ibl >= 0; --ibl) {
+            const int ib = (3 - wg) * 2 + ibl;
             uint32_t vq[8], vk[8], va[16], vb[16];
             tmem_ld_x8(t8::taddr(tmem, warp, ib * 8), vq);
             tmem_ld_x8(t8::taddr(tmem, warp, 384 + ib * 8), vk);
@@ -1233,23 +1233,24 @@ __global__ void __launch_bounds__(288) grad_tc_kernel(GradP p) {
                 ep = ee;                                  // e^{ghat} of token i-1
             }
         }
-        if (wg == 0) upper_total[k] = run;
-        asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight epilogue warps only
-        const float add = wg == 0 ? 0.f : upper_total[k];
+        group_total[wg][k] = run;
+        asm volatile("bar.sync 1, 512;" ::: "memory");     // the sixteen epilogue warps only
+        float add = 0.f;
+        for (int w = 0; w < wg; ++w) add += group_total[w][k];
 #pragma unroll 4
-        for (int jj = 0; jj < 32; ++jj) {
-            const int i = (wg == 0 ? 32 : 0) + jj;
+        for (int jj = 0; jj < 16; ++jj) {
+            const int i = (3 - wg) * 16 + jj;
             const int t = n * C + i;
             if (t < p.T) st_elem(p.dgk, (((size_t)b * p.T + t) * p.H + h) * K + k, p.gdt, dgk_loc[i * K + k] + add);
         }
-        // dv: accumulator lane = value channel; each warpgroup writes 32 tokens
+        // dv: accumulator lane = value channel; each warpgroup writes 16 tokens
         {
-            uint32_t v[32];
-            tmem_ld_x32(t8::taddr(tmem, warp, 64 + wg * 32), v);
+            uint32_t v[16];
+            tmem_ld_x16(t8::taddr(tmem, warp, 64 + wg * 16), v);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int t = n * C + wg * 32 + j;
+            for (int j = 0; j < 16; ++j) {
+                const int t = n * C + wg * 16 + j;
                 if (t < p.T) p.dv[(((size_t)b * p.T + t) * p.H + h) * V + k] = __float2bfloat16_rn(__uint_as_float(v[j]));
             }
         }
@@ -1407,7 +1408,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
              U4(pl.Aqk), U4(pl.dW), U4(pl.M), U4(pl.dAab), U4(pl.dAak), U4(pl.V2), U4(pl.Ah), U4(pl.Qh), U4(pl.Vc),
              F(pl.ghat), F(pl.dgl), (bp)dq, (bp)dk, (bp)dv, (bp)da, (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype,
              status};
-    grad_tc_kernel<<<G, 288, kGradSmem, st>>>(gp);
+    grad_tc_kernel<<<G, 544, kGradSmem, st>>>(gp);
     HDLA_CHECK_LAUNCH("grad_tc_kernel");
     return HDLA_OK;
 }
