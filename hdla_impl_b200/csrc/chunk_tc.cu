@@ -267,21 +267,23 @@ __global__ void __launch_bounds__(128) gram_tc_kernel(GramP p) {
     tc_fence_after();
     {
         const int r = tid, i = r >> 1;
-        for (int cg = 0; cg < 8; ++cg) {                      // Aak: columns j < i
-            uint32_t v[8]; float f[8];
-            tmem_ld_x8(t8::taddr(tmem, warp, cg * 8), v);
-            tmem_wait_ld();
+        float f[64];
+        tmem_row64(t8::taddr(tmem, warp, 0), f);              // Aak: columns j < i
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = (cg * 8 + j) < i ? __uint_as_float(v[j]) : 0.f;
-            p.Aak[g * CH64 + cg * 128 + r] = t8::pack8(f);    // [128 x 64] tile: 8 column groups of 128 rows
+        for (int cg = 0; cg < 8; ++cg) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) if (!((cg * 8 + j) < i)) f[cg * 8 + j] = 0.f;
+            p.Aak[g * CH64 + cg * 128 + r] = t8::pack8(f + cg * 8);   // [128 x 64] tile: 8 column groups of 128 rows
         }
-        for (int cg = 0; cg < 16; ++cg) {                     // Aab: column token < row token
-            uint32_t v[8]; float f[8];
-            tmem_ld_x8(t8::taddr(tmem, warp, 64 + cg * 8), v);
-            tmem_wait_ld();
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {                      // Aab: column token < row token
+            tmem_row64(t8::taddr(tmem, warp, 64 + hh * 64), f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = ((cg * 8 + j) >> 1) < i ? __uint_as_float(v[j]) : 0.f;
-            p.Aab[g * CH128 + cg * 128 + r] = t8::pack8(f);
+            for (int cg = 0; cg < 8; ++cg) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) if (!(((hh * 64 + cg * 8 + j) >> 1) < i)) f[cg * 8 + j] = 0.f;
+                p.Aab[g * CH128 + (hh * 8 + cg) * 128 + r] = t8::pack8(f + cg * 8);
+            }
         }
     }
     tc_fence_before();
@@ -297,21 +299,23 @@ __global__ void __launch_bounds__(128) gram_tc_kernel(GramP p) {
     tc_fence_after();
     if (warp < 2) {
         const int i = tid;
-        for (int cg = 0; cg < 8; ++cg) {                      // Aqk: j <= i
-            uint32_t v[8]; float f[8];
-            tmem_ld_x8(t8::taddr(tmem, warp, cg * 8), v);
-            tmem_wait_ld();
+        float f[64];
+        tmem_row64(t8::taddr(tmem, warp, 0), f);              // Aqk: j <= i
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = (cg * 8 + j) <= i ? __uint_as_float(v[j]) : 0.f;
-            p.Aqk[g * 512 + cg * 64 + i] = t8::pack8(f);
+        for (int cg = 0; cg < 8; ++cg) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) if (!((cg * 8 + j) <= i)) f[cg * 8 + j] = 0.f;
+            p.Aqk[g * 512 + cg * 64 + i] = t8::pack8(f + cg * 8);
         }
-        for (int cg = 0; cg < 16; ++cg) {                     // Aqb: column token <= i
-            uint32_t v[8]; float f[8];
-            tmem_ld_x8(t8::taddr(tmem, warp, 64 + cg * 8), v);
-            tmem_wait_ld();
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {                      // Aqb: column token <= i
+            tmem_row64(t8::taddr(tmem, warp, 64 + hh * 64), f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = ((cg * 8 + j) >> 1) <= i ? __uint_as_float(v[j]) : 0.f;
-            p.Aqb[g * CH64 + cg * 64 + i] = t8::pack8(f);
+            for (int cg = 0; cg < 8; ++cg) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) if (!(((hh * 64 + cg * 8 + j) >> 1) <= i)) f[cg * 8 + j] = 0.f;
+                p.Aqb[g * CH64 + (hh * 8 + cg) * 64 + i] = t8::pack8(f + cg * 8);
+            }
         }
     }
     tc_fence_before();
@@ -388,13 +392,12 @@ __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
         wait_or_flag(&mma_bar, phase, p.status, 6);
         phase ^= 1;
         tc_fence_after();
-        for (int cg = 0; cg < 16; ++cg) {
-            uint32_t v[8]; float f[8];
-            tmem_ld_x8(t8::taddr(tmem, warp, cg * 8), v);
-            tmem_wait_ld();
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+            float f[64];
+            tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]);
-            sX[cg * 128 + tid] = t8::pack8(f);
+            for (int cg = 0; cg < 8; ++cg) sX[(hh * 8 + cg) * 128 + tid] = t8::pack8(f + cg * 8);
         }
         fence_proxy_async();
         tc_fence_before();
@@ -478,15 +481,16 @@ __global__ void __launch_bounds__(128) wu_tc_kernel(WuP p) {
     }
     wait_or_flag(&mma_bar, 0, p.status, 9);
     tc_fence_after();
-    for (int cg = 0; cg < 16; ++cg) {
-        uint32_t v[8]; float f[8];
-        tmem_ld_x8(t8::taddr(tmem, warp, cg * 8), v);
-        tmem_wait_ld();
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {
+        float f[64];
+        tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]);
-        const uint4 c = t8::pack8(f);
-        sP[cg * 128 + tid] = c;
-        p.P[g * CH128 + cg * 128 + tid] = c;
+        for (int cg = 0; cg < 8; ++cg) {
+            const uint4 c = t8::pack8(f + cg * 8);
+            sP[(hh * 8 + cg) * 128 + tid] = c;
+            p.P[g * CH128 + (hh * 8 + cg) * 128 + tid] = c;
+        }
     }
     fence_proxy_async();
     tc_fence_before();
@@ -496,23 +500,21 @@ __global__ void __launch_bounds__(128) wu_tc_kernel(WuP p) {
         t8::mma_chain<false, true>(tmem, tM, 0, 0, tP, 0, 0, 128, 128, false);           // u = M P
         umma_commit(&mma_bar);
     }
-    for (int cg = 0; cg < 16; ++cg) {                                                     // Wh while u runs
-        uint32_t v[8]; float f[8];
-        tmem_ld_x8(t8::taddr(tmem, warp, 128 + cg * 8), v);
-        tmem_wait_ld();
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {                                                      // Wh while u runs
+        float f[64];
+        tmem_row64(t8::taddr(tmem, warp, 128 + hh * 64), f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]);
-        p.W[g * CH128 + cg * 128 + tid] = t8::pack8(f);
+        for (int cg = 0; cg < 8; ++cg) p.W[g * CH128 + (hh * 8 + cg) * 128 + tid] = t8::pack8(f + cg * 8);
     }
     wait_or_flag(&mma_bar, 1, p.status, 10);
     tc_fence_after();
-    for (int cg = 0; cg < 16; ++cg) {
-        uint32_t v[8]; float f[8];
-        tmem_ld_x8(t8::taddr(tmem, warp, cg * 8), v);
-        tmem_wait_ld();
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {
+        float f[64];
+        tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]);
-        p.U[g * CH128 + cg * 128 + tid] = t8::pack8(f);
+        for (int cg = 0; cg < 8; ++cg) p.U[g * CH128 + (hh * 8 + cg) * 128 + tid] = t8::pack8(f + cg * 8);
     }
     tc_fence_before();
     __syncthreads();
@@ -1012,13 +1014,14 @@ __global__ void __launch_bounds__(128) out_tc_kernel(OutP p) {
         const int b = bh / p.H, h = bh % p.H;
         const int t = n * C + tid;
         uint4* dst = reinterpret_cast<uint4*>(p.o + (((size_t)b * p.T + t) * p.H + h) * V);
-        for (int cg = 0; cg < 16; ++cg) {
-            uint32_t v[8]; float f[8];
-            tmem_ld_x8(t8::taddr(tmem, warp, cg * 8), v);
-            tmem_wait_ld();
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+            float f[64];
+            tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
+            if (t < p.T) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]);
-            if (t < p.T) dst[cg] = t8::pack8(f);
+                for (int cg = 0; cg < 8; ++cg) dst[hh * 8 + cg] = t8::pack8(f + cg * 8);
+            }
         }
     }
     tc_fence_before();
