@@ -19,7 +19,7 @@ PHASE_ALL, PHASE_PRE, PHASE_TRANSITION, PHASE_STATE, PHASE_POST = 0x00, 0x10, 0x
 
 EXPORTS = (
     "hdla_version", "hdla_last_error", "hdla_chunk_workspace_bytes", "hdla_chunk_fwd", "hdla_chunk_bwd",
-    "hdla_recurrent_fwd", "hdla_kernel_launches", "hdla_debug_tc_buffer", "hdla_chunk_fwd_noalloc", "hdla_timing_enable", "hdla_timing_report", "hdla_param_ab_fwd", "hdla_param_ab_bwd",
+    "hdla_recurrent_fwd", "hdla_kernel_launches", "hdla_debug_tc_buffer", "hdla_chunk_fwd_noalloc", "hdla_timing_enable", "hdla_timing_report", "hdla_param_ab_fwd", "hdla_param_ab_bwd", "hdla_norm_gate_fwd", "hdla_norm_gate_bwd",
 )
 
 
@@ -60,6 +60,10 @@ def load() -> C.CDLL:
         lib.hdla_param_ab_fwd.argtypes = [vp, vp, vp, vp, vp, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, vp]
         lib.hdla_param_ab_bwd.restype = C.c_int
         lib.hdla_param_ab_bwd.argtypes = [vp] * 8 + [C.c_int32] * 5 + [vp]
+        lib.hdla_norm_gate_fwd.restype = C.c_int
+        lib.hdla_norm_gate_fwd.argtypes = [vp, vp, vp, vp, C.c_int64, C.c_int32, C.c_float, C.c_int32, vp]
+        lib.hdla_norm_gate_bwd.restype = C.c_int
+        lib.hdla_norm_gate_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, C.c_int64, C.c_int32, C.c_float, C.c_int32, vp]
         lib.hdla_timing_enable.restype = None
         lib.hdla_timing_enable.argtypes = [C.c_int]
         lib.hdla_timing_report.restype = C.c_size_t

@@ -223,4 +223,25 @@ int hdla_param_ab_bwd(const void* beta, const void* k, const void* log_f, const 
                            H, K, dtype, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int hdla_norm_gate_fwd(const void* x, const void* gate, const void* weight, void* o, int64_t rows, int32_t D,
+                       float eps, int32_t dtype, void* cuda_stream) {
+    if (!x || !gate || !weight || !o) return fail(HDLA_ERR_INVALID, "norm_gate_fwd: null tensor pointer");
+    if (rows <= 0 || D <= 0 || rows > 0x7fffffffLL) return fail(HDLA_ERR_INVALID, "norm_gate_fwd: bad size");
+    if (dtype != HDLA_F32 && dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", dtype);
+    begin_call(cuda_stream);
+    return norm_gate_launch(false, x, gate, weight, nullptr, o, nullptr, nullptr, nullptr, rows, D, eps, dtype,
+                            static_cast<cudaStream_t>(cuda_stream));
+}
+
+int hdla_norm_gate_bwd(const void* x, const void* gate, const void* weight, const void* d_o, void* dx, void* dgate,
+                       float* dweight, int64_t rows, int32_t D, float eps, int32_t dtype, void* cuda_stream) {
+    if (!x || !gate || !weight || !d_o || !dx || !dgate || !dweight)
+        return fail(HDLA_ERR_INVALID, "norm_gate_bwd: null tensor pointer");
+    if (rows <= 0 || D <= 0 || rows > 0x7fffffffLL) return fail(HDLA_ERR_INVALID, "norm_gate_bwd: bad size");
+    if (dtype != HDLA_F32 && dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", dtype);
+    begin_call(cuda_stream);
+    return norm_gate_launch(true, x, gate, weight, d_o, nullptr, dx, dgate, dweight, rows, D, eps, dtype,
+                            static_cast<cudaStream_t>(cuda_stream));
+}
+
 }  // extern "C"

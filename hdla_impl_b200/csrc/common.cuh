@@ -57,6 +57,9 @@ int simt_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* 
 int param_ab_launch(bool backward, const void* beta, const void* k, const void* log_f, void* a, void* b, void* dbeta,
                     void* dk, void* dlog_f, int B, int T, int H, int K, int dt, cudaStream_t st);
 
+int norm_gate_launch(bool backward, const void* x, const void* gate, const void* weight, const void* d_o, void* o,
+                     void* dx, void* dgate, float* dweight, long long rows, int D, float eps, int dt, cudaStream_t st);
+
 // tensor-core (bf16) pipeline, chunk_tc.cu
 bool tc_supported(const HdlaDims& d);
 size_t tc_workspace_bytes(const HdlaDims& d, int with_backward);

@@ -324,3 +324,24 @@ def test_bf16_recompute_and_forward_only(dev, monkeypatch):
         o, ht = H.chunk_hrdplr_delta_rule(*[x[n].to(dev) for n in ("q", "k", "v", "a", "b", "gk")], R, scale=0.1,
                                           initial_state=x["h0"].to(dev), output_final_state=True, chunk_size=64)
     assert torch.equal(o, a["o"]) and torch.equal(ht, a["ht"])
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+def test_rms_norm_fused_gate_forward_backward(dev, dtype, tol):
+    """Against the arithmetic of the reference's normalize_torch (c = sqrt(D), no mean, sigmoid gate applied before)."""
+    from hdla_impl_b200.layer_ops import rms_norm_fused_gate
+    g = torch.Generator().manual_seed(5)
+    rows, D, eps = 37, 2048, 1e-5
+    x, gate = torch.randn(3, rows, D, generator=g), torch.randn(3, rows, D, generator=g)
+    w, go = 1 + 0.1 * torch.randn(D, generator=g), torch.randn(3, rows, D, generator=g)
+    rd = lambda t: t.to(dtype).double().requires_grad_(True)
+    rx, rg, rw = rd(x), rd(gate), rd(w)
+    y = rx * torch.sigmoid(rg)
+    ro = (D ** 0.5) * y / torch.sqrt((y * y).sum(-1, keepdim=True) + eps) * rw
+    rgrads = torch.autograd.grad((ro * go.to(dtype).double()).sum(), [rx, rg, rw])
+    dx, dg, dw = (t.to(dtype).to(dev).requires_grad_(True) for t in (x, gate, w))
+    o = rms_norm_fused_gate(dx, dg, dw, eps)
+    grads = torch.autograd.grad((o.float() * go.to(dtype).to(dev).float()).sum(), [dx, dg, dw])
+    assert orc.rel_err(o, ro) < tol
+    for got, ref, n in zip(grads, rgrads, ("dx", "dgate", "dweight")):
+        assert orc.rel_err(got, ref) < tol, n
