@@ -1,0 +1,64 @@
+"""GPU: parity at the benchmark's full sizes.  The oracle is too slow for the whole problem, but
+(batch, head) pairs are independent, so one pair of the full-size run is compared with the oracle run
+on that pair alone; and the full-size results must not depend on how the batch is cut."""
+import pytest
+import torch
+
+from oracle import hdla_oracle as orc
+from hdla_impl_b200.synthetic import make_inputs
+
+pytestmark = pytest.mark.gpu
+R = 2
+NAMES = ("q", "k", "v", "a", "b", "gk")
+
+
+def test_cfg1_full_size_slice_against_oracle():
+    """B8 T4096 H16 K=V=128 bf16 chunk 64: forward + backward of the whole batch on the GPU; (b, h) = (5, 11)
+    against the fp64 oracle; gradients of all inputs within 2e-2."""
+    import hdla_impl_b200 as H
+    dev = torch.device("cuda:0")
+    B, T, Hh, K, V = 8, 4096, 16, 128, 128
+    x = make_inputs(B, T, Hh, K, V, R, seed=0, dtype=torch.bfloat16)
+    lv = [x[n].to(dev).requires_grad_(True) for n in NAMES]
+    o, ht = H.chunk_hrdplr_delta_rule(*lv, R, chunk_size=64, output_final_state=True)
+    grads = torch.autograd.grad(o, lv, x["do"].to(dev))
+    H.check_status(dev, wait=True)
+    b, h = 5, 11
+    sl = lambda t: t[b:b + 1, :, h:h + 1].double()
+    st = orc.staged_forward(*[sl(x[n]) for n in NAMES], R, K ** -0.5, None, 64)
+    g = orc.staged_backward(st, sl(x["do"]), None)
+    bad = []
+    for name, got, ref in [("o", o, st["o_bthv"]), ("ht", ht[b:b + 1, h:h + 1], st["ht"])] + \
+            [(n, t, g[n]) for n, t in zip(("dq", "dk", "dv", "da", "db", "dgk"), grads)]:
+        got = got if name == "ht" else got[b:b + 1, :, h:h + 1]
+        e = orc.rel_err(got, ref)
+        if not e < 2e-2:
+            bad.append(f"{name}: {e:.3e}")
+    assert not bad, "; ".join(bad)
+    # independence of the batch cut: the first two sequences alone give bit-identical results
+    lv2 = [x[n][:2].to(dev).requires_grad_(True) for n in NAMES]
+    o2, _ = H.chunk_hrdplr_delta_rule(*lv2, R, chunk_size=64)
+    g2 = torch.autograd.grad(o2, lv2, x["do"][:2].to(dev))
+    assert torch.equal(o2, o[:2])
+    for a_, b_ in zip(g2, grads):
+        assert torch.equal(a_, b_[:2])
+
+
+def test_cfg2_full_size_decode_against_oracle():
+    """256 sequences x 32 heads, K=V=128, bf16 tokens, fp32 state N(0, 0.02): 4 decode steps on the GPU;
+    sequences 0 and 200 against the fp64 recurrence."""
+    import hdla_impl_b200 as H
+    dev = torch.device("cuda:0")
+    B, Hh, K, V, steps = 256, 32, 128, 128, 4
+    x = make_inputs(B, steps, Hh, K, V, R, seed=2, dtype=torch.bfloat16, h0_std=0.02)
+    S = x["h0"].to(dev).clone()
+    outs = []
+    for t in range(steps):
+        cur = [x[n][:, t * (R if n in ("a", "b") else 1):(t + 1) * (R if n in ("a", "b") else 1)].to(dev) for n in NAMES]
+        o, S = H.fused_recurrent_dplr_delta_rule_fwd(*cur, R, K ** -0.5, S, True, inplace_state=True)
+        outs.append(o)
+    o = torch.cat(outs, 1)
+    for s in (0, 200):
+        ro, rh = orc.recurrent_ref(*[x[n][s:s + 1].double() for n in NAMES], R, None, x["h0"][s:s + 1])
+        assert orc.rel_err(o[s:s + 1], ro) < 2e-2
+        assert orc.rel_err(S[s:s + 1], rh) < 1e-3
