@@ -19,7 +19,7 @@ PHASE_ALL, PHASE_PRE, PHASE_TRANSITION, PHASE_STATE, PHASE_POST = 0x00, 0x10, 0x
 
 EXPORTS = (
     "hdla_version", "hdla_last_error", "hdla_chunk_workspace_bytes", "hdla_chunk_fwd", "hdla_chunk_bwd",
-    "hdla_recurrent_fwd", "hdla_kernel_launches", "hdla_debug_tc_buffer", "hdla_chunk_fwd_noalloc", "hdla_timing_enable", "hdla_timing_report", "hdla_param_ab_fwd", "hdla_param_ab_bwd", "hdla_norm_gate_fwd", "hdla_norm_gate_bwd",
+    "hdla_recurrent_fwd", "hdla_kernel_launches", "hdla_debug_tc_buffer", "hdla_chunk_uses_tensor_cores", "hdla_chunk_fwd_noalloc", "hdla_timing_enable", "hdla_timing_report", "hdla_param_ab_fwd", "hdla_param_ab_bwd", "hdla_norm_gate_fwd", "hdla_norm_gate_bwd",
 )
 
 
@@ -68,6 +68,8 @@ def load() -> C.CDLL:
         lib.hdla_timing_enable.argtypes = [C.c_int]
         lib.hdla_timing_report.restype = C.c_size_t
         lib.hdla_timing_report.argtypes = [C.c_char_p, C.c_size_t]
+        lib.hdla_chunk_uses_tensor_cores.restype = C.c_int
+        lib.hdla_chunk_uses_tensor_cores.argtypes = [dp]
         lib.hdla_debug_tc_buffer.restype = C.c_int
         lib.hdla_debug_tc_buffer.argtypes = [dp, vp, C.c_char_p, vp, vp]
         lib.hdla_chunk_workspace_bytes.restype = C.c_size_t

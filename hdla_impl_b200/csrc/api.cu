@@ -136,6 +136,11 @@ size_t hdla_chunk_workspace_bytes(const HdlaDims* dims, int with_backward) {
     return simt;
 }
 
+int hdla_chunk_uses_tensor_cores(const HdlaDims* dims) {
+    if (check_common(dims, true) != HDLA_OK) return 0;
+    return tc_supported(*dims) ? 1 : 0;
+}
+
 int hdla_debug_tc_buffer(const HdlaDims* dims, const void* workspace, const char* name, float* out,
                          void* cuda_stream) {
     int rc = check_common(dims, true);

@@ -29,7 +29,20 @@ def contiguous(fn):
     return wrapper
 
 
+def _internal_chunk(q, v, RANK_AB: int, chunk_size: int) -> int:
+    """Chunk size actually used.  The operator's result does not depend on the chunk size (it only sets how
+    the recurrence is blocked), and the reference layer asks for 16 (HRDPLR/hdla_custom.py:308) only because its
+    own backward is limited to that.  Problems the tensor-core pipeline supports are therefore run at its chunk
+    of 64 whatever was requested; ``HDLA_HONOR_CHUNK=1`` keeps the requested value."""
+    T, K, V = q.shape[1], q.shape[-1], v.shape[-1]
+    if (os.environ.get("HDLA_HONOR_CHUNK", "0") != "1" and q.dtype == torch.bfloat16 and RANK_AB == 2
+            and K == 128 and V == 128 and T > 32 and os.environ.get("HDLA_FORCE_SIMT", "0") != "1"):
+        return 64
+    return chunk_size
+
+
 def _dims(q, v, a, gk, RANK_AB: int, chunk_size: int, flags: int = 0) -> _lib.HdlaDims:
+    chunk_size = _internal_chunk(q, v, RANK_AB, chunk_size)
     B, T, H, K = q.shape
     if os.environ.get("HDLA_FORCE_SIMT", "0") == "1":      # debugging aid: fp32 CUDA-core pipeline for any dtype
         flags |= _lib.FLAG_FORCE_SIMT
@@ -154,7 +167,7 @@ def chunk_hrdplr_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state
                                 _lib.ptr(gk), float(scale), _lib.ptr(h0), _lib.ptr(o), _lib.ptr(ht),
                                 _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
     _lib.check(rc, "hdla_chunk_fwd")
-    if q.dtype == torch.bfloat16 and not (dims.flags & _lib.FLAG_FORCE_SIMT):
+    if lib.hdla_chunk_uses_tensor_cores(C.byref(dims)):
         with torch.cuda.device(dev):
             _post_status(ws, dev)
     if _keep_ws:

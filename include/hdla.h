@@ -111,6 +111,10 @@ HDLA_API size_t hdla_timing_report(char* buf, size_t size);
  * HRDPLR/bwd_func.py:33-36,84-86,139,181-185,238-241,300-309. */
 HDLA_API size_t hdla_chunk_workspace_bytes(const HdlaDims* dims, int with_backward);
 
+/* 1 if hdla_chunk_fwd / hdla_chunk_bwd run these dims on the bf16 tensor-core pipeline (and so write the status
+ * words described below), 0 if on the fp32 CUDA-core pipeline.  No counterpart in the reference. */
+HDLA_API int hdla_chunk_uses_tensor_cores(const HdlaDims* dims);
+
 /* Debugging aid for tests: converts one named bf16 tile buffer of the tensor-core workspace
  * ("Qh","Kh","Ah","Bh","Vc","Aqk","Aqb","Aak","Aab","M","W","P","U","Hs","V2") to fp32 row-major
  * [B*H*NT][rows][cols] in `out` (device memory), or copies "E" / the 4-byte "status" word.  It has no

@@ -345,3 +345,22 @@ def test_rms_norm_fused_gate_forward_backward(dev, dtype, tol):
     assert orc.rel_err(o, ro) < tol
     for got, ref, n in zip(grads, rgrads, ("dx", "dgate", "dweight")):
         assert orc.rel_err(got, ref) < tol, n
+
+
+def test_bf16_requested_chunk_16_runs_on_tensor_cores(dev, monkeypatch):
+    """The reference layer passes chunk_size=16; the result is chunk-size independent, so supported bf16
+    problems still take the tensor-core pipeline (10 launches for forward+backward, not the 43 of the fp32 one)."""
+    import hdla_impl_b200 as H
+    from hdla_impl_b200 import _lib
+    x = make_inputs(1, 256, 2, 128, 128, R, seed=17, dtype=torch.bfloat16, with_dht=True)
+    n0 = _lib.kernel_launches()
+    a = run_chunk(x, dev, 1.0, 16, False, True, torch.bfloat16)
+    assert _lib.kernel_launches() - n0 == 10
+    b = run_chunk(x, dev, 1.0, 64, False, True, torch.bfloat16)
+    for n in a:
+        assert torch.equal(a[n], b[n]), n
+    monkeypatch.setenv("HDLA_HONOR_CHUNK", "1")
+    c = run_chunk(x, dev, 1.0, 16, False, True, torch.bfloat16)      # fp32 pipeline at chunk 16
+    ref = oracle_chunk(x, 1.0, False, True, torch.bfloat16)
+    assert_close(c, ref, 2e-2, "chunk 16 honoured")
+    assert_close(a, ref, 2e-2, "chunk 16 requested")
