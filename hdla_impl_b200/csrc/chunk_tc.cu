@@ -34,6 +34,8 @@ struct TcPlan {
     int B, T, H, NT, BH;
     long long G;
     size_t status, Qh, Kh, Ah, Bh, Vc, E, ghat, Aqk, Aqb, Aak, Aab, M, W, P, U, Hs, V2, HT, zero;
+    int nseg, seg_len;                 // two-level scan: segments per sequence, chunks per segment
+    size_t Tseg, Fseg, Sin;            // per (b, h, segment): transition [K,K], state from zero [K,V], entering state [K,V]
     size_t dOc, dAqk, dAqb, DV2, DE, dgl, dW, dP, dAak, dM, tmp, dAab, dQh, dKh, dAh, dBh;
     size_t total_fwd, total;
 };
@@ -57,6 +59,15 @@ TcPlan make_tc_plan(const HdlaDims& d) {
     p.W = take(32768); p.P = take(32768); p.U = take(32768); p.Hs = take(32768); p.V2 = take(32768);
     p.HT = off; off += (((size_t)p.BH * K * V * 4 + 255) / 256) * 256;
     p.zero = off; off += 32768;
+    // Few (batch, head) pairs leave most SMs idle during the serial scan: cut each sequence into segments that
+    // are scanned concurrently (transition + state-from-zero per segment, composed, then the real scan).
+    p.nseg = 1;
+    while (p.nseg < 8 && 2 * p.BH * (p.nseg * 2) <= 148 && p.NT / (p.nseg * 2) >= 4) p.nseg *= 2;
+    p.seg_len = (p.NT + p.nseg - 1) / p.nseg;
+    const size_t slots = (size_t)p.BH * p.nseg;
+    p.Tseg = off; off += p.nseg > 1 ? slots * K * K * 4 : 0;
+    p.Fseg = off; off += p.nseg > 1 ? slots * K * V * 4 : 0;
+    p.Sin = off; off += p.nseg > 1 ? slots * K * V * 4 : 0;
     p.total_fwd = off;
     p.dOc = take(16384); p.dAqk = take(8192); p.dAqb = take(16384); p.DV2 = take(32768); p.DE = take(32768);
     p.dgl = take(K * 4); p.dW = take(32768); p.dP = take(32768); p.dAak = take(16384); p.dM = take(32768);
@@ -550,6 +561,15 @@ struct ScanTcP {
     int add_stride, r1_stride;               // chunk strides of ADD / R1 in tiles: 1, or 0 for one shared (zero) tile
     int no_store;                            // 1: do not write CK, Y, dgl (state-only passes)
     int init_identity;                       // 1: start from the K x K identity (transition pass, needs K == V)
+    // two-level scan: the chunks of a sequence are cut into nseg segments of seg_len chunks, one CTA each
+    // (grid.x = B*H*nseg).  State buffers are then indexed by slot = bh*nseg + seg where *_by_slot is set.
+    int nseg, seg_len;
+    int init_by_slot, fin_by_slot;
+    int fin_last_only;                       // write fin / fin2 only from the segment that ends the scan
+    // dual mode (grid.y = 2): CTAs with blockIdx.y == 1 run the transition pass instead (identity start, no
+    // inputs) and write their result to fin_transition[slot]
+    const uint4* zero_tile;
+    float* fin_transition;
 };
 
 __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
@@ -564,13 +584,20 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     __shared__ __align__(8) uint64_t ldA, ldB, barA, barB;
     __shared__ uint32_t tmem_s;
     __shared__ float red[K];
-    const int bh = blockIdx.x;
+    const int bh = blockIdx.x / p.nseg, seg = blockIdx.x % p.nseg;
+    const long long slot = blockIdx.x;
+    if (blockIdx.y == 1) {                   // transition twin of this segment
+        p.ADD = p.zero_tile; p.R1 = p.zero_tile; p.add_stride = 0; p.r1_stride = 0;
+        p.init_identity = 1; p.init = nullptr; p.fin = p.fin_transition; p.fin2 = nullptr;
+    }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row = (warp & 3) * 32 + lane;
     const int half = warp >> 2;
     if (warp == 0) { tmem_alloc(&tmem_s, 256); tmem_relinquish(); }
     const long long g0 = (long long)bh * p.NT;
-    const int n_first = p.reverse ? p.NT - 1 : 0, dn = p.reverse ? -1 : 1;
+    const int n_lo = seg * p.seg_len, n_hi = min(p.NT, n_lo + p.seg_len);
+    const int steps = n_hi - n_lo;
+    const int n_first = p.reverse ? n_hi - 1 : n_lo, dn = p.reverse ? -1 : 1;
     if (tid == 0) {
         const long long g = g0 + n_first;
         mbar_init(&ldA, 1); mbar_init(&ldB, 1); mbar_init(&barA, 1); mbar_init(&barB, 1); fence_mbar_init();
@@ -587,7 +614,8 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
 #pragma unroll
         for (int j = 0; j < 64; ++j) S[j] = (half * 64 + j == row) ? 1.f : 0.f;
     } else if (p.init) {
-        const float4* src = reinterpret_cast<const float4*>(p.init + ((size_t)bh * K + row) * V + half * 64);
+        const size_t is = p.init_by_slot ? (size_t)slot : (size_t)bh;
+        const float4* src = reinterpret_cast<const float4*>(p.init + (is * K + row) * V + half * 64);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float4 x = src[j];
@@ -603,11 +631,11 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     const uint32_t tmem = tmem_s;
     const Tile tA1 = t8::tile(sA1, 128), tL1 = t8::tile(sL1, 64), tR1 = t8::tile(sR1, 64), tL2 = t8::tile(sL2, 128),
                tT = t8::tile(sT, 128), tY = t8::tile(sY, 128);
-    for (int it = 0; it < p.NT; ++it) {
+    for (int it = 0; it < steps; ++it) {
         const int n = n_first + it * dn;
         const long long g = g0 + n;
         const uint32_t ph = it & 1;
-        const bool more = it + 1 < p.NT;
+        const bool more = it + 1 < steps;
         const float e = p.E[(size_t)g * K + row];
         float part = 0.f;
         if (p.reverse && !p.no_store) {       // dgl = rowsum(dS (.) S_{n+1})
@@ -701,13 +729,16 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         }
         tc_fence_before();
     }
-    {
-        const size_t off = ((size_t)bh * K + row) * V + half * 64;
+    const bool ends_scan = p.reverse ? (seg == 0) : (seg == p.nseg - 1);
+    if (!p.fin_last_only || ends_scan) {
+        const size_t fs = p.fin_by_slot ? (size_t)slot : (size_t)bh;
+        const size_t off = (fs * K + row) * V + half * 64;
+        const size_t off2 = ((size_t)bh * K + row) * V + half * 64;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float4 x = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
             if (p.fin) reinterpret_cast<float4*>(p.fin + off)[j] = x;
-            if (p.fin2) reinterpret_cast<float4*>(p.fin2 + off)[j] = x;
+            if (p.fin2) reinterpret_cast<float4*>(p.fin2 + off2)[j] = x;
         }
     }
     __syncthreads();
@@ -1263,6 +1294,46 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
+// ------------------------------------------------------------------------------------------
+// two-level scan, composition step: the state entering each segment from the per-segment affine maps
+//   forward:  Sin[0] = S0,            Sin[s+1] = T[s] Sin[s] + F[s]
+//   reverse:  Sin[P-1] = D (dht),     Sin[s-1] = T[s]^T Sin[s] + F[s]        (F = per-segment gradient from zero)
+// fp32 CUDA-core products, one CTA per (batch*head, 32 columns); the chain over segments is serial but short.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) compose_segments_kernel(const float* T, const float* F, const float* S0,
+                                                               float* Sin, int nseg, int reverse) {
+    __shared__ float cur[K][33];
+    const int bh = blockIdx.x, c0 = blockIdx.y * 32, k = threadIdx.x;
+    float x[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) x[c] = S0 ? S0[((size_t)bh * K + k) * V + c0 + c] : 0.f;
+    const int first = reverse ? nseg - 1 : 0, step = reverse ? -1 : 1;
+    for (int i = 0; i < nseg; ++i) {
+        const int sgm = first + i * step;
+        const size_t slot = (size_t)bh * nseg + sgm;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+            Sin[(slot * K + k) * V + c0 + c] = x[c];
+            cur[k][c] = x[c];
+        }
+        __syncthreads();
+        if (i + 1 < nseg) {
+            const float* Tm = T + slot * K * K;
+            float acc[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) acc[c] = F[(slot * K + k) * V + c0 + c];
+            for (int j = 0; j < K; ++j) {
+                const float t = reverse ? Tm[(size_t)j * K + k] : Tm[(size_t)k * K + j];
+#pragma unroll
+                for (int c = 0; c < 32; ++c) acc[c] = fmaf(t, cur[j][c], acc[c]);
+            }
+#pragma unroll
+            for (int c = 0; c < 32; ++c) x[c] = acc[c];
+        }
+        __syncthreads();
+    }
+}
+
 constexpr int kGradSmem = 5 * 32768 + 3 * 16384 + 2 * 8192;
 constexpr int kWySmem = 6 * 32768 + 16384;
 
@@ -1330,28 +1401,50 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         HDLA_CHECK_LAUNCH("wu_tc_kernel");
         if (phase == HDLA_PHASE_PRE) return HDLA_OK;
     }
+    auto scan_params = [&](const float* init, uint4* ck, uint4* y, float* fin, float* fin2, int no_store) {
+        ScanTcP sp{};
+        sp.A1 = U4(pl.W); sp.ADD = U4(pl.U); sp.L1 = U4(pl.Kh); sp.R1 = U4(pl.Vc); sp.L2 = U4(pl.Bh); sp.E = F(pl.E);
+        sp.init = init; sp.CK = ck; sp.Y = y; sp.fin = fin; sp.fin2 = fin2;
+        sp.NT = pl.NT; sp.reverse = 0; sp.status = status; sp.add_stride = 1; sp.r1_stride = 1; sp.no_store = no_store;
+        sp.nseg = 1; sp.seg_len = pl.NT; sp.zero_tile = U4(pl.zero);
+        return sp;
+    };
     if (phase == HDLA_PHASE_TRANSITION) {
         // chunk transition matrices composed over this call's chunks: state K x K from the identity,
         // no inputs (u = 0, v = 0):  X <- E (.) (I + Bh^T Wh) (E (.) X)
         if (!ht) return fail(HDLA_ERR_INVALID, "transition pass needs the output pointer (ht)");
-        ScanTcP sp{U4(pl.W), U4(pl.zero), U4(pl.Kh), U4(pl.zero), U4(pl.Bh), F(pl.E), nullptr, nullptr, nullptr, ht,
-                   nullptr, nullptr, nullptr, nullptr, pl.NT, 0, status, 0, 0, 1, 1};
+        ScanTcP sp = scan_params(nullptr, nullptr, nullptr, ht, nullptr, 1);
+        sp.ADD = U4(pl.zero); sp.R1 = U4(pl.zero); sp.add_stride = 0; sp.r1_stride = 0; sp.init_identity = 1;
         scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         return HDLA_OK;
     }
     if (phase == HDLA_PHASE_STATE) {
         if (!ht) return fail(HDLA_ERR_INVALID, "state pass needs the output pointer (ht)");
-        ScanTcP sp{U4(pl.W), U4(pl.U), U4(pl.Kh), U4(pl.Vc), U4(pl.Bh), F(pl.E), h0, nullptr, nullptr, ht, nullptr,
-                   nullptr, nullptr, nullptr, pl.NT, 0, status, 1, 1, 1, 0};
+        ScanTcP sp = scan_params(h0, nullptr, nullptr, ht, nullptr, 1);
         scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         return HDLA_OK;
     }
-    ScanTcP sp{U4(pl.W), U4(pl.U), U4(pl.Kh), U4(pl.Vc), U4(pl.Bh), F(pl.E), h0, U4(pl.Hs), U4(pl.V2), ht, F(pl.HT),
-               nullptr, nullptr, nullptr, pl.NT, 0, status, 1, 1, 0, 0};
-    scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
-    HDLA_CHECK_LAUNCH("scan_tc_kernel");
+    if (pl.nseg > 1 && phase == HDLA_PHASE_ALL) {
+        // two-level scan: per segment, transition and state-from-zero side by side (grid.y = 2) ...
+        ScanTcP s1 = scan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
+        s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1; s1.fin_transition = F(pl.Tseg);
+        scan_tc_kernel<<<dim3(pl.BH * pl.nseg, 2), 256, 196608, st>>>(s1);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+        // ... composed into the state entering every segment ...
+        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), pl.nseg, 0);
+        HDLA_CHECK_LAUNCH("compose_segments_kernel");
+        // ... and the real scan of all segments at once
+        ScanTcP s2 = scan_params(F(pl.Sin), U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
+        s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;
+        scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s2);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+    } else {
+        ScanTcP sp = scan_params(h0, U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
+        scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+    }
     if (need_o) {
         OutP op{U4(pl.Qh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Vc), U4(pl.Hs), U4(pl.V2), (__nv_bfloat16*)o, d.T, d.H,
                 pl.NT, status};
@@ -1387,20 +1480,41 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         if (phase == HDLA_PHASE_PRE) return HDLA_OK;
     }
     if (phase == HDLA_PHASE_TRANSITION) return fail(HDLA_ERR_INVALID, "the transition pass belongs to the forward call");
+    auto rscan_params = [&](const float* init, uint4* ck, uint4* y, float* fin, float* dgl, int no_store) {
+        ScanTcP sp{};
+        sp.A1 = U4(pl.Bh); sp.ADD = U4(pl.DV2); sp.L1 = U4(pl.Qh); sp.R1 = U4(pl.dOc); sp.L2 = U4(pl.W); sp.E = F(pl.E);
+        sp.init = init; sp.CK = ck; sp.Y = y; sp.fin = fin; sp.fin2 = nullptr;
+        sp.Hs = U4(pl.Hs); sp.HT = F(pl.HT); sp.dgl = dgl;
+        sp.NT = pl.NT; sp.reverse = 1; sp.status = status; sp.add_stride = 1; sp.r1_stride = 1; sp.no_store = no_store;
+        sp.nseg = 1; sp.seg_len = pl.NT; sp.zero_tile = U4(pl.zero);
+        return sp;
+    };
     if (phase == HDLA_PHASE_STATE) {
         // state gradient leaving this call's first chunk for the given incoming dht; nothing is stored
         if (!dh0) return fail(HDLA_ERR_INVALID, "state pass needs the output pointer (dh0)");
-        ScanTcP sp{U4(pl.Bh), U4(pl.DV2), U4(pl.Qh), U4(pl.dOc), U4(pl.W), F(pl.E), dht, nullptr, nullptr, dh0, nullptr,
-                   U4(pl.Hs), F(pl.HT), nullptr, pl.NT, 1, status, 1, 1, 1, 0};
+        ScanTcP sp = rscan_params(dht, nullptr, nullptr, dh0, nullptr, 1);
         scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         return HDLA_OK;
     }
     // --- dhu: reverse scan (dv2 is accumulated in place over dv2_intra)
-    ScanTcP sp{U4(pl.Bh), U4(pl.DV2), U4(pl.Qh), U4(pl.dOc), U4(pl.W), F(pl.E), dht, U4(pl.DE), U4(pl.DV2), dh0, nullptr,
-               U4(pl.Hs), F(pl.HT), F(pl.dgl), pl.NT, 1, status, 1, 1, 0, 0};
-    scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
-    HDLA_CHECK_LAUNCH("scan_tc_kernel");
+    if (pl.nseg > 1 && phase == HDLA_PHASE_ALL) {
+        // two-level reverse scan; the segment transitions were left in the workspace by the forward pass
+        ScanTcP s1 = rscan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
+        s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1;
+        scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), pl.nseg, 1);
+        HDLA_CHECK_LAUNCH("compose_segments_kernel");
+        ScanTcP s2 = rscan_params(F(pl.Sin), U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
+        s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;
+        scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s2);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+    } else {
+        ScanTcP sp = rscan_params(dht, U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
+        scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+    }
     // --- wy: dWh, dP, dAak, dAab in one kernel
     WyBwdP wyp{U4(pl.M), U4(pl.DV2), U4(pl.Hs), U4(pl.Vc), U4(pl.P), U4(pl.Ah), U4(pl.dW), U4(pl.dP), U4(pl.dAak),
                U4(pl.dAab), status};
