@@ -1300,28 +1300,32 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
 //   reverse:  Sin[P-1] = D (dht),     Sin[s-1] = T[s]^T Sin[s] + F[s]        (F = per-segment gradient from zero)
 // fp32 CUDA-core products, one CTA per (batch*head, 32 columns); the chain over segments is serial but short.
 // ------------------------------------------------------------------------------------------
+// With s0_identity the start is the identity and F is ignored (composition of the transitions themselves); `fin`
+// (optional) receives the state after the last segment.
 __global__ void __launch_bounds__(128) compose_segments_kernel(const float* T, const float* F, const float* S0,
-                                                               float* Sin, int nseg, int reverse) {
+                                                               float* Sin, float* fin, int nseg, int reverse,
+                                                               int s0_identity) {
     __shared__ float cur[K][33];
     const int bh = blockIdx.x, c0 = blockIdx.y * 32, k = threadIdx.x;
     float x[32];
 #pragma unroll
-    for (int c = 0; c < 32; ++c) x[c] = S0 ? S0[((size_t)bh * K + k) * V + c0 + c] : 0.f;
+    for (int c = 0; c < 32; ++c)
+        x[c] = s0_identity ? (c0 + c == k ? 1.f : 0.f) : (S0 ? S0[((size_t)bh * K + k) * V + c0 + c] : 0.f);
     const int first = reverse ? nseg - 1 : 0, step = reverse ? -1 : 1;
     for (int i = 0; i < nseg; ++i) {
         const int sgm = first + i * step;
         const size_t slot = (size_t)bh * nseg + sgm;
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-            Sin[(slot * K + k) * V + c0 + c] = x[c];
+            if (Sin) Sin[(slot * K + k) * V + c0 + c] = x[c];
             cur[k][c] = x[c];
         }
         __syncthreads();
-        if (i + 1 < nseg) {
+        if (i + 1 < nseg || fin) {
             const float* Tm = T + slot * K * K;
             float acc[32];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) acc[c] = F[(slot * K + k) * V + c0 + c];
+            for (int c = 0; c < 32; ++c) acc[c] = s0_identity ? 0.f : F[(slot * K + k) * V + c0 + c];
             for (int j = 0; j < K; ++j) {
                 const float t = reverse ? Tm[(size_t)j * K + k] : Tm[(size_t)k * K + j];
 #pragma unroll
@@ -1331,6 +1335,10 @@ __global__ void __launch_bounds__(128) compose_segments_kernel(const float* T, c
             for (int c = 0; c < 32; ++c) x[c] = acc[c];
         }
         __syncthreads();
+    }
+    if (fin) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) fin[((size_t)bh * K + k) * V + c0 + c] = x[c];
     }
 }
 
@@ -1413,6 +1421,18 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         // chunk transition matrices composed over this call's chunks: state K x K from the identity,
         // no inputs (u = 0, v = 0):  X <- E (.) (I + Bh^T Wh) (E (.) X)
         if (!ht) return fail(HDLA_ERR_INVALID, "transition pass needs the output pointer (ht)");
+        if (pl.nseg > 1) {
+            // per-segment transitions and states-from-zero side by side, then the product of the transitions;
+            // both stay in the workspace for the STATE and POST phases of this sequence slice
+            ScanTcP s1 = scan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
+            s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1; s1.fin_transition = F(pl.Tseg);
+            scan_tc_kernel<<<dim3(pl.BH * pl.nseg, 2), 256, 196608, st>>>(s1);
+            HDLA_CHECK_LAUNCH("scan_tc_kernel");
+            compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, nullptr, ht,
+                                                                         pl.nseg, 0, 1);
+            HDLA_CHECK_LAUNCH("compose_segments_kernel");
+            return HDLA_OK;
+        }
         ScanTcP sp = scan_params(nullptr, nullptr, nullptr, ht, nullptr, 1);
         sp.ADD = U4(pl.zero); sp.R1 = U4(pl.zero); sp.add_stride = 0; sp.r1_stride = 0; sp.init_identity = 1;
         scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
@@ -1421,19 +1441,27 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     }
     if (phase == HDLA_PHASE_STATE) {
         if (!ht) return fail(HDLA_ERR_INVALID, "state pass needs the output pointer (ht)");
+        if (pl.nseg > 1) {                    // affine maps of the segments are in the workspace (TRANSITION phase)
+            compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), h0, nullptr, ht,
+                                                                         pl.nseg, 0, 0);
+            HDLA_CHECK_LAUNCH("compose_segments_kernel");
+            return HDLA_OK;
+        }
         ScanTcP sp = scan_params(h0, nullptr, nullptr, ht, nullptr, 1);
         scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         return HDLA_OK;
     }
-    if (pl.nseg > 1 && phase == HDLA_PHASE_ALL) {
+    if (pl.nseg > 1) {
         // two-level scan: per segment, transition and state-from-zero side by side (grid.y = 2) ...
-        ScanTcP s1 = scan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
-        s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1; s1.fin_transition = F(pl.Tseg);
-        scan_tc_kernel<<<dim3(pl.BH * pl.nseg, 2), 256, 196608, st>>>(s1);
-        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+        if (phase == HDLA_PHASE_ALL) {        // (a phased POST call finds them in the workspace)
+            ScanTcP s1 = scan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
+            s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1; s1.fin_transition = F(pl.Tseg);
+            scan_tc_kernel<<<dim3(pl.BH * pl.nseg, 2), 256, 196608, st>>>(s1);
+            HDLA_CHECK_LAUNCH("scan_tc_kernel");
+        }
         // ... composed into the state entering every segment ...
-        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), pl.nseg, 0);
+        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), nullptr, pl.nseg, 0, 0);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         // ... and the real scan of all segments at once
         ScanTcP s2 = scan_params(F(pl.Sin), U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
@@ -1492,19 +1520,31 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     if (phase == HDLA_PHASE_STATE) {
         // state gradient leaving this call's first chunk for the given incoming dht; nothing is stored
         if (!dh0) return fail(HDLA_ERR_INVALID, "state pass needs the output pointer (dh0)");
+        if (pl.nseg > 1) {                    // per-segment gradients from zero, then composed with T^T
+            ScanTcP s1 = rscan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
+            s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1;
+            scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
+            HDLA_CHECK_LAUNCH("scan_tc_kernel");
+            compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), dht, nullptr, dh0,
+                                                                         pl.nseg, 1, 0);
+            HDLA_CHECK_LAUNCH("compose_segments_kernel");
+            return HDLA_OK;
+        }
         ScanTcP sp = rscan_params(dht, nullptr, nullptr, dh0, nullptr, 1);
         scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         return HDLA_OK;
     }
     // --- dhu: reverse scan (dv2 is accumulated in place over dv2_intra)
-    if (pl.nseg > 1 && phase == HDLA_PHASE_ALL) {
+    if (pl.nseg > 1) {
         // two-level reverse scan; the segment transitions were left in the workspace by the forward pass
-        ScanTcP s1 = rscan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
-        s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1;
-        scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
-        HDLA_CHECK_LAUNCH("scan_tc_kernel");
-        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), pl.nseg, 1);
+        if (phase == HDLA_PHASE_ALL) {        // (a phased POST call finds the per-segment gradients in the workspace)
+            ScanTcP s1 = rscan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
+            s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1;
+            scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
+            HDLA_CHECK_LAUNCH("scan_tc_kernel");
+        }
+        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), nullptr, pl.nseg, 1, 0);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         ScanTcP s2 = rscan_params(F(pl.Sin), U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
         s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;

@@ -61,8 +61,10 @@ extern "C" {
  *   PHASE_STATE       forward: ht <- state after this call's chunks from h0, nothing else written;
  *                     backward: dh0 <- state gradient entering this call's first chunk from dht
  *   PHASE_POST        forward: scan + output;  backward: reverse scan + all gradients
- * Phased calls use one workspace (sized with_backward = 1) across all phases; backward phases need
- * HDLA_FLAG_WS_HOLDS_FWD.  The bf16 tensor-core pipeline implements them; other problems report
+ * Phased calls use one workspace (sized with_backward = 1) across all phases, in the order PRE, TRANSITION,
+ * STATE, POST (forward) and PRE, STATE, POST (backward): later phases reuse what earlier ones left in the
+ * workspace (for long slices the scan itself is split into concurrently scanned segments whose affine maps
+ * are kept there).  Backward phases need HDLA_FLAG_WS_HOLDS_FWD.  The bf16 tensor-core pipeline implements them; other problems report
  * HDLA_ERR_UNSUPPORTED. */
 #define HDLA_PHASE_MASK        0xF0
 #define HDLA_PHASE_ALL         0x00

@@ -15,7 +15,7 @@ def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
 
 
-def _worker(rank, world, port, out):
+def _worker(rank, world, port, T, out):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     dev = torch.device("cuda", rank)
@@ -27,7 +27,7 @@ def _worker(rank, world, port, out):
         from hdla_impl_b200.sharding import shard_time
         from hdla_impl_b200.synthetic import make_inputs
         from oracle import hdla_oracle as orc
-        T, C = 512, 64
+        C = 64
         x = make_inputs(1, T, 2, 128, 128, R, seed=4, dtype=torch.bfloat16, h0_std=0.1, with_dht=True)
         x["gk"] = x["gk"].float()
         names = ("q", "k", "v", "a", "b", "gk")
@@ -59,11 +59,12 @@ def _worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
-def test_context_parallel_two_gpus_matches_one_gpu():
+@pytest.mark.parametrize("T", [512, 4096])      # 4096: 32 chunks per rank, scanned as 4 concurrent segments
+def test_context_parallel_two_gpus_matches_one_gpu(T):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), T, out), nprocs=2, join=True)
     # the two paths round the boundary state differently (bf16 checkpoints): bf16 tolerance
     assert len(out) == 2 and max(out.values()) < 2e-2, dict(out)
