@@ -631,14 +631,36 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     const uint32_t tmem = tmem_s;
     const Tile tA1 = t8::tile(sA1, 128), tL1 = t8::tile(sL1, 64), tR1 = t8::tile(sR1, 64), tL2 = t8::tile(sL2, 128),
                tT = t8::tile(sT, 128), tY = t8::tile(sY, 128);
+    float e_next = steps > 0 ? p.E[(size_t)(g0 + n_first) * K + row] : 0.f;
     for (int it = 0; it < steps; ++it) {
         const int n = n_first + it * dn;
         const long long g = g0 + n;
         const uint32_t ph = it & 1;
         const bool more = it + 1 < steps;
-        const float e = p.E[(size_t)g * K + row];
+        const float e = e_next;                                  // loaded one chunk ahead: off the critical path
+        if (more) e_next = p.E[(size_t)(g + dn) * K + row];
+        // T = E (.) X  -> operand tile and checkpoint
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = e * S[c8 * 8 + j];
+            const uint4 c = t8::pack8(f);
+            const int cg = half * 8 + c8;
+            sT[cg * 128 + row] = c;
+            if (!p.no_store) p.CK[g * CH128 + cg * 128 + row] = c;
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            wait_or_flag(&ldA, ph, p.status, 11);
+            tc_fence_after();
+            t8::mma_chain<false, true>(tmem, tA1, 0, 0, tT, 0, 0, 128, 128, false);      // A1 T
+            umma_commit(&barA);
+        }
         float part = 0.f;
-        if (p.reverse && !p.no_store) {       // dgl = rowsum(dS (.) S_{n+1})
+        if (p.reverse && !p.no_store) {       // dgl = rowsum(dS (.) S_{n+1}), computed while the product runs
             if (n + 1 < p.NT) {
                 const float inv = 1.f / p.E[(size_t)(g + 1) * K + row];
 #pragma unroll
@@ -658,27 +680,6 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
                 }
             }
             if (half == 1) red[row] = part;
-        }
-        // T = E (.) X  -> operand tile and checkpoint
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-            float f[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = e * S[c8 * 8 + j];
-            const uint4 c = t8::pack8(f);
-            const int cg = half * 8 + c8;
-            sT[cg * 128 + row] = c;
-            if (!p.no_store) p.CK[g * CH128 + cg * 128 + row] = c;
-        }
-        fence_proxy_async();
-        tc_fence_before();
-        __syncthreads();
-        if (p.reverse && !p.no_store && half == 0) p.dgl[(size_t)g * K + row] = part + red[row];
-        if (tid == 0) {
-            wait_or_flag(&ldA, ph, p.status, 11);
-            tc_fence_after();
-            t8::mma_chain<false, true>(tmem, tA1, 0, 0, tT, 0, 0, 128, 128, false);      // A1 T
-            umma_commit(&barA);
         }
         wait_or_flag(&barA, ph, p.status, 12);
         wait_or_flag(&ldA, ph, p.status, 13);         // ADD is read from shared memory below
@@ -701,6 +702,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
+        if (p.reverse && !p.no_store && half == 0) p.dgl[(size_t)g * K + row] = part + red[row];
         if (tid == 0) {
             if (more) {                                // A1 and ADD buffers are free: prefetch the next chunk's
                 mbar_expect_tx(&ldA, 65536);
