@@ -64,6 +64,7 @@ TcPlan make_tc_plan(const HdlaDims& d) {
     p.nseg = 1;
     while (p.nseg < 8 && 2 * p.BH * (p.nseg * 2) <= 148 && p.NT / (p.nseg * 2) >= 4) p.nseg *= 2;
     p.seg_len = (p.NT + p.nseg - 1) / p.nseg;
+    p.nseg = (p.NT + p.seg_len - 1) / p.seg_len;      // no empty segment when NT is not a multiple
     const size_t slots = (size_t)p.BH * p.nseg;
     p.Tseg = off; off += p.nseg > 1 ? slots * K * K * 4 : 0;
     p.Fseg = off; off += p.nseg > 1 ? slots * K * V * 4 : 0;

@@ -366,11 +366,12 @@ def test_bf16_requested_chunk_16_runs_on_tensor_cores(dev, monkeypatch):
     assert_close(a, ref, 2e-2, "chunk 16 requested")
 
 
-def test_bf16_two_level_scan_long_sequence(dev):
+@pytest.mark.parametrize("T", [2000, 2100])      # 32 chunks in 4 segments; 33 chunks in 7 segments of 5
+def test_bf16_two_level_scan_long_sequence(dev, T):
     """Few (batch, head) pairs and many chunks: the scan runs segment-parallel (transition + state-from-zero per
     segment, composed, then the real scan), forward and reverse.  T = 2000 -> 32 chunks in 4 segments, ragged tail,
     initial state and dht."""
-    x = make_inputs(1, 2000, 2, 128, 128, R, seed=18, dtype=torch.bfloat16, h0_std=0.2, with_dht=True)
+    x = make_inputs(1, T, 2, 128, 128, R, seed=18, dtype=torch.bfloat16, h0_std=0.2, with_dht=True)
     x["gk"] = x["gk"].float()
     got = run_chunk(x, dev, 128 ** -0.5, 64, True, True, torch.bfloat16)
     ref = oracle_chunk(x, 128 ** -0.5, True, True, torch.bfloat16)
