@@ -44,6 +44,8 @@ WORKLOADS = {
     # name: (B, T, H, K, V, C, dtype)
     "cfg1": (8, 4096, 16, 128, 128, 64, "bf16"),
     "cfg0": (2, 256, 4, 64, 64, 64, "f32"),
+    # profiling case: cfg 1 with a quarter of the batch (inputs still larger than L2, ~2 GB on the device)
+    "cfg1_small": (2, 4096, 16, 128, 128, 64, "bf16"),
     "cfg3": (1, 65536, 16, 128, 128, 64, "bf16"),
     # one layer of the 24-layer stack of cfg 4 (B32 sharded over the GPUs by batch): operator only
     "cfg4": (32, 4096, 16, 128, 128, 64, "bf16"),

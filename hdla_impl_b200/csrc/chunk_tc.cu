@@ -91,6 +91,26 @@ __device__ __forceinline__ void wait_idle_or_flag(uint64_t* bar, uint32_t parity
     }
 }
 
+#ifdef HDLA_TIMELINE
+// Optional tracing build (-DHDLA_TIMELINE): per-CTA time stamps of the last backward kernel's stages.
+__device__ unsigned long long g_timeline[16384 * 16];
+__device__ __forceinline__ void tl_mark(long long g, int i) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    if (g < 16384) {
+        g_timeline[g * 16 + i] = t;
+        if (i == 0) {
+            unsigned sm;
+            asm volatile("mov.u32 %0, %smid;" : "=r"(sm));
+            g_timeline[g * 16 + 15] = sm;
+        }
+    }
+}
+#define TL(i) tl_mark(g, i)
+#else
+#define TL(i)
+#endif
+
 // ------------------------------------------------------------------------------------------
 // K1: cumulative decay and hat operands (CUDA cores, streaming)
 //   gi = inclusive cumsum of gk within the chunk; ge = gi - gk (fla chunk_rwkv6_fwd_cumsum, call
@@ -110,6 +130,29 @@ struct PrepP {
 // channel they leave the bf16/fp32 exponent range and the caller must use the fp32 pipeline.
 constexpr float kMaxChunkDecay = 150.f;
 
+// the seven 16-byte input pieces one thread handles per step: (row r, column group kc) of q, k, v, a0, a1, b0, b1
+struct PrepIn { uint4 q, k, v, a0, a1, b0, b1; };
+
+__device__ __forceinline__ PrepIn prep_load(const PrepP& p, int b, int h, int t0, int valid, int blk, int lane) {
+    const int r = (blk >> 2) * 8 + (lane & 7);
+    const int kc = (blk & 3) * 4 + (lane >> 3);
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    PrepIn x{zero, zero, zero, zero, zero, zero, zero};
+    if (r < valid) {
+        const size_t src = (((size_t)b * p.T + t0 + r) * p.H + h) * K + kc * 8;
+        const size_t sa0 = (((size_t)b * p.T * R + (size_t)(t0 + r) * R) * p.H + h) * K + kc * 8;
+        const size_t sa1 = sa0 + (size_t)p.H * K;
+        x.q = __ldg(reinterpret_cast<const uint4*>(p.q + src));
+        x.k = __ldg(reinterpret_cast<const uint4*>(p.k + src));
+        x.v = __ldg(reinterpret_cast<const uint4*>(p.v + (((size_t)b * p.T + t0 + r) * p.H + h) * V + kc * 8));
+        x.a0 = __ldg(reinterpret_cast<const uint4*>(p.a + sa0));
+        x.a1 = __ldg(reinterpret_cast<const uint4*>(p.a + sa1));
+        x.b0 = __ldg(reinterpret_cast<const uint4*>(p.b + sa0));
+        x.b1 = __ldg(reinterpret_cast<const uint4*>(p.b + sa1));
+    }
+    return x;
+}
+
 __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
     __shared__ float gis[C][K + 4];
     __shared__ float tot[4][K];
@@ -119,22 +162,32 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
     const int t0 = n * C;
     const int valid = min(C, p.T - t0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // The kernel is a stream: keep loads in flight at all times. The first step's operand pieces are requested
+    // before the decay sums (they do not depend on them), and inside the loop the next step's pieces are
+    // requested before the current step's arithmetic and stores.
+    if (tid == 0) TL(0);
+    PrepIn cur = prep_load(p, b, h, t0, valid, warp * 8, lane);
     {   // two-level cumulative sum: warp w owns rows [16w, 16w+16), lane owns 4 columns
+        // (all sixteen loads are issued before the first value is used: the dtype branch stays outside the loops)
         float4 x[16];
+        const size_t row0 = (((size_t)b * p.T + t0 + warp * 16) * p.H + h) * K + lane * 4;
+        const size_t rstride = (size_t)p.H * K;
+        const int nrow = valid - warp * 16;                    // rows of this warp that exist
+        if (p.gdt == HDLA_F32) {
+            const float* src = static_cast<const float*>(p.gk) + row0;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const int r = warp * 16 + i;
-            x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (r < valid) {
-                const size_t src = (((size_t)b * p.T + t0 + r) * p.H + h) * K + lane * 4;
-                if (p.gdt == HDLA_F32) {
-                    x[i] = *reinterpret_cast<const float4*>(static_cast<const float*>(p.gk) + src);
-                } else {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.gk) + src);
-                    x[i] = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
-                                       __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
-                }
-            }
+            for (int i = 0; i < 16; ++i)
+                x[i] = i < nrow ? __ldg(reinterpret_cast<const float4*>(src + i * rstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+            const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.gk) + row0;
+            uint2 raw[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                raw[i] = i < nrow ? __ldg(reinterpret_cast<const uint2*>(src + i * rstride)) : make_uint2(0u, 0u);
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                x[i] = make_float4(__uint_as_float(raw[i].x << 16), __uint_as_float(raw[i].x & 0xffff0000u),
+                                   __uint_as_float(raw[i].y << 16), __uint_as_float(raw[i].y & 0xffff0000u));
         }
         float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -143,7 +196,9 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
             x[i] = run;
         }
         *reinterpret_cast<float4*>(&tot[warp][lane * 4]) = run;
+        if (tid == 0) TL(10);
         __syncthreads();
+        if (tid == 0) TL(11);
         float4 off = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int w = 0; w < warp; ++w) {
             const float4 t = *reinterpret_cast<const float4*>(&tot[w][lane * 4]);
@@ -155,6 +210,7 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
                 make_float4(x[i].x + off.x, x[i].y + off.y, x[i].z + off.z, x[i].w + off.w);
     }
     __syncthreads();
+    if (tid == 0) TL(1);
     if (tid < K) {
         const float gl = gis[C - 1][tid];
         p.E[(size_t)g * K + tid] = __expf(0.5f * gl);
@@ -162,12 +218,13 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
     }
     // hat operands: per instruction a warp covers 8 rows x 4 column groups, so every global access
     // is a run of full 32-byte sectors (64 B per row in, 128 B per column group out)
-    const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll 2
     for (int it = 0; it < 8; ++it) {
         const int blk = warp * 8 + it;                 // 32 blocks of (8 rows x 4 column groups)
         const int r = (blk >> 2) * 8 + (lane & 7);
         const int kc = (blk & 3) * 4 + (lane >> 3);
-        const bool rowok = r < valid;
+        PrepIn nxt = cur;
+        if (it < 7) nxt = prep_load(p, b, h, t0, valid, blk + 1, lane);
         float gi[8], ge[8], hf[8];
         {
             const float4 g0 = *reinterpret_cast<const float4*>(&gis[r][kc * 8]);
@@ -184,54 +241,51 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
             hf[0] = .5f * l0.x; hf[1] = .5f * l0.y; hf[2] = .5f * l0.z; hf[3] = .5f * l0.w;
             hf[4] = .5f * l1.x; hf[5] = .5f * l1.y; hf[6] = .5f * l1.z; hf[7] = .5f * l1.w;
         }
-        // all seven input chunks first (independent loads in flight together), then the arithmetic and stores
-        const size_t src = (((size_t)b * p.T + t0 + r) * p.H + h) * K + kc * 8;
-        const size_t sa0 = (((size_t)b * p.T * R + (size_t)(t0 + r) * R) * p.H + h) * K + kc * 8;
-        const size_t sa1 = sa0 + (size_t)p.H * K;
-        uint4 rq = zero, rk = zero, rv = zero, ra0 = zero, ra1 = zero, rb0 = zero, rb1 = zero;
-        if (rowok) {
-            rq = __ldg(reinterpret_cast<const uint4*>(p.q + src));
-            rk = __ldg(reinterpret_cast<const uint4*>(p.k + src));
-            rv = __ldg(reinterpret_cast<const uint4*>(p.v + (((size_t)b * p.T + t0 + r) * p.H + h) * V + kc * 8));
-            ra0 = __ldg(reinterpret_cast<const uint4*>(p.a + sa0));
-            ra1 = __ldg(reinterpret_cast<const uint4*>(p.a + sa1));
-            rb0 = __ldg(reinterpret_cast<const uint4*>(p.b + sa0));
-            rb1 = __ldg(reinterpret_cast<const uint4*>(p.b + sa1));
-        }
         float x[8], y[8], ep[8], em[8], ea[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             ep[j] = __expf(gi[j] - hf[j]); em[j] = __frcp_rn(ep[j]); ea[j] = __expf(ge[j] - hf[j]);
         }
-        t8::unpack8(rq, x);
+        t8::unpack8(cur.q, x);
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = x[j] * p.scale * ep[j];
         p.Qh[(size_t)g * CH64 + kc * 64 + r] = t8::pack8(y);
-        t8::unpack8(rk, x);
+        t8::unpack8(cur.k, x);
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
         p.Kh[(size_t)g * CH64 + kc * 64 + r] = t8::pack8(y);
-        p.Vc[(size_t)g * CH64 + kc * 64 + r] = rv;
-        t8::unpack8(ra0, x);
+        p.Vc[(size_t)g * CH64 + kc * 64 + r] = cur.v;
+        {   // rows 2r, 2r+1 of Ah / Bh are adjacent chunks: one 32-byte store each
+            uint4 c0, c1;
+            t8::unpack8(cur.a0, x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = x[j] * ea[j];
-        p.Ah[(size_t)g * CH128 + kc * 128 + r * R] = t8::pack8(y);
-        t8::unpack8(ra1, x);
+            for (int j = 0; j < 8; ++j) y[j] = x[j] * ea[j];
+            c0 = t8::pack8(y);
+            t8::unpack8(cur.a1, x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = x[j] * ea[j];
-        p.Ah[(size_t)g * CH128 + kc * 128 + r * R + 1] = t8::pack8(y);
-        t8::unpack8(rb0, x);
+            for (int j = 0; j < 8; ++j) y[j] = x[j] * ea[j];
+            c1 = t8::pack8(y);
+            sm100::st_global_32B(p.Ah + (size_t)g * CH128 + kc * 128 + r * R, c0, c1);
+            t8::unpack8(cur.b0, x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
-        p.Bh[(size_t)g * CH128 + kc * 128 + r * R] = t8::pack8(y);
-        t8::unpack8(rb1, x);
+            for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
+            c0 = t8::pack8(y);
+            t8::unpack8(cur.b1, x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
-        p.Bh[(size_t)g * CH128 + kc * 128 + r * R + 1] = t8::pack8(y);
-        float4* gh = reinterpret_cast<float4*>(p.ghat + (size_t)g * C * K + (size_t)r * K + kc * 8);
-        gh[0] = make_float4(gi[0] - hf[0], gi[1] - hf[1], gi[2] - hf[2], gi[3] - hf[3]);
-        gh[1] = make_float4(gi[4] - hf[4], gi[5] - hf[5], gi[6] - hf[6], gi[7] - hf[7]);
+            for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
+            c1 = t8::pack8(y);
+            sm100::st_global_32B(p.Bh + (size_t)g * CH128 + kc * 128 + r * R, c0, c1);
+            float gh[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) gh[j] = gi[j] - hf[j];
+            sm100::st_global_32B(p.ghat + (size_t)g * C * K + (size_t)r * K + kc * 8,
+                                 make_uint4(__float_as_uint(gh[0]), __float_as_uint(gh[1]), __float_as_uint(gh[2]), __float_as_uint(gh[3])),
+                                 make_uint4(__float_as_uint(gh[4]), __float_as_uint(gh[5]), __float_as_uint(gh[6]), __float_as_uint(gh[7])));
+        }
+        cur = nxt;
+        if (tid == 0) TL(2 + it);
     }
+    if (tid == 0) TL(12);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -932,15 +986,23 @@ __global__ void __launch_bounds__(128) dau_tc_kernel(DauP p) {
     {
         const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
         const int b = bh / p.H, h = bh % p.H;
+        uint4 c[8];                                    // all eight loads in flight before the first store
+#pragma unroll
         for (int it = 0; it < 8; ++it) {
             const int blk = warp * 8 + it;
             const int r = (blk >> 2) * 8 + (lane & 7);
             const int kc = (blk & 3) * 4 + (lane >> 3);
             const int t = n * C + r;
-            uint4 c = make_uint4(0, 0, 0, 0);
-            if (t < p.T) c = *reinterpret_cast<const uint4*>(p.d_o + (((size_t)b * p.T + t) * p.H + h) * V + kc * 8);
-            sdO[kc * 64 + r] = c;
-            p.dOc[g * CH64 + kc * 64 + r] = c;
+            c[it] = make_uint4(0, 0, 0, 0);
+            if (t < p.T) c[it] = __ldg(reinterpret_cast<const uint4*>(p.d_o + (((size_t)b * p.T + t) * p.H + h) * V + kc * 8));
+        }
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int blk = warp * 8 + it;
+            const int r = (blk >> 2) * 8 + (lane & 7);
+            const int kc = (blk & 3) * 4 + (lane >> 3);
+            sdO[kc * 64 + r] = c[it];
+            p.dOc[g * CH64 + kc * 64 + r] = c[it];
         }
     }
     fence_proxy_async();
@@ -1054,7 +1116,8 @@ __global__ void __launch_bounds__(128) out_tc_kernel(OutP p) {
             tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
             if (t < p.T) {
 #pragma unroll
-                for (int cg = 0; cg < 8; ++cg) dst[hh * 8 + cg] = t8::pack8(f + cg * 8);
+                for (int cg = 0; cg < 8; cg += 2)          // whole 32-byte sectors per lane (lanes are 4 KB apart)
+                    sm100::st_global_32B(dst + hh * 8 + cg, t8::pack8(f + cg * 8), t8::pack8(f + cg * 8 + 8));
             }
         }
     }
@@ -1092,10 +1155,10 @@ __global__ void c8_to_rowmajor_kernel(const uint4* src, float* dst, int rows, in
 //   P1 after L1, P2 after L2
 //   L3: dWh->A (after P1)  M->D dAab->E dAak->a (after P2);   P3 after L3
 //   L4: V2->A Ah->B Qh->D.lo v->D.hi (after P3);              P4, P5 after L4
-//   L5: Bh->A, ghat->C (after P4)
-// All five accumulators stay in TMEM (448 columns) until the end; then thread k walks the 64 tokens
-// backwards, un-gates (dq = scale e^{gi-half} dQh, ...), forms the running sum for dgk in registers
-// and writes every gradient in the public layout (a warp writes 32 adjacent channels of one token).
+// All five accumulators stay in TMEM (448 columns). Sixteen epilogue warps un-gate them (dq = scale e^{gi-half}
+// dQh, ...) and write every gradient in the public layout (a warp writes 32 adjacent channels of one token)
+// as soon as the product is complete -- dv and dq after P1/P2, da after P3, overlapping the later loads --
+// and after P4/P5 walk their tokens backwards for dk, db and the running sum of dgk.
 // ------------------------------------------------------------------------------------------
 struct GradP {
     const uint4 *Hs, *Bh, *dOc, *Kh, *dAqb, *dAqk, *DE, *dP, *Aak, *Aqk, *dW, *M, *dAab, *dAak, *V2, *Ah, *Qh, *Vc;
@@ -1129,14 +1192,15 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
     uint4* sc = sb + CH64;
     uint4* sx = sc + CH64;                               // 8 KB slots
     uint4* sy = sx + 512;
-    __shared__ __align__(8) uint64_t L1, L2, L3, L4, L5, m1, m2, m3, m4;
+    __shared__ __align__(8) uint64_t L1, L2, L3, L4, m1, m2, m3, m4;
     __shared__ uint32_t tmem_s;
     const long long g = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5;
     const bool producer = tid == 512;                   // lane 0 of the seventeenth warp loads tiles and issues MMAs
     if (warp == 0) { tmem_alloc(&tmem_s, 512); tmem_relinquish(); }
     if (producer) {
-        mbar_init(&L1, 1); mbar_init(&L2, 1); mbar_init(&L3, 1); mbar_init(&L4, 1); mbar_init(&L5, 1);
+        TL(0);
+        mbar_init(&L1, 1); mbar_init(&L2, 1); mbar_init(&L3, 1); mbar_init(&L4, 1);
         mbar_init(&m1, 1); mbar_init(&m2, 1); mbar_init(&m3, 1); mbar_init(&m4, 1);
         fence_mbar_init();
         mbar_expect_tx(&L1, 32768 + 32768 + 16384 + 16384 + 16384 + 8192);
@@ -1158,35 +1222,42 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
     const uint32_t tmem = tmem_s;
     // TMEM columns: dQh^T 0..63, dv^T 64..127, dAh^T 128..255, dBh^T 256..383, dKh^T 384..447
     if (producer) {
+        TL(1);
         wait_or_flag(&L1, 0, p.status, 40);
+        TL(2);
         chain0<false, false>(tmem, t8::tile(sA, 128), t8::tile(sa, 64), 64, 128, false);          // St dO^T
         chain0<true, false>(tmem, t8::tile(sb, 64), t8::tile(sx, 64), 64, 64, true);              // Kh^T dAqk^T
         chain0<true, false>(tmem, t8::tile(sB, 128), t8::tile(sc, 64), 64, 128, true);            // Bh^T dAqb^T
         umma_commit(&m1);
         wait_or_flag(&L2, 0, p.status, 41);
+        TL(3);
         chain0<true, false>(tmem + 64, t8::tile(sC, 128), t8::tile(sb, 64), 64, 128, false);      // dSt^T Kh^T
         chain0<true, true>(tmem + 64, t8::tile(sa, 64), t8::tile(sy, 64), 64, 64, true);          // dO^T Aqk
         chain0<true, true>(tmem + 64, t8::tile(sD, 128), t8::tile(sE, 128), 64, 128, true);       // dP^T Aak
         umma_commit(&m2);
         wait_or_flag(&m1, 0, p.status, 42);
         wait_or_flag(&m2, 0, p.status, 43);
+        TL(4);
         mbar_expect_tx(&L3, 32768 + 32768 + 32768 + 16384);
         bulk_g2s(sA, p.dW + g * CH128, 32768, &L3);
         bulk_g2s(sD, p.M + g * CH128, 32768, &L3);
         bulk_g2s(sE, p.dAab + g * CH128, 32768, &L3);
         bulk_g2s(sa, p.dAak + g * CH64, 16384, &L3);
         wait_or_flag(&L3, 0, p.status, 44);
+        TL(5);
         chain0<true, true>(tmem + 128, t8::tile(sA, 128), t8::tile(sD, 128), 128, 128, false);    // dWh^T M
         chain0<true, false>(tmem + 128, t8::tile(sb, 64), t8::tile(sa, 128), 128, 64, true);      // Kh^T dAak^T
         chain0<true, false>(tmem + 128, t8::tile(sB, 128), t8::tile(sE, 128), 128, 128, true);    // Bh^T dAab^T
         umma_commit(&m3);
         wait_or_flag(&m3, 0, p.status, 45);
+        TL(6);
         mbar_expect_tx(&L4, 32768 + 32768 + 16384 + 16384);
         bulk_g2s(sA, p.V2 + g * CH128, 32768, &L4);
         bulk_g2s(sB, p.Ah + g * CH128, 32768, &L4);
         bulk_g2s(sD, p.Qh + g * CH64, 16384, &L4);
         bulk_g2s(sD + CH64, p.Vc + g * CH64, 16384, &L4);
         wait_or_flag(&L4, 0, p.status, 46);
+        TL(7);
         chain0<false, false>(tmem + 256, t8::tile(sC, 128), t8::tile(sA, 128), 128, 128, false);  // dSt V2^T
         chain0<true, true>(tmem + 256, t8::tile(sD, 64), t8::tile(sc, 64), 128, 64, true);        // Qh^T dAqb
         chain0<true, true>(tmem + 256, t8::tile(sB, 128), t8::tile(sE, 128), 128, 128, true);     // Ah^T dAab
@@ -1195,105 +1266,130 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         chain0<true, true>(tmem + 384, t8::tile(sB, 128), t8::tile(sa, 128), 64, 128, true);      // Ah^T dAak
         umma_commit(&m4);
         wait_or_flag(&m4, 0, p.status, 47);
-        mbar_expect_tx(&L5, 65536);
-        bulk_g2s(sA, p.Bh + g * CH128, 32768, &L5);
-        bulk_g2s(sC, p.ghat + (size_t)g * C * K, 32768, &L5);      // fp32 [64][128] over the dSt slot
+        TL(8);
     }
     if (warp < 16) {
-        wait_idle_or_flag(&m4, 0, p.status, 48);
-        wait_idle_or_flag(&L5, 0, p.status, 49);
-    }
-    tc_fence_after();
-    if (warp < 16) {
-        // four warpgroups share the token loop (the work is latency bound): group w walks tokens
-        // 63-16w .. 48-16w and adds the totals of the groups above it to its running sums afterwards
+        // Sixteen epilogue warps in four token groups: group w owns tokens 48-16w .. 63-16w of the chunk and
+        // thread k of a group the channel k.  Everything that does not need the last products runs while the
+        // producer is still loading: the decay factors and this thread's Bh elements are fetched from global
+        // memory into registers at once, dv and dq are written as soon as P1 and P2 are complete, da after P3;
+        // only dk, db and the dgk sums wait for P4 and P5.
         float (*group_total)[K] = reinterpret_cast<float (*)[K]>(sy);      // 2 KB in the (consumed) Aqk slot
         const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
         const int b = bh / p.H, h = bh % p.H;
         const int k = tid & 127, wg = tid >> 7;
-        const float* gh = reinterpret_cast<const float*>(sC);
-        const float half = gh[(size_t)(C - 1) * K + k];
-        const float dgl = p.dgl[(size_t)g * K + k];
-        // per-thread element pointers into the four hat tiles (token i sits 16 bytes after token i-1)
-        const __nv_bfloat16* eq = reinterpret_cast<const __nv_bfloat16*>(sD + (k >> 3) * 64) + (k & 7);
-        const __nv_bfloat16* ek = reinterpret_cast<const __nv_bfloat16*>(sb + (k >> 3) * 64) + (k & 7);
-        const __nv_bfloat16* ea = reinterpret_cast<const __nv_bfloat16*>(sB + (k >> 3) * 128) + (k & 7);
-        const __nv_bfloat16* eb = reinterpret_cast<const __nv_bfloat16*>(sA + (k >> 3) * 128) + (k & 7);
-        const size_t tok_stride = (size_t)p.H * K;                    // elements between tokens in [B,T,H,K]
-        const size_t base_qk = (((size_t)b * p.T + (size_t)n * C) * p.H + h) * K + k;
-        const size_t base_ab = (((size_t)b * p.T + (size_t)n * C) * R * p.H + h) * K + k;
-        float run = 0.f;
-        float* dgk_loc = reinterpret_cast<float*>(sE);    // [64][128] fp32 over the (consumed) dAab slot
-        const int i_hi = 63 - 16 * wg;
-        float ep = __expf(gh[(size_t)i_hi * K + k]);
+        const int i_lo = 48 - 16 * wg;
         const int t_left = p.T - n * C;                               // tokens of this chunk that exist
-#pragma unroll 1
-        for (int ibl = 1; ibl >= 0; --ibl) {
-            const int ib = (3 - wg) * 2 + ibl;
-            uint32_t vq[8], vk[8], va[16], vb[16];
-            tmem_ld_x8(t8::taddr(tmem, warp, ib * 8), vq);
-            tmem_ld_x8(t8::taddr(tmem, warp, 384 + ib * 8), vk);
-            tmem_ld_x16(t8::taddr(tmem, warp, 128 + ib * 16), va);
-            tmem_ld_x16(t8::taddr(tmem, warp, 256 + ib * 16), vb);
-            tmem_wait_ld();
-            const int i0 = ib * 8;
-            const __nv_bfloat16 *bq = eq + i0 * 8, *bk = ek + i0 * 8, *ba = ea + i0 * 16, *bb = eb + i0 * 16;
-            const float* bg = gh + (size_t)i0 * K + k;
-            float* bd = dgk_loc + (size_t)i0 * K + k;
-            __nv_bfloat16 *oq = p.dq + base_qk + (size_t)i0 * tok_stride, *ok_ = p.dk + base_qk + (size_t)i0 * tok_stride;
-            __nv_bfloat16 *oa = p.da + base_ab + (size_t)i0 * R * tok_stride, *ob = p.db + base_ab + (size_t)i0 * R * tok_stride;
-#pragma unroll
-            for (int j = 7; j >= 0; --j) {
-                const bool ok = i0 + j < t_left;
-                const float xe = (i0 + j) > 0 ? bg[(j - 1) * K] : -half;           // ge - half
-                const float ee = __expf(xe);
-                const float em = __frcp_rn(ep);
-                const float dqh = __uint_as_float(vq[j]), dkh = __uint_as_float(vk[j]);
-                float d_gi = __bfloat162float(bq[j * 8]) * dqh - __bfloat162float(bk[j * 8]) * dkh;
-                float d_ge = 0.f;
-#pragma unroll
-                for (int rr = 0; rr < R; ++rr) {
-                    const float dah = __uint_as_float(va[2 * j + rr]), dbh = __uint_as_float(vb[2 * j + rr]);
-                    d_ge = fmaf(__bfloat162float(ba[(2 * j + rr) * 8]), dah, d_ge);
-                    d_gi = fmaf(-__bfloat162float(bb[(2 * j + rr) * 8]), dbh, d_gi);
-                    if (ok) {
-                        oa[(size_t)(2 * j + rr) * tok_stride] = __float2bfloat16_rn(ee * dah);
-                        ob[(size_t)(2 * j + rr) * tok_stride] = __float2bfloat16_rn(em * dbh);
-                    }
-                }
-                run += d_gi + d_ge;
-                bd[j * K] = run - d_ge + dgl;
-                if (ok) {
-                    oq[(size_t)j * tok_stride] = __float2bfloat16_rn(p.scale * ep * dqh);
-                    ok_[(size_t)j * tok_stride] = __float2bfloat16_rn(em * dkh);
-                }
-                ep = ee;                                  // e^{ghat} of token i-1
-            }
-        }
-        group_total[wg][k] = run;
-        asm volatile("bar.sync 1, 512;" ::: "memory");     // the sixteen epilogue warps only
-        float add = 0.f;
-        for (int w = 0; w < wg; ++w) add += group_total[w][k];
-#pragma unroll 4
-        for (int jj = 0; jj < 16; ++jj) {
-            const int i = (3 - wg) * 16 + jj;
-            const int t = n * C + i;
-            if (t < p.T) st_elem(p.dgk, (((size_t)b * p.T + t) * p.H + h) * K + k, p.gdt, dgk_loc[i * K + k] + add);
-        }
-        // dv: accumulator lane = value channel; each warpgroup writes 16 tokens
+        const size_t tok_stride = (size_t)p.H * K;                    // elements between tokens in [B,T,H,K]
+        const size_t base_qk = (((size_t)b * p.T + (size_t)n * C + i_lo) * p.H + h) * K + k;
+        const size_t base_ab = (((size_t)b * p.T + (size_t)n * C + i_lo) * R * p.H + h) * K + k;
+        // eg[j] = e^{ghat} of token i_lo + j - 1 (ghat = gi - half; the token before the chunk has ge - half = -half)
+        float eg[17];
+        uint32_t bhp[16];                                             // Bh rows 2i, 2i+1 of this thread's tokens
         {
-            uint32_t v[16];
+            const float* ghg = p.ghat + (size_t)g * C * K + k;
+            const float half = __ldg(ghg + (size_t)(C - 1) * K);
+#pragma unroll
+            for (int j = 0; j < 17; ++j) eg[j] = (i_lo + j - 1 >= 0) ? __ldg(ghg + (size_t)(i_lo + j - 1) * K) : -half;
+            const unsigned short* bg = reinterpret_cast<const unsigned short*>(p.Bh + g * CH128 + (k >> 3) * 128) + (k & 7);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const uint32_t lo = __ldg(bg + (size_t)(2 * (i_lo + j)) * 8), hi = __ldg(bg + (size_t)(2 * (i_lo + j) + 1) * 8);
+                bhp[j] = lo | (hi << 16);
+            }
+#pragma unroll
+            for (int j = 0; j < 17; ++j) eg[j] = __expf(eg[j]);
+        }
+        const float dgl = __ldg(p.dgl + (size_t)g * K + k);
+        // ---- after P1, P2: dv (lane = value channel; group w writes tokens 16w..16w+15) and dq
+        wait_idle_or_flag(&m1, 0, p.status, 48);
+        wait_idle_or_flag(&m2, 0, p.status, 49);
+        tc_fence_after();
+        {
+            uint32_t v[16], u[16];
             tmem_ld_x16(t8::taddr(tmem, warp, 64 + wg * 16), v);
+            tmem_ld_x16(t8::taddr(tmem, warp, i_lo), u);
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const int t = n * C + wg * 16 + j;
                 if (t < p.T) p.dv[(((size_t)b * p.T + t) * p.H + h) * V + k] = __float2bfloat16_rn(__uint_as_float(v[j]));
             }
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (i_lo + j < t_left) p.dq[base_qk + (size_t)j * tok_stride] = __float2bfloat16_rn(p.scale * eg[j + 1] * __uint_as_float(u[j]));
+        }
+        // ---- after P3: da = e^{ge-half} dAh
+        wait_idle_or_flag(&m3, 0, p.status, 50);
+        tc_fence_after();
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+            uint32_t v[16];
+            tmem_ld_x16(t8::taddr(tmem, warp, 128 + 2 * i_lo + hb * 16), v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int jt = hb * 8 + j;
+                if (i_lo + jt < t_left) {
+                    p.da[base_ab + (size_t)(2 * jt) * tok_stride] = __float2bfloat16_rn(eg[jt] * __uint_as_float(v[2 * j]));
+                    p.da[base_ab + (size_t)(2 * jt + 1) * tok_stride] = __float2bfloat16_rn(eg[jt] * __uint_as_float(v[2 * j + 1]));
+                }
+            }
+        }
+        // ---- after P4, P5: dk, db and the reverse running sum for dgk
+        wait_idle_or_flag(&m4, 0, p.status, 51);
+        tc_fence_after();
+        if (tid == 0) TL(9);
+        // per-thread element pointers into the hat tiles still in shared memory (token i sits 16 bytes after token i-1)
+        const __nv_bfloat16* eq = reinterpret_cast<const __nv_bfloat16*>(sD + (k >> 3) * 64) + (k & 7) + i_lo * 8;
+        const __nv_bfloat16* ek = reinterpret_cast<const __nv_bfloat16*>(sb + (k >> 3) * 64) + (k & 7) + i_lo * 8;
+        const __nv_bfloat16* ea = reinterpret_cast<const __nv_bfloat16*>(sB + (k >> 3) * 128) + (k & 7) + i_lo * 16;
+        float run = 0.f;
+        float* dgk_loc = reinterpret_cast<float*>(sE) + (size_t)i_lo * K + k;    // [64][128] fp32 over the (consumed) dAab slot
+#pragma unroll
+        for (int hb = 1; hb >= 0; --hb) {
+            uint32_t vq[8], vk[8], va[16], vb[16];
+            tmem_ld_x8(t8::taddr(tmem, warp, i_lo + hb * 8), vq);
+            tmem_ld_x8(t8::taddr(tmem, warp, 384 + i_lo + hb * 8), vk);
+            tmem_ld_x16(t8::taddr(tmem, warp, 128 + 2 * i_lo + hb * 16), va);
+            tmem_ld_x16(t8::taddr(tmem, warp, 256 + 2 * i_lo + hb * 16), vb);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 7; j >= 0; --j) {
+                const int jt = hb * 8 + j;
+                const bool ok = i_lo + jt < t_left;
+                const float em = __frcp_rn(eg[jt + 1]);
+                const float dqh = __uint_as_float(vq[j]), dkh = __uint_as_float(vk[j]);
+                const float db0 = __uint_as_float(vb[2 * j]), db1 = __uint_as_float(vb[2 * j + 1]);
+                float d_gi = __bfloat162float(eq[jt * 8]) * dqh - __bfloat162float(ek[jt * 8]) * dkh;
+                d_gi = fmaf(-__uint_as_float(bhp[jt] << 16), db0, d_gi);
+                d_gi = fmaf(-__uint_as_float(bhp[jt] & 0xffff0000u), db1, d_gi);
+                float d_ge = __bfloat162float(ea[(2 * jt) * 8]) * __uint_as_float(va[2 * j]);
+                d_ge = fmaf(__bfloat162float(ea[(2 * jt + 1) * 8]), __uint_as_float(va[2 * j + 1]), d_ge);
+                if (ok) {
+                    p.dk[base_qk + (size_t)jt * tok_stride] = __float2bfloat16_rn(em * dkh);
+                    p.db[base_ab + (size_t)(2 * jt) * tok_stride] = __float2bfloat16_rn(em * db0);
+                    p.db[base_ab + (size_t)(2 * jt + 1) * tok_stride] = __float2bfloat16_rn(em * db1);
+                }
+                run += d_gi + d_ge;
+                dgk_loc[jt * K] = run - d_ge + dgl;
+            }
+        }
+        if (tid == 0) TL(10);
+        group_total[wg][k] = run;
+        asm volatile("bar.sync 1, 512;" ::: "memory");     // the sixteen epilogue warps only
+        if (tid == 0) TL(11);
+        float add = 0.f;
+        for (int w = 0; w < wg; ++w) add += group_total[w][k];
+#pragma unroll 4
+        for (int jj = 0; jj < 16; ++jj) {
+            const int t = n * C + i_lo + jj;
+            if (t < p.T) st_elem(p.dgk, (((size_t)b * p.T + t) * p.H + h) * K + k, p.gdt, dgk_loc[jj * K] + add);
         }
     }
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) TL(12);
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
@@ -1610,3 +1706,9 @@ int tc_debug_buffer(const HdlaDims& d, const unsigned char* ws, const char* name
 }
 
 }  // namespace hdla
+
+#ifdef HDLA_TIMELINE
+extern "C" __attribute__((visibility("default"))) int hdla_debug_timeline(unsigned long long* host_dst, size_t count) {
+    return (int)cudaMemcpyFromSymbol(host_dst, hdla::g_timeline, count * sizeof(unsigned long long));
+}
+#endif

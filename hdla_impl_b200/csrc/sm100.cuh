@@ -156,6 +156,13 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                  ::"r"(smem_u32(bar)) : "memory");
 }
 
+// One 32-byte store (address 32-byte aligned): a lane that owns two adjacent 16-byte chunks writes a whole
+// sector with one instruction instead of two half-sector stores.
+__device__ __forceinline__ void st_global_32B(void* p, uint4 a, uint4 b) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"l"(p), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
