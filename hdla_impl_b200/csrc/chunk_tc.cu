@@ -408,14 +408,14 @@ __device__ __forceinline__ float c8_elem(const uint4* tile, int rows, int r, int
 
 __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    uint4* sL = reinterpret_cast<uint4*>(smem);
-    uint4* sD = sL + CH128;
-    uint4* sX = sD + CH128;
+    uint4* sL = reinterpret_cast<uint4*>(smem);      // 32 KB: L = Aab
+    uint4* sD = sL + CH128;                          // 32 KB: the inverse being assembled
+    uint4* sX = sD + CH128;                          //  8 KB: the X blocks of one level
     __shared__ __align__(8) uint64_t ld_bar, mma_bar;
     __shared__ uint32_t tmem_s;
     const long long g = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5;
-    if (warp == 0) { tmem_alloc(&tmem_s, 128); tmem_relinquish(); }
+    if (warp == 0) { tmem_alloc(&tmem_s, 64); tmem_relinquish(); }
     if (tid == 0) {
         mbar_init(&ld_bar, 1); mbar_init(&mma_bar, 1); fence_mbar_init();
         mbar_expect_tx(&ld_bar, 32768);
@@ -447,61 +447,79 @@ __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
     }
     fence_proxy_async();
     __syncthreads();
-    const Tile tL = t8::tile(sL, 128), tD = t8::tile(sD, 128), tX = t8::tile(sX, 128);
+    // Doubling: with the diagonal blocks of size bs inverted, the block below the diagonal of every pair
+    // (even block J, odd block I = J+1) is  M[I,J] = D[I,I] L[I,J] D[J,J].  Each product is restricted to the
+    // pair's own column range (N = bs) and contraction range (K = bs); the accumulator rows outside block I
+    // are computed but never read.  Pair p uses accumulator columns [p bs, (p+1) bs).
+    const Tile tL = t8::tile(sL, 128), tD = t8::tile(sD, 128);
     uint32_t phase = 0;
+#pragma unroll 1
     for (int bs = 16; bs <= 64; bs <<= 1) {
+        const int npair = 64 / bs;
+        const int xt_chunks = bs * bs / 8;                      // 16-byte chunks of one pair's X block
         if (tid == 0) {
             tc_fence_after();
-            t8::mma_chain<false, true>(tmem, tL, 0, 0, tD, 0, 0, 128, 128, false);   // X = L D
+            for (int pr = 0; pr < npair; ++pr) {
+                const int J = 2 * pr * bs;
+                t8::mma_chain<false, true>(tmem + pr * bs, tL, J, 0, tD, J, J, bs, bs, false);     // X = L[:, J] D[J, J]
+            }
             umma_commit(&mma_bar);
         }
         wait_or_flag(&mma_bar, phase, p.status, 6);
         phase ^= 1;
         tc_fence_after();
-#pragma unroll 1
-        for (int hh = 0; hh < 2; ++hh) {
-            float f[64];
-            tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
+        const int blk = tid / bs, pr = blk >> 1;                // pr is uniform within a warp
+        const bool odd = blk & 1;
+        const int rr = tid - blk * bs;
+        {
+            uint4* xt = sX + pr * xt_chunks;                    // C8 tile [bs x bs]
+            for (int cg = 0; cg < (bs >> 3); ++cg) {
+                uint32_t v[8]; float f[8];
+                tmem_ld_x8(t8::taddr(tmem, warp, pr * bs + cg * 8), v);
+                tmem_wait_ld();
 #pragma unroll
-            for (int cg = 0; cg < 8; ++cg) sX[(hh * 8 + cg) * 128 + tid] = t8::pack8(f + cg * 8);
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]);
+                if (odd) xt[cg * bs + rr] = t8::pack8(f);
+            }
         }
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
         if (tid == 0) {
             tc_fence_after();
-            t8::mma_chain<false, true>(tmem, tD, 0, 0, tX, 0, 0, 128, 128, false);   // Y = D X
+            for (int pr2 = 0; pr2 < npair; ++pr2) {
+                const int I = (2 * pr2 + 1) * bs;
+                const Tile tX = t8::tile(sX + pr2 * xt_chunks, bs);
+                t8::mma_chain<false, true>(tmem + pr2 * bs, tD, I, 0, tX, 0, 0, bs, bs, false);    // Y = D[:, I] X
+            }
             umma_commit(&mma_bar);
         }
         wait_or_flag(&mma_bar, phase, p.status, 7);
         phase ^= 1;
         tc_fence_after();
         {
-            // rows of an odd block I take the columns of block I-1; the column range is warp-uniform
-            const int row_lo = warp * 32;
-            const int I_hi = (row_lo + 31) / bs;                // block of the warp's last row
-            const int I_odd = (I_hi & 1) ? I_hi : -1;
-            if (I_odd > 0 && (I_odd * bs) < row_lo + 32) {
-                const int c_lo = (I_odd - 1) * bs;
-                const bool mine = (tid / bs) == I_odd;
-                for (int cg = c_lo >> 3; cg < (c_lo + bs) >> 3; ++cg) {
-                    uint32_t v[8]; float f[8];
-                    tmem_ld_x8(t8::taddr(tmem, warp, cg * 8), v);
-                    tmem_wait_ld();
+            const int cg0 = (2 * pr * bs) >> 3;                 // first column group of block J in the full tile
+            for (int cg = 0; cg < (bs >> 3); ++cg) {
+                uint32_t v[8]; float f[8];
+                tmem_ld_x8(t8::taddr(tmem, warp, pr * bs + cg * 8), v);
+                tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]);
-                    if (mine) sD[cg * 128 + tid] = t8::pack8(f);
-                }
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]);
+                if (odd) sD[(cg0 + cg) * 128 + tid] = t8::pack8(f);
             }
         }
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
     }
-    for (int e = tid; e < CH128; e += 128) p.M[g * CH128 + e] = sD[e];
+    if (tid == 0) {
+        bulk_s2g(p.M + g * CH128, sD, 32768);
+        bulk_commit();
+        bulk_wait_read<0>();
+    }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, 128);
+    if (warp == 0) tmem_dealloc(tmem, 64);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -1474,7 +1492,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     cudaGetDevice(&dev);
     if (attr_dev != dev) {
         TRY(set_smem(gram_tc_kernel, 98304 + 1024));
-        TRY(set_smem(inverse_tc_kernel, 98304));
+        TRY(set_smem(inverse_tc_kernel, 73728));
         TRY(set_smem(wu_tc_kernel, 98304));
         TRY(set_smem(scan_tc_kernel, 196608));
         TRY(set_smem(out_tc_kernel, 122880));
@@ -1501,7 +1519,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         gram_tc_kernel<<<G, 128, 98304 + 1024, st>>>(gp);
         HDLA_CHECK_LAUNCH("gram_tc_kernel");
         InvP ivp{U4(pl.Aab), U4(pl.M), status};
-        inverse_tc_kernel<<<G, 128, 98304, st>>>(ivp);
+        inverse_tc_kernel<<<G, 128, 73728, st>>>(ivp);
         HDLA_CHECK_LAUNCH("inverse_tc_kernel");
         WuP wp{U4(pl.M), U4(pl.Ah), U4(pl.Aak), U4(pl.Vc), U4(pl.P), U4(pl.U), U4(pl.W), status};
         wu_tc_kernel<<<G, 128, 98304, st>>>(wp);
