@@ -408,8 +408,10 @@ __device__ __forceinline__ float c8_elem(const uint4* tile, int rows, int r, int
 
 __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    uint4* sL = reinterpret_cast<uint4*>(smem);      // 32 KB: L = Aab
-    uint4* sD = sL + CH128;                          // 32 KB: the inverse being assembled
+    // One 32 KB tile holds L = Aab and, block by block, the inverse that replaces it: a block of L is read for the
+    // last time at the level that produces the block of M at the same place (later levels read it only into
+    // accumulator rows that are never used).
+    uint4* sD = reinterpret_cast<uint4*>(smem);      // 32 KB: L, overwritten by M
     uint4* sX = sD + CH128;                          //  8 KB: the X blocks of one level
     __shared__ __align__(8) uint64_t ld_bar, mma_bar;
     __shared__ uint32_t tmem_s;
@@ -419,9 +421,8 @@ __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
     if (tid == 0) {
         mbar_init(&ld_bar, 1); mbar_init(&mma_bar, 1); fence_mbar_init();
         mbar_expect_tx(&ld_bar, 32768);
-        bulk_g2s(sL, p.Aab + g * CH128, 32768, &ld_bar);
+        bulk_g2s(sD, p.Aab + g * CH128, 32768, &ld_bar);
     }
-    for (int e = tid; e < CH128; e += 128) sD[e] = make_uint4(0, 0, 0, 0);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -435,9 +436,10 @@ __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
             float s = (i == c) ? 1.f : 0.f;
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-                if (j < i) s = fmaf(c8_elem(sL, 128, base + i, base + j), mcol[j], s);
+                if (j < i) s = fmaf(c8_elem(sD, 128, base + i, base + j), mcol[j], s);
             mcol[i] = s;
         }
+        __syncthreads();                               // every column of a block is computed before the block is replaced
         __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(sD);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -451,7 +453,7 @@ __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
     // (even block J, odd block I = J+1) is  M[I,J] = D[I,I] L[I,J] D[J,J].  Each product is restricted to the
     // pair's own column range (N = bs) and contraction range (K = bs); the accumulator rows outside block I
     // are computed but never read.  Pair p uses accumulator columns [p bs, (p+1) bs).
-    const Tile tL = t8::tile(sL, 128), tD = t8::tile(sD, 128);
+    const Tile tD = t8::tile(sD, 128);
     uint32_t phase = 0;
 #pragma unroll 1
     for (int bs = 16; bs <= 64; bs <<= 1) {
@@ -461,7 +463,7 @@ __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
             tc_fence_after();
             for (int pr = 0; pr < npair; ++pr) {
                 const int J = 2 * pr * bs;
-                t8::mma_chain<false, true>(tmem + pr * bs, tL, J, 0, tD, J, J, bs, bs, false);     // X = L[:, J] D[J, J]
+                t8::mma_chain<false, true>(tmem + pr * bs, tD, J, 0, tD, J, J, bs, bs, false);     // X = L[:, J] D[J, J]
             }
             umma_commit(&mma_bar);
         }
@@ -1492,7 +1494,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     cudaGetDevice(&dev);
     if (attr_dev != dev) {
         TRY(set_smem(gram_tc_kernel, 98304 + 1024));
-        TRY(set_smem(inverse_tc_kernel, 73728));
+        TRY(set_smem(inverse_tc_kernel, 40960));
         TRY(set_smem(wu_tc_kernel, 98304));
         TRY(set_smem(scan_tc_kernel, 196608));
         TRY(set_smem(out_tc_kernel, 122880));
@@ -1519,7 +1521,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         gram_tc_kernel<<<G, 128, 98304 + 1024, st>>>(gp);
         HDLA_CHECK_LAUNCH("gram_tc_kernel");
         InvP ivp{U4(pl.Aab), U4(pl.M), status};
-        inverse_tc_kernel<<<G, 128, 73728, st>>>(ivp);
+        inverse_tc_kernel<<<G, 128, 40960, st>>>(ivp);
         HDLA_CHECK_LAUNCH("inverse_tc_kernel");
         WuP wp{U4(pl.M), U4(pl.Ah), U4(pl.Aak), U4(pl.Vc), U4(pl.P), U4(pl.U), U4(pl.W), status};
         wu_tc_kernel<<<G, 128, 98304, st>>>(wp);
