@@ -1090,40 +1090,45 @@ struct OutP {
 
 __global__ void __launch_bounds__(128) out_tc_kernel(OutP p) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    uint4* sQ = reinterpret_cast<uint4*>(smem);      // 16 KB [64 x 128]
-    uint4* sAqk = sQ + CH64;                         //  8 KB [64 x 64]
-    uint4* sAqb = sAqk + 512;                        // 16 KB [64 x 128]
-    uint4* sV = sAqb + CH64;                         // 16 KB [64 x 128]
-    uint4* sH = sV + CH64;                           // 32 KB [128 x 128]
-    uint4* sV2 = sH + CH128;                         // 32 KB [128 x 128]
-    __shared__ __align__(8) uint64_t ld_bar, mma_bar;
+    // 72 KB, three CTAs per SM: the operands of the last product (Aqb, v2) take the place of the first
+    // product's (Qh, St) once that has completed; the other CTAs on the SM cover the extra round trip.
+    uint4* sQ = reinterpret_cast<uint4*>(smem);      // 16 KB [64 x 128]  Qh, then Aqb
+    uint4* sH = sQ + CH64;                           // 32 KB [128 x 128] St, then v2
+    uint4* sAqk = sH + CH128;                        //  8 KB [64 x 64]
+    uint4* sV = sAqk + 512;                          // 16 KB [64 x 128]
+    __shared__ __align__(8) uint64_t ld_bar, ld2_bar, mma_bar, mma2_bar;
     __shared__ uint32_t tmem_s;
     const long long g = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5;
     if (warp == 0) { tmem_alloc(&tmem_s, 128); tmem_relinquish(); }
     if (tid == 0) {
-        mbar_init(&ld_bar, 1); mbar_init(&mma_bar, 1); fence_mbar_init();
-        mbar_expect_tx(&ld_bar, 122880);
+        mbar_init(&ld_bar, 1); mbar_init(&ld2_bar, 1); mbar_init(&mma_bar, 1); mbar_init(&mma2_bar, 1); fence_mbar_init();
+        mbar_expect_tx(&ld_bar, 16384 + 32768 + 8192 + 16384);
         bulk_g2s(sQ, p.Qh + g * CH64, 16384, &ld_bar);
         bulk_g2s(sH, p.Hs + g * CH128, 32768, &ld_bar);
         bulk_g2s(sAqk, p.Aqk + g * 512, 8192, &ld_bar);
         bulk_g2s(sV, p.Vc + g * CH64, 16384, &ld_bar);
-        bulk_g2s(sAqb, p.Aqb + g * CH64, 16384, &ld_bar);
-        bulk_g2s(sV2, p.V2 + g * CH128, 32768, &ld_bar);
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_s;
-    wait_or_flag(&ld_bar, 0, p.status, 16);
     if (tid == 0) {
         // the three A operands have 64 rows; lanes 64..127 of the accumulator are never read
+        wait_or_flag(&ld_bar, 0, p.status, 16);
         t8::mma_chain<false, true>(tmem, t8::tile(sQ, 64), 0, 0, t8::tile(sH, 128), 0, 0, 128, 128, false);
         t8::mma_chain<false, true>(tmem, t8::tile(sAqk, 64), 0, 0, t8::tile(sV, 64), 0, 0, 128, 64, true);
-        t8::mma_chain<false, true>(tmem, t8::tile(sAqb, 64), 0, 0, t8::tile(sV2, 128), 0, 0, 128, 128, true);
         umma_commit(&mma_bar);
+        wait_or_flag(&mma_bar, 0, p.status, 17);
+        mbar_expect_tx(&ld2_bar, 16384 + 32768);
+        bulk_g2s(sQ, p.Aqb + g * CH64, 16384, &ld2_bar);
+        bulk_g2s(sH, p.V2 + g * CH128, 32768, &ld2_bar);
+        wait_or_flag(&ld2_bar, 0, p.status, 18);
+        tc_fence_after();
+        t8::mma_chain<false, true>(tmem, t8::tile(sQ, 64), 0, 0, t8::tile(sH, 128), 0, 0, 128, 128, true);
+        umma_commit(&mma2_bar);
     }
-    wait_or_flag(&mma_bar, 0, p.status, 17);
+    if (warp < 2) wait_idle_or_flag(&mma2_bar, 0, p.status, 19);
     tc_fence_after();
     if (warp < 2) {
         const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
@@ -1497,7 +1502,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         TRY(set_smem(inverse_tc_kernel, 40960));
         TRY(set_smem(wu_tc_kernel, 98304));
         TRY(set_smem(scan_tc_kernel, 196608));
-        TRY(set_smem(out_tc_kernel, 122880));
+        TRY(set_smem(out_tc_kernel, 73728));
         TRY(set_smem(wy_bwd_tc_kernel, kWySmem));
         TRY(set_smem(grad_tc_kernel, kGradSmem));
         TRY(set_smem(dau_tc_kernel, 81920));
@@ -1595,7 +1600,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     if (need_o) {
         OutP op{U4(pl.Qh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Vc), U4(pl.Hs), U4(pl.V2), (__nv_bfloat16*)o, d.T, d.H,
                 pl.NT, status};
-        out_tc_kernel<<<G, 128, 122880, st>>>(op);
+        out_tc_kernel<<<G, 128, 73728, st>>>(op);
         HDLA_CHECK_LAUNCH("out_tc_kernel");
     }
     return HDLA_OK;
