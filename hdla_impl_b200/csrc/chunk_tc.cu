@@ -633,7 +633,8 @@ struct ScanTcP {
     float* dgl;                              // rev only
     int NT, reverse;
     int* status;
-    int add_stride, r1_stride;               // chunk strides of ADD / R1 in tiles: 1, or 0 for one shared (zero) tile
+    int add_stride, r1_stride;               // chunk strides of ADD and of L1 / R1 in tiles: 1, or 0 for one shared (zero) tile
+                                             // (with R1 = 0 the product L1^T R1 vanishes, so L1 is not fetched either)
     int no_store;                            // 1: do not write CK, Y, dgl (state-only passes)
     int init_identity;                       // 1: start from the K x K identity (transition pass, needs K == V)
     // two-level scan: the chunks of a sequence are cut into nseg segments of seg_len chunks, one CTA each
@@ -662,7 +663,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     const int bh = blockIdx.x / p.nseg, seg = blockIdx.x % p.nseg;
     const long long slot = blockIdx.x;
     if (blockIdx.y == 1) {                   // transition twin of this segment
-        p.ADD = p.zero_tile; p.R1 = p.zero_tile; p.add_stride = 0; p.r1_stride = 0;
+        p.ADD = p.zero_tile; p.R1 = p.zero_tile; p.L1 = p.zero_tile; p.add_stride = 0; p.r1_stride = 0;
         p.init_identity = 1; p.init = nullptr; p.fin = p.fin_transition; p.fin2 = nullptr;
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -680,7 +681,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         bulk_g2s(sA1, p.A1 + g * CH128, 32768, &ldA);
         bulk_g2s(sADD, p.ADD + g * p.add_stride * CH128, 32768, &ldA);
         mbar_expect_tx(&ldB, 65536);
-        bulk_g2s(sL1, p.L1 + g * CH64, 16384, &ldB);
+        bulk_g2s(sL1, p.L1 + g * p.r1_stride * CH64, 16384, &ldB);
         bulk_g2s(sR1, p.R1 + g * p.r1_stride * CH64, 16384, &ldB);
         bulk_g2s(sL2, p.L2 + g * CH128, 32768, &ldB);
     }
@@ -794,7 +795,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         tc_fence_after();
         if (tid == 0 && more) {
             mbar_expect_tx(&ldB, 65536);
-            bulk_g2s(sL1, p.L1 + (g + dn) * CH64, 16384, &ldB);
+            bulk_g2s(sL1, p.L1 + (g + dn) * p.r1_stride * CH64, 16384, &ldB);
             bulk_g2s(sR1, p.R1 + (g + dn) * p.r1_stride * CH64, 16384, &ldB);
             bulk_g2s(sL2, p.L2 + (g + dn) * CH128, 32768, &ldB);
         }
@@ -1176,10 +1177,10 @@ __global__ void c8_to_rowmajor_kernel(const uint4* src, float* dst, int rows, in
 // They read 18 distinct tiles (416 KB) -- more than shared memory holds -- so the tiles go through
 // a fixed slot schedule: five 32 KB slots A..E, three 16 KB slots a..c, two 8 KB slots x, y; a tile
 // is loaded (bulk copy) as soon as the product that last read its slot has completed:
-//   L1: St->A Bh->B dO->a Kh->b dAqb->c dAqk->x      L2: dSt->C dP->D Aak->E Aqk->y
-//   P1 after L1, P2 after L2
-//   L3: dWh->A (after P1)  M->D dAab->E dAak->a (after P2);   P3 after L3
-//   L4: V2->A Ah->B Qh->D.lo v->D.hi (after P3);              P4, P5 after L4
+//   at the start: St->A dO->a Aqk->y dP->D Aak->E Kh->b dAqk->x Bh->B dAqb->c dSt->C
+//   dWh->A once St dO^T is complete, dAak->a once dO^T Aqk is, M->D and dAab->E once dP^T Aak is;
+//   Ah->B once Bh^T dAab^T is complete, V2->A, Qh->D.lo, v->D.hi once dWh^T M is.
+// Every group of tiles has its own load barrier, and a chain is issued when its own operands have landed.
 // All five accumulators stay in TMEM (448 columns). Sixteen epilogue warps un-gate them (dq = scale e^{gi-half}
 // dQh, ...) and write every gradient in the public layout (a warp writes 32 adjacent channels of one token)
 // as soon as the product is complete -- dv and dq after P1/P2, da after P3, overlapping the later loads --
@@ -1217,7 +1218,9 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
     uint4* sc = sb + CH64;
     uint4* sx = sc + CH64;                               // 8 KB slots
     uint4* sy = sx + 512;
-    __shared__ __align__(8) uint64_t L1, L2, L3, L4, m1, m2, m3, m4;
+    // load barriers (one per group of tiles that a chain waits for) and commit barriers (chains or whole products)
+    __shared__ __align__(8) uint64_t ld[13], mc1, mc5, mc6, mc7, mc9, m1, m2, m3, m4;
+    enum { T_StdO, T_Aqk, T_dPAak, T_KhdAqk, T_BhdAqb, T_dSt, T_dW, T_dAak, T_M, T_dAab, T_V2, T_QhVc, T_Ah };
     __shared__ uint32_t tmem_s;
     const long long g = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5;
@@ -1225,21 +1228,28 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
     if (warp == 0) { tmem_alloc(&tmem_s, 512); tmem_relinquish(); }
     if (producer) {
         TL(0);
-        mbar_init(&L1, 1); mbar_init(&L2, 1); mbar_init(&L3, 1); mbar_init(&L4, 1);
+#pragma unroll
+        for (int i = 0; i < 13; ++i) mbar_init(&ld[i], 1);
+        mbar_init(&mc1, 1); mbar_init(&mc5, 1); mbar_init(&mc6, 1); mbar_init(&mc7, 1); mbar_init(&mc9, 1);
         mbar_init(&m1, 1); mbar_init(&m2, 1); mbar_init(&m3, 1); mbar_init(&m4, 1);
         fence_mbar_init();
-        mbar_expect_tx(&L1, 32768 + 32768 + 16384 + 16384 + 16384 + 8192);
-        bulk_g2s(sA, p.Hs + g * CH128, 32768, &L1);
-        bulk_g2s(sB, p.Bh + g * CH128, 32768, &L1);
-        bulk_g2s(sa, p.dOc + g * CH64, 16384, &L1);
-        bulk_g2s(sb, p.Kh + g * CH64, 16384, &L1);
-        bulk_g2s(sc, p.dAqb + g * CH64, 16384, &L1);
-        bulk_g2s(sx, p.dAqk + g * 512, 8192, &L1);
-        mbar_expect_tx(&L2, 32768 + 32768 + 16384 + 8192);
-        bulk_g2s(sC, p.DE + g * CH128, 32768, &L2);
-        bulk_g2s(sD, p.dP + g * CH128, 32768, &L2);
-        bulk_g2s(sE, p.Aak + g * CH64, 16384, &L2);
-        bulk_g2s(sy, p.Aqk + g * 512, 8192, &L2);
+        // first loads, in the order the chains need them
+        mbar_expect_tx(&ld[T_StdO], 32768 + 16384);
+        bulk_g2s(sA, p.Hs + g * CH128, 32768, &ld[T_StdO]);
+        bulk_g2s(sa, p.dOc + g * CH64, 16384, &ld[T_StdO]);
+        mbar_expect_tx(&ld[T_Aqk], 8192);
+        bulk_g2s(sy, p.Aqk + g * 512, 8192, &ld[T_Aqk]);
+        mbar_expect_tx(&ld[T_dPAak], 32768 + 16384);
+        bulk_g2s(sD, p.dP + g * CH128, 32768, &ld[T_dPAak]);
+        bulk_g2s(sE, p.Aak + g * CH64, 16384, &ld[T_dPAak]);
+        mbar_expect_tx(&ld[T_KhdAqk], 16384 + 8192);
+        bulk_g2s(sb, p.Kh + g * CH64, 16384, &ld[T_KhdAqk]);
+        bulk_g2s(sx, p.dAqk + g * 512, 8192, &ld[T_KhdAqk]);
+        mbar_expect_tx(&ld[T_BhdAqb], 32768 + 16384);
+        bulk_g2s(sB, p.Bh + g * CH128, 32768, &ld[T_BhdAqb]);
+        bulk_g2s(sc, p.dAqb + g * CH64, 16384, &ld[T_BhdAqb]);
+        mbar_expect_tx(&ld[T_dSt], 32768);
+        bulk_g2s(sC, p.DE + g * CH128, 32768, &ld[T_dSt]);
     }
     tc_fence_before();
     __syncthreads();
@@ -1247,50 +1257,70 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
     const uint32_t tmem = tmem_s;
     // TMEM columns: dQh^T 0..63, dv^T 64..127, dAh^T 128..255, dBh^T 256..383, dKh^T 384..447
     if (producer) {
-        TL(1);
-        wait_or_flag(&L1, 0, p.status, 40);
-        TL(2);
-        chain0<false, false>(tmem, t8::tile(sA, 128), t8::tile(sa, 64), 64, 128, false);          // St dO^T
-        chain0<true, false>(tmem, t8::tile(sb, 64), t8::tile(sx, 64), 64, 64, true);              // Kh^T dAqk^T
-        chain0<true, false>(tmem, t8::tile(sB, 128), t8::tile(sc, 64), 64, 128, true);            // Bh^T dAqb^T
+        // Chains are issued as soon as their own tiles have landed, and the chains that read a slot for the last
+        // time are issued first and committed on their own, so that the slot is refilled while the rest of the
+        // product still runs.
+        wait_or_flag(&ld[T_StdO], 0, p.status, 70);
+        chain0<false, false>(tmem, t8::tile(sA, 128), t8::tile(sa, 64), 64, 128, false);          // P1: St dO^T
+        umma_commit(&mc1);                                                                        // slot A free
+        wait_or_flag(&ld[T_Aqk], 0, p.status, 71);
+        chain0<true, true>(tmem + 64, t8::tile(sa, 64), t8::tile(sy, 64), 64, 64, false);         // P2: dO^T Aqk
+        umma_commit(&mc5);                                                                        // slots a, y free
+        wait_or_flag(&ld[T_dPAak], 0, p.status, 72);
+        chain0<true, true>(tmem + 64, t8::tile(sD, 128), t8::tile(sE, 128), 64, 128, true);       // P2: dP^T Aak
+        umma_commit(&mc6);                                                                        // slots D, E free
+        wait_or_flag(&mc1, 0, p.status, 73);
+        mbar_expect_tx(&ld[T_dW], 32768);
+        bulk_g2s(sA, p.dW + g * CH128, 32768, &ld[T_dW]);
+        wait_or_flag(&ld[T_KhdAqk], 0, p.status, 74);
+        chain0<true, false>(tmem, t8::tile(sb, 64), t8::tile(sx, 64), 64, 64, true);              // P1: Kh^T dAqk^T
+        wait_or_flag(&mc5, 0, p.status, 75);
+        mbar_expect_tx(&ld[T_dAak], 16384);
+        bulk_g2s(sa, p.dAak + g * CH64, 16384, &ld[T_dAak]);
+        wait_or_flag(&ld[T_BhdAqb], 0, p.status, 76);
+        chain0<true, false>(tmem, t8::tile(sB, 128), t8::tile(sc, 64), 64, 128, true);            // P1: Bh^T dAqb^T
         umma_commit(&m1);
-        wait_or_flag(&L2, 0, p.status, 41);
-        TL(3);
-        chain0<true, false>(tmem + 64, t8::tile(sC, 128), t8::tile(sb, 64), 64, 128, false);      // dSt^T Kh^T
-        chain0<true, true>(tmem + 64, t8::tile(sa, 64), t8::tile(sy, 64), 64, 64, true);          // dO^T Aqk
-        chain0<true, true>(tmem + 64, t8::tile(sD, 128), t8::tile(sE, 128), 64, 128, true);       // dP^T Aak
+        wait_or_flag(&mc6, 0, p.status, 77);
+        mbar_expect_tx(&ld[T_M], 32768);
+        bulk_g2s(sD, p.M + g * CH128, 32768, &ld[T_M]);
+        mbar_expect_tx(&ld[T_dAab], 32768);
+        bulk_g2s(sE, p.dAab + g * CH128, 32768, &ld[T_dAab]);
+        wait_or_flag(&ld[T_dSt], 0, p.status, 78);
+        chain0<true, false>(tmem + 64, t8::tile(sC, 128), t8::tile(sb, 64), 64, 128, true);       // P2: dSt^T Kh^T
         umma_commit(&m2);
-        wait_or_flag(&m1, 0, p.status, 42);
-        wait_or_flag(&m2, 0, p.status, 43);
         TL(4);
-        mbar_expect_tx(&L3, 32768 + 32768 + 32768 + 16384);
-        bulk_g2s(sA, p.dW + g * CH128, 32768, &L3);
-        bulk_g2s(sD, p.M + g * CH128, 32768, &L3);
-        bulk_g2s(sE, p.dAab + g * CH128, 32768, &L3);
-        bulk_g2s(sa, p.dAak + g * CH64, 16384, &L3);
-        wait_or_flag(&L3, 0, p.status, 44);
-        TL(5);
-        chain0<true, true>(tmem + 128, t8::tile(sA, 128), t8::tile(sD, 128), 128, 128, false);    // dWh^T M
-        chain0<true, false>(tmem + 128, t8::tile(sb, 64), t8::tile(sa, 128), 128, 64, true);      // Kh^T dAak^T
-        chain0<true, false>(tmem + 128, t8::tile(sB, 128), t8::tile(sE, 128), 128, 128, true);    // Bh^T dAab^T
+        wait_or_flag(&ld[T_dAab], 0, p.status, 79);
+        chain0<true, false>(tmem + 128, t8::tile(sB, 128), t8::tile(sE, 128), 128, 128, false);   // P3: Bh^T dAab^T
+        umma_commit(&mc9);                                                                        // slot B free
+        wait_or_flag(&ld[T_dW], 0, p.status, 80);
+        wait_or_flag(&ld[T_M], 0, p.status, 81);
+        chain0<true, true>(tmem + 128, t8::tile(sA, 128), t8::tile(sD, 128), 128, 128, true);     // P3: dWh^T M
+        umma_commit(&mc7);                                                                        // slots A, D free
+        wait_or_flag(&ld[T_dAak], 0, p.status, 82);
+        chain0<true, false>(tmem + 128, t8::tile(sb, 64), t8::tile(sa, 128), 128, 64, true);      // P3: Kh^T dAak^T
         umma_commit(&m3);
-        wait_or_flag(&m3, 0, p.status, 45);
+        wait_or_flag(&mc9, 0, p.status, 83);
+        mbar_expect_tx(&ld[T_Ah], 32768);
+        bulk_g2s(sB, p.Ah + g * CH128, 32768, &ld[T_Ah]);
+        wait_or_flag(&mc7, 0, p.status, 84);
         TL(6);
-        mbar_expect_tx(&L4, 32768 + 32768 + 16384 + 16384);
-        bulk_g2s(sA, p.V2 + g * CH128, 32768, &L4);
-        bulk_g2s(sB, p.Ah + g * CH128, 32768, &L4);
-        bulk_g2s(sD, p.Qh + g * CH64, 16384, &L4);
-        bulk_g2s(sD + CH64, p.Vc + g * CH64, 16384, &L4);
-        wait_or_flag(&L4, 0, p.status, 46);
+        mbar_expect_tx(&ld[T_V2], 32768);
+        bulk_g2s(sA, p.V2 + g * CH128, 32768, &ld[T_V2]);
+        mbar_expect_tx(&ld[T_QhVc], 16384 + 16384);
+        bulk_g2s(sD, p.Qh + g * CH64, 16384, &ld[T_QhVc]);
+        bulk_g2s(sD + CH64, p.Vc + g * CH64, 16384, &ld[T_QhVc]);
+        wait_or_flag(&ld[T_V2], 0, p.status, 85);
+        chain0<false, false>(tmem + 256, t8::tile(sC, 128), t8::tile(sA, 128), 128, 128, false);  // P4: dSt V2^T
+        wait_or_flag(&ld[T_QhVc], 0, p.status, 86);
+        chain0<false, false>(tmem + 384, t8::tile(sC, 128), t8::tile(sD + CH64, 64), 64, 128, false);  // P5: dSt v^T
+        chain0<true, true>(tmem + 256, t8::tile(sD, 64), t8::tile(sc, 64), 128, 64, true);        // P4: Qh^T dAqb
+        chain0<true, true>(tmem + 384, t8::tile(sD, 64), t8::tile(sx, 64), 64, 64, true);         // P5: Qh^T dAqk
+        wait_or_flag(&ld[T_Ah], 0, p.status, 87);
         TL(7);
-        chain0<false, false>(tmem + 256, t8::tile(sC, 128), t8::tile(sA, 128), 128, 128, false);  // dSt V2^T
-        chain0<true, true>(tmem + 256, t8::tile(sD, 64), t8::tile(sc, 64), 128, 64, true);        // Qh^T dAqb
-        chain0<true, true>(tmem + 256, t8::tile(sB, 128), t8::tile(sE, 128), 128, 128, true);     // Ah^T dAab
-        chain0<false, false>(tmem + 384, t8::tile(sC, 128), t8::tile(sD + CH64, 64), 64, 128, false);  // dSt v^T
-        chain0<true, true>(tmem + 384, t8::tile(sD, 64), t8::tile(sx, 64), 64, 64, true);         // Qh^T dAqk
-        chain0<true, true>(tmem + 384, t8::tile(sB, 128), t8::tile(sa, 128), 64, 128, true);      // Ah^T dAak
+        chain0<true, true>(tmem + 256, t8::tile(sB, 128), t8::tile(sE, 128), 128, 128, true);     // P4: Ah^T dAab
+        chain0<true, true>(tmem + 384, t8::tile(sB, 128), t8::tile(sa, 128), 64, 128, true);      // P5: Ah^T dAak
         umma_commit(&m4);
-        wait_or_flag(&m4, 0, p.status, 47);
+        wait_or_flag(&m4, 0, p.status, 88);
         TL(8);
     }
     if (warp < 16) {
@@ -1327,8 +1357,8 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         }
         const float dgl = __ldg(p.dgl + (size_t)g * K + k);
         // ---- after P1, P2: dv (lane = value channel; group w writes tokens 16w..16w+15) and dq
-        wait_idle_or_flag(&m1, 0, p.status, 48);
-        wait_idle_or_flag(&m2, 0, p.status, 49);
+        wait_idle_or_flag(&m1, 0, p.status, 89);
+        wait_idle_or_flag(&m2, 0, p.status, 90);
         tc_fence_after();
         {
             uint32_t v[16], u[16];
@@ -1345,7 +1375,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
                 if (i_lo + j < t_left) p.dq[base_qk + (size_t)j * tok_stride] = __float2bfloat16_rn(p.scale * eg[j + 1] * __uint_as_float(u[j]));
         }
         // ---- after P3: da = e^{ge-half} dAh
-        wait_idle_or_flag(&m3, 0, p.status, 50);
+        wait_idle_or_flag(&m3, 0, p.status, 91);
         tc_fence_after();
 #pragma unroll
         for (int hb = 0; hb < 2; ++hb) {
@@ -1362,7 +1392,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
             }
         }
         // ---- after P4, P5: dk, db and the reverse running sum for dgk
-        wait_idle_or_flag(&m4, 0, p.status, 51);
+        wait_idle_or_flag(&m4, 0, p.status, 92);
         tc_fence_after();
         if (tid == 0) TL(9);
         // per-thread element pointers into the hat tiles still in shared memory (token i sits 16 bytes after token i-1)
@@ -1558,7 +1588,8 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             return HDLA_OK;
         }
         ScanTcP sp = scan_params(nullptr, nullptr, nullptr, ht, nullptr, 1);
-        sp.ADD = U4(pl.zero); sp.R1 = U4(pl.zero); sp.add_stride = 0; sp.r1_stride = 0; sp.init_identity = 1;
+        sp.ADD = U4(pl.zero); sp.R1 = U4(pl.zero); sp.L1 = U4(pl.zero); sp.add_stride = 0; sp.r1_stride = 0;
+        sp.init_identity = 1;
         scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         return HDLA_OK;

@@ -8,11 +8,67 @@ direction rather than by the sum of copies and compute.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional
 
 import torch
 
 from .hrdplr import chunk_hrdplr_delta_rule
+
+def _parse_cpulist(text: str) -> set:
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+class numa_local_to(object):
+    """Context manager: run the calling thread on the CPUs of the NUMA node the GPU hangs off.
+
+    Pinned host memory is placed on the node of the thread that allocates it, and a DMA that has to
+    cross the socket interconnect runs at a fraction of the PCIe rate, so the pinned buffers of
+    ``chunk_fwd_bwd_from_host`` should be allocated (and the copies issued) inside this context.
+    Best effort: without NUMA information in sysfs, or when the node's CPUs are outside the allowed
+    set, nothing changes.  ``node`` is the node bound to, or None.  The previous affinity is restored
+    on exit."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.node = None
+        self._saved = None
+
+    def __enter__(self):
+        try:
+            pr = torch.cuda.get_device_properties(self.device)
+            bdf = f"{pr.pci_domain_id:04x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+            with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+                node = int(f.read().strip())
+            if node < 0:
+                return self
+            with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+                cpus = _parse_cpulist(f.read())
+            allowed = os.sched_getaffinity(0)
+            target = cpus & allowed
+            if target and target != allowed:
+                os.sched_setaffinity(0, target)
+                self._saved = allowed
+            if target:
+                self.node = node
+        except (OSError, ValueError, AttributeError, RuntimeError, AssertionError):
+            pass
+        return self
+
+    def __exit__(self, *exc):
+        if self._saved is not None:
+            try:
+                os.sched_setaffinity(0, self._saved)
+            except OSError:
+                pass
+        return False
+
 
 _IN = ("q", "k", "v", "a", "b", "gk")
 _OUT = ("o", "dq", "dk", "dv", "da", "db", "dgk")

@@ -72,3 +72,15 @@ def test_dtype_codes():
     assert _lib.dtype_code(torch.float32) == 0 and _lib.dtype_code(torch.bfloat16) == 1
     with pytest.raises(TypeError):
         _lib.dtype_code(torch.float16)
+
+
+def test_numa_binding_is_best_effort_and_restores_affinity():
+    import os
+    from hdla_impl_b200.host import _parse_cpulist, numa_local_to
+    assert _parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert _parse_cpulist("") == set()
+    before = os.sched_getaffinity(0)
+    with numa_local_to("cuda:0") as nb:         # no GPU here: nothing to bind to, nothing changes
+        inside = os.sched_getaffinity(0)
+        assert nb.node is None or inside <= before
+    assert os.sched_getaffinity(0) == before
