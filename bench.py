@@ -88,9 +88,9 @@ KERNEL_KIB = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch (GB) at cfg 1: one ncu capture at B=2 (a quarter of
 # cfg 1; traffic is proportional to the number of chunks), scaled by 4 -- see profiles/chunk_tc_pipeline_traffic.md
 KERNEL_NCU_TRAFFIC_GB = {
-    "prep_hat_kernel": 2.10, "gram_tc_kernel": 1.20, "inverse_tc_kernel": 0.35, "wu_tc_kernel": 1.39,
-    "scan_tc_kernel": (1.49 + 1.77) / 2, "out_tc_kernel": 1.09, "dau_tc_kernel": 1.08, "wy_bwd_tc_kernel": 2.24,
-    "grad_tc_kernel": 4.75,
+    "prep_hat_kernel": 2.09, "gram_tc_kernel": 1.20, "inverse_tc_kernel": 0.33, "wu_tc_kernel": 1.39,
+    "scan_tc_kernel": (1.51 + 1.79) / 2, "out_tc_kernel": 1.08, "dau_tc_kernel": 1.06, "wy_bwd_tc_kernel": 2.25,
+    "grad_tc_kernel": 4.85,
 }
 
 
