@@ -1201,11 +1201,6 @@ __device__ __forceinline__ void chain0(uint32_t tm, Tile A, Tile B, int N, int k
     t8::mma_chain<A_MN, B_MN>(tm, A, 0, 0, B, 0, 0, N, kdim, acc);
 }
 
-__device__ __forceinline__ float c8s(const uint4* tile, int rows, int r, int c) {      // element of a C8 tile in smem
-    const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(tile + (c >> 3) * rows + r);
-    return __bfloat162float(q[c & 7]);
-}
-
 __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint4* sA = reinterpret_cast<uint4*>(smem);          // 32 KB slots
