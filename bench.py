@@ -78,12 +78,12 @@ def bytes_per_token_head(C: int, D: int, elt: int) -> float:
 
 
 # Algorithmic HBM bytes per (chunk, head) of each kernel of the bf16 pipeline: every operand tile it
-# needs read once, every result written once (KiB; bf16 tiles, fp32 ghat/E; K = V = 128, chunk 64, R = 2).
+# needs read once, every result written once (KiB; bf16 tiles and un-gating factors, fp32 E; K = V = 128, chunk 64, R = 2).
 # scan_tc_kernel is launched twice per step (forward 192.5, reverse 225).
 KERNEL_KIB = {
-    "prep_hat_kernel": 272.5, "gram_tc_kernel": 168.0, "inverse_tc_kernel": 64.0, "wu_tc_kernel": 192.0,
+    "prep_hat_kernel": 256.5, "gram_tc_kernel": 168.0, "inverse_tc_kernel": 64.0, "wu_tc_kernel": 192.0,
     "scan_tc_kernel": (192.5 + 225.0) / 2, "out_tc_kernel": 136.0, "dau_tc_kernel": 152.0,
-    "wy_bwd_tc_kernel": 288.0, "grad_tc_kernel": 576.5,
+    "wy_bwd_tc_kernel": 288.0, "grad_tc_kernel": 560.5,
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch (GB) at cfg 1: one ncu capture at B=2 (a quarter of
 # cfg 1; traffic is proportional to the number of chunks), scaled by 4 -- see profiles/chunk_tc_pipeline_traffic.md

@@ -54,7 +54,7 @@ TcPlan make_tc_plan(const HdlaDims& d) {
     };
     p.status = off; off += 256;
     p.Qh = take(16384); p.Kh = take(16384); p.Ah = take(32768); p.Bh = take(32768); p.Vc = take(16384);
-    p.E = take(K * 4); p.ghat = take(C * K * 4);
+    p.E = take(K * 4); p.ghat = take(C * K * 2);
     p.Aqk = take(8192); p.Aqb = take(16384); p.Aak = take(16384); p.Aab = take(32768); p.M = take(32768);
     p.W = take(32768); p.P = take(32768); p.U = take(32768); p.Hs = take(32768); p.V2 = take(32768);
     p.HT = off; off += (((size_t)p.BH * K * V * 4 + 255) / 256) * 256;
@@ -120,7 +120,8 @@ struct PrepP {
     const __nv_bfloat16 *q, *k, *v, *a, *b;
     const void* gk;
     uint4 *Qh, *Kh, *Ah, *Bh, *Vc;
-    float *E, *ghat;
+    float* E;
+    __nv_bfloat16* ghat;                  // e^{gi - half} per (token, channel), bf16 row-major [64][128]
     float scale;
     int T, H, NT, gdt;
     int* status;
@@ -275,12 +276,9 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
             for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
             c1 = t8::pack8(y);
             sm100::st_global_32B(p.Bh + (size_t)g * CH128 + kc * 128 + r * R, c0, c1);
-            float gh[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) gh[j] = gi[j] - hf[j];
-            sm100::st_global_32B(p.ghat + (size_t)g * C * K + (size_t)r * K + kc * 8,
-                                 make_uint4(__float_as_uint(gh[0]), __float_as_uint(gh[1]), __float_as_uint(gh[2]), __float_as_uint(gh[3])),
-                                 make_uint4(__float_as_uint(gh[4]), __float_as_uint(gh[5]), __float_as_uint(gh[6]), __float_as_uint(gh[7])));
+            // the un-gating factors of the backward pass, e^{gi - half}, in bf16 (their error, 2^-9, is below the
+            // rounding of the bf16 gradients they scale)
+            *reinterpret_cast<uint4*>(p.ghat + (size_t)g * C * K + (size_t)r * K + kc * 8) = t8::pack8(ep);
         }
         cur = nxt;
         if (tid == 0) TL(2 + it);
@@ -1188,7 +1186,8 @@ __global__ void c8_to_rowmajor_kernel(const uint4* src, float* dst, int rows, in
 // ------------------------------------------------------------------------------------------
 struct GradP {
     const uint4 *Hs, *Bh, *dOc, *Kh, *dAqb, *dAqk, *DE, *dP, *Aak, *Aqk, *dW, *M, *dAab, *dAak, *V2, *Ah, *Qh, *Vc;
-    const float *ghat, *dgl;
+    const __nv_bfloat16* ghat;            // e^{gi - half}, bf16 [64][128] per tile
+    const float *E, *dgl;                 // e^{half} per (tile, channel); dgL from the reverse scan
     __nv_bfloat16 *dq, *dk, *dv, *da, *db;
     void* dgk;
     float scale;
@@ -1333,22 +1332,22 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         const size_t tok_stride = (size_t)p.H * K;                    // elements between tokens in [B,T,H,K]
         const size_t base_qk = (((size_t)b * p.T + (size_t)n * C + i_lo) * p.H + h) * K + k;
         const size_t base_ab = (((size_t)b * p.T + (size_t)n * C + i_lo) * R * p.H + h) * K + k;
-        // eg[j] = e^{ghat} of token i_lo + j - 1 (ghat = gi - half; the token before the chunk has ge - half = -half)
+        // eg[j] = e^{gi - half} of token i_lo + j - 1 (the token before the chunk has e^{ge - half} = e^{-half})
         float eg[17];
         uint32_t bhp[16];                                             // Bh rows 2i, 2i+1 of this thread's tokens
         {
-            const float* ghg = p.ghat + (size_t)g * C * K + k;
-            const float half = __ldg(ghg + (size_t)(C - 1) * K);
+            const unsigned short* egp = reinterpret_cast<const unsigned short*>(p.ghat + (size_t)g * C * K) + k;
+            const float e_half = __ldg(p.E + (size_t)g * K + k);
 #pragma unroll
-            for (int j = 0; j < 17; ++j) eg[j] = (i_lo + j - 1 >= 0) ? __ldg(ghg + (size_t)(i_lo + j - 1) * K) : -half;
+            for (int j = 0; j < 17; ++j)
+                eg[j] = (i_lo + j - 1 >= 0) ? __uint_as_float((uint32_t)__ldg(egp + (size_t)(i_lo + j - 1) * K) << 16) : 0.f;
+            if (i_lo == 0) eg[0] = __frcp_rn(e_half);        // e^{ge - half} of the chunk's first token
             const unsigned short* bg = reinterpret_cast<const unsigned short*>(p.Bh + g * CH128 + (k >> 3) * 128) + (k & 7);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const uint32_t lo = __ldg(bg + (size_t)(2 * (i_lo + j)) * 8), hi = __ldg(bg + (size_t)(2 * (i_lo + j) + 1) * 8);
                 bhp[j] = lo | (hi << 16);
             }
-#pragma unroll
-            for (int j = 0; j < 17; ++j) eg[j] = __expf(eg[j]);
         }
         const float dgl = __ldg(p.dgl + (size_t)g * K + k);
         // ---- after P1, P2: dv (lane = value channel; group w writes tokens 16w..16w+15) and dq
@@ -1544,7 +1543,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         if (e == cudaSuccess) e = cudaMemsetAsync(ws + pl.zero, 0, 32768, st);
         if (e != cudaSuccess) return fail(HDLA_ERR_CUDA, "workspace clear: %s", cudaGetErrorString(e));
         PrepP pp{(bp)q, (bp)k, (bp)v, (bp)a, (bp)b, gk, U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc),
-                 F(pl.E), F(pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status};
+                 F(pl.E), (__nv_bfloat16*)(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status};
         prep_hat_kernel<<<G, 128, 0, st>>>(pp);
         HDLA_CHECK_LAUNCH("prep_hat_kernel");
         GramP gp{U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Aak), U4(pl.Aab), status};
@@ -1713,7 +1712,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     // --- everything else: hat-operand gradients, dv, un-gating, dgk
     GradP gp{U4(pl.Hs), U4(pl.Bh), U4(pl.dOc), U4(pl.Kh), U4(pl.dAqb), U4(pl.dAqk), U4(pl.DE), U4(pl.dP), U4(pl.Aak),
              U4(pl.Aqk), U4(pl.dW), U4(pl.M), U4(pl.dAab), U4(pl.dAak), U4(pl.V2), U4(pl.Ah), U4(pl.Qh), U4(pl.Vc),
-             F(pl.ghat), F(pl.dgl), (bp)dq, (bp)dk, (bp)dv, (bp)da, (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype,
+             (bp)(ws + pl.ghat), F(pl.E), F(pl.dgl), (bp)dq, (bp)dk, (bp)dv, (bp)da, (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype,
              status};
     grad_tc_kernel<<<G, 544, kGradSmem, st>>>(gp);
     HDLA_CHECK_LAUNCH("grad_tc_kernel");
