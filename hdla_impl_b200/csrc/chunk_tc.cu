@@ -833,8 +833,13 @@ struct WyBwdP {
     const uint4 *M, *DV2, *Hs, *Vc, *P, *Ah;
     uint4 *dW, *dP, *dAak, *dAab;
     int* status;
+    long long G;           // number of tiles; the grid is persistent
 };
 
+// Persistent: one CTA per SM walks over the tiles g = blockIdx.x, blockIdx.x + gridDim.x, ...  The 208 KB of operand
+// slots leave no room for a second CTA, so the next tile's operands are requested as soon as the slot they go to has
+// been read for the last time (St, v, Ah after phase 2, dv2 after phase 3, M and P after phase 4): the loads of tile
+// n+1 run under phases 3 and 4 of tile n.
 __global__ void __launch_bounds__(128) wy_bwd_tc_kernel(WyBwdP p) {
     extern __shared__ __align__(1024) unsigned char smem[];
     uint4* bM = reinterpret_cast<uint4*>(smem);      // M
@@ -846,19 +851,21 @@ __global__ void __launch_bounds__(128) wy_bwd_tc_kernel(WyBwdP p) {
     uint4* bVc = bdP + CH128;                        // v  [64 x 128]
     __shared__ __align__(8) uint64_t ld1, ld2, mma_bar;
     __shared__ uint32_t tmem_s;
-    const long long g = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5;
     if (warp == 0) { tmem_alloc(&tmem_s, 256); tmem_relinquish(); }
     if (tid == 0) {
         mbar_init(&ld1, 1); mbar_init(&ld2, 1); mbar_init(&mma_bar, 1); fence_mbar_init();
-        mbar_expect_tx(&ld1, 98304);
-        bulk_g2s(bDV2, p.DV2 + g * CH128, 32768, &ld1);
-        bulk_g2s(bHs, p.Hs + g * CH128, 32768, &ld1);
-        bulk_g2s(bM, p.M + g * CH128, 32768, &ld1);
-        mbar_expect_tx(&ld2, 81920);
-        bulk_g2s(bVc, p.Vc + g * CH64, 16384, &ld2);
-        bulk_g2s(bP, p.P + g * CH128, 32768, &ld2);
-        bulk_g2s(bAh, p.Ah + g * CH128, 32768, &ld2);
+        const long long g = blockIdx.x;
+        if (g < p.G) {
+            mbar_expect_tx(&ld1, 98304);
+            bulk_g2s(bDV2, p.DV2 + g * CH128, 32768, &ld1);
+            bulk_g2s(bHs, p.Hs + g * CH128, 32768, &ld1);
+            bulk_g2s(bM, p.M + g * CH128, 32768, &ld1);
+            mbar_expect_tx(&ld2, 81920);
+            bulk_g2s(bVc, p.Vc + g * CH64, 16384, &ld2);
+            bulk_g2s(bP, p.P + g * CH128, 32768, &ld2);
+            bulk_g2s(bAh, p.Ah + g * CH128, 32768, &ld2);
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -868,105 +875,125 @@ __global__ void __launch_bounds__(128) wy_bwd_tc_kernel(WyBwdP p) {
                tAh = t8::tile(bAh, 128), tdP = t8::tile(bdP, 128), tVc = t8::tile(bVc, 64);
     const int r = tid;
     float f[64];
-    // ---- phase 1: dWh = dv2 St^T (cols 0..127), dP = M^T dv2 (cols 128..255)
-    wait_or_flag(&ld1, 0, p.status, 30);
-    if (tid == 0) {
-        t8::mma_chain<false, false>(tmem, tDV2, 0, 0, tHs, 0, 0, 128, 128, false);
-        t8::mma_chain<true, true>(tmem + 128, tM, 0, 0, tDV2, 0, 0, 128, 128, false);
-        umma_commit(&mma_bar);
-    }
-    wait_or_flag(&mma_bar, 0, p.status, 31);
-    tc_fence_after();
-#pragma unroll 1
-    for (int hh = 0; hh < 2; ++hh) {
-        tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-            const uint4 c = t8::pack8(f + c8 * 8);
-            bHs[(hh * 8 + c8) * 128 + r] = c;                       // dWh replaces St
-            p.dW[g * CH128 + (hh * 8 + c8) * 128 + r] = c;
+    uint32_t it = 0;
+    for (long long g = blockIdx.x; g < p.G; g += gridDim.x, ++it) {
+        const uint32_t ph = it & 1;
+        const long long gn = g + gridDim.x;              // next tile of this CTA
+        const bool more = gn < p.G;
+        // ---- phase 1: dWh = dv2 St^T (cols 0..127), dP = M^T dv2 (cols 128..255)
+        wait_or_flag(&ld1, ph, p.status, 30);
+        if (tid == 0) {
+            tc_fence_after();
+            t8::mma_chain<false, false>(tmem, tDV2, 0, 0, tHs, 0, 0, 128, 128, false);
+            t8::mma_chain<true, true>(tmem + 128, tM, 0, 0, tDV2, 0, 0, 128, 128, false);
+            umma_commit(&mma_bar);
         }
-        tmem_row64(t8::taddr(tmem, warp, 128 + hh * 64), f);
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-            const uint4 c = t8::pack8(f + c8 * 8);
-            bdP[(hh * 8 + c8) * 128 + r] = c;
-            p.dP[g * CH128 + (hh * 8 + c8) * 128 + r] = c;
-        }
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    // ---- phase 2: dAak = dP v^T (cols 0..63), dM = dv2 P^T + dWh Ah^T (cols 128..255)
-    wait_or_flag(&ld2, 0, p.status, 32);
-    if (tid == 0) {
+        wait_or_flag(&mma_bar, 0, p.status, 31);
         tc_fence_after();
-        t8::mma_chain<false, false>(tmem, tdP, 0, 0, tVc, 0, 0, 64, 128, false);
-        t8::mma_chain<false, false>(tmem + 128, tDV2, 0, 0, tP, 0, 0, 128, 128, false);
-        t8::mma_chain<false, false>(tmem + 128, tHs, 0, 0, tAh, 0, 0, 128, 128, true);
-        umma_commit(&mma_bar);
-    }
-    wait_or_flag(&mma_bar, 1, p.status, 33);
-    tc_fence_after();
-    {
-        const int i = r >> 1;
-        tmem_row64(t8::taddr(tmem, warp, 0), f);
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) if (!((c8 * 8 + j) < i)) f[c8 * 8 + j] = 0.f;
-            p.dAak[g * CH64 + c8 * 128 + r] = t8::pack8(f + c8 * 8);
-        }
 #pragma unroll 1
         for (int hh = 0; hh < 2; ++hh) {
-            tmem_row64(t8::taddr(tmem, warp, 128 + hh * 64), f);
+            tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
 #pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) bDV2[(hh * 8 + c8) * 128 + r] = t8::pack8(f + c8 * 8);   // dM replaces dv2
-        }
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    // ---- phase 3: tmp = M^T dM
-    if (tid == 0) {
-        tc_fence_after();
-        t8::mma_chain<true, true>(tmem, tM, 0, 0, tDV2, 0, 0, 128, 128, false);
-        umma_commit(&mma_bar);
-    }
-    wait_or_flag(&mma_bar, 0, p.status, 34);
-    tc_fence_after();
-#pragma unroll 1
-    for (int hh = 0; hh < 2; ++hh) {
-        tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) bP[(hh * 8 + c8) * 128 + r] = t8::pack8(f + c8 * 8);         // tmp replaces P
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    // ---- phase 4: dAab = smask(tmp M^T)
-    if (tid == 0) {
-        tc_fence_after();
-        t8::mma_chain<false, false>(tmem + 128, tP, 0, 0, tM, 0, 0, 128, 128, false);
-        umma_commit(&mma_bar);
-    }
-    wait_or_flag(&mma_bar, 1, p.status, 35);
-    tc_fence_after();
-    {
-        const int i = r >> 1;
-#pragma unroll 1
-        for (int hh = 0; hh < 2; ++hh) {
+            for (int c8 = 0; c8 < 8; ++c8) {
+                const uint4 c = t8::pack8(f + c8 * 8);
+                bHs[(hh * 8 + c8) * 128 + r] = c;                       // dWh replaces St
+                p.dW[g * CH128 + (hh * 8 + c8) * 128 + r] = c;
+            }
             tmem_row64(t8::taddr(tmem, warp, 128 + hh * 64), f);
 #pragma unroll
             for (int c8 = 0; c8 < 8; ++c8) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) if (!(((hh * 64 + c8 * 8 + j) >> 1) < i)) f[c8 * 8 + j] = 0.f;
-                p.dAab[g * CH128 + (hh * 8 + c8) * 128 + r] = t8::pack8(f + c8 * 8);
+                const uint4 c = t8::pack8(f + c8 * 8);
+                bdP[(hh * 8 + c8) * 128 + r] = c;
+                p.dP[g * CH128 + (hh * 8 + c8) * 128 + r] = c;
             }
         }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+        // ---- phase 2: dAak = dP v^T (cols 0..63), dM = dv2 P^T + dWh Ah^T (cols 128..255)
+        wait_or_flag(&ld2, ph, p.status, 32);
+        if (tid == 0) {
+            tc_fence_after();
+            t8::mma_chain<false, false>(tmem, tdP, 0, 0, tVc, 0, 0, 64, 128, false);
+            t8::mma_chain<false, false>(tmem + 128, tDV2, 0, 0, tP, 0, 0, 128, 128, false);
+            t8::mma_chain<false, false>(tmem + 128, tHs, 0, 0, tAh, 0, 0, 128, 128, true);
+            umma_commit(&mma_bar);
+        }
+        wait_or_flag(&mma_bar, 1, p.status, 33);
+        tc_fence_after();
+        if (tid == 0 && more) {                          // St, v, Ah slots have been read for the last time
+            mbar_expect_tx(&ld1, 98304);
+            bulk_g2s(bHs, p.Hs + gn * CH128, 32768, &ld1);
+            mbar_expect_tx(&ld2, 81920);
+            bulk_g2s(bVc, p.Vc + gn * CH64, 16384, &ld2);
+            bulk_g2s(bAh, p.Ah + gn * CH128, 32768, &ld2);
+        }
+        {
+            const int i = r >> 1;
+            tmem_row64(t8::taddr(tmem, warp, 0), f);
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) if (!((c8 * 8 + j) < i)) f[c8 * 8 + j] = 0.f;
+                p.dAak[g * CH64 + c8 * 128 + r] = t8::pack8(f + c8 * 8);
+            }
+#pragma unroll 1
+            for (int hh = 0; hh < 2; ++hh) {
+                tmem_row64(t8::taddr(tmem, warp, 128 + hh * 64), f);
+#pragma unroll
+                for (int c8 = 0; c8 < 8; ++c8) bDV2[(hh * 8 + c8) * 128 + r] = t8::pack8(f + c8 * 8);   // dM replaces dv2
+            }
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+        // ---- phase 3: tmp = M^T dM
+        if (tid == 0) {
+            tc_fence_after();
+            t8::mma_chain<true, true>(tmem, tM, 0, 0, tDV2, 0, 0, 128, 128, false);
+            umma_commit(&mma_bar);
+        }
+        wait_or_flag(&mma_bar, 0, p.status, 34);
+        tc_fence_after();
+        if (tid == 0 && more) bulk_g2s(bDV2, p.DV2 + gn * CH128, 32768, &ld1);     // dM has been consumed
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+            tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) bP[(hh * 8 + c8) * 128 + r] = t8::pack8(f + c8 * 8);         // tmp replaces P
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncthreads();
+        // ---- phase 4: dAab = smask(tmp M^T)
+        if (tid == 0) {
+            tc_fence_after();
+            t8::mma_chain<false, false>(tmem + 128, tP, 0, 0, tM, 0, 0, 128, 128, false);
+            umma_commit(&mma_bar);
+        }
+        wait_or_flag(&mma_bar, 1, p.status, 35);
+        tc_fence_after();
+        if (tid == 0 && more) {                          // M and tmp have been consumed
+            bulk_g2s(bM, p.M + gn * CH128, 32768, &ld1);
+            bulk_g2s(bP, p.P + gn * CH128, 32768, &ld2);
+        }
+        {
+            const int i = r >> 1;
+#pragma unroll 1
+            for (int hh = 0; hh < 2; ++hh) {
+                tmem_row64(t8::taddr(tmem, warp, 128 + hh * 64), f);
+#pragma unroll
+                for (int c8 = 0; c8 < 8; ++c8) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) if (!(((hh * 64 + c8 * 8 + j) >> 1) < i)) f[c8 * 8 + j] = 0.f;
+                    p.dAab[g * CH128 + (hh * 8 + c8) * 128 + r] = t8::pack8(f + c8 * 8);
+                }
+            }
+        }
+        // the accumulators are read; the next tile's first products overwrite them
+        tc_fence_before();
+        __syncthreads();
     }
-    tc_fence_before();
-    __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
@@ -1500,6 +1527,20 @@ int set_smem(Kern kern, int bytes) {
     return HDLA_OK;
 }
 
+// number of SMs of the current device (grid size of the persistent kernels), cached per host thread and device
+int sm_count() {
+    static thread_local int cached_dev = -1, cached = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cached_dev != dev) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached = n;
+        cached_dev = dev;
+    }
+    return cached;
+}
+
 }  // namespace
 
 bool tc_supported(const HdlaDims& d) {
@@ -1706,8 +1747,9 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     }
     // --- wy: dWh, dP, dAak, dAab in one kernel
     WyBwdP wyp{U4(pl.M), U4(pl.DV2), U4(pl.Hs), U4(pl.Vc), U4(pl.P), U4(pl.Ah), U4(pl.dW), U4(pl.dP), U4(pl.dAak),
-               U4(pl.dAab), status};
-    wy_bwd_tc_kernel<<<G, 128, kWySmem, st>>>(wyp);
+               U4(pl.dAab), status, (long long)G};
+    const unsigned wy_grid = G < (unsigned)sm_count() ? G : (unsigned)sm_count();      // one persistent CTA per SM
+    wy_bwd_tc_kernel<<<wy_grid, 128, kWySmem, st>>>(wyp);
     HDLA_CHECK_LAUNCH("wy_bwd_tc_kernel");
     // --- everything else: hat-operand gradients, dv, un-gating, dgk
     GradP gp{U4(pl.Hs), U4(pl.Bh), U4(pl.dOc), U4(pl.Kh), U4(pl.dAqb), U4(pl.dAqk), U4(pl.DE), U4(pl.dP), U4(pl.Aak),
