@@ -1423,16 +1423,16 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         float run = 0.f;
         float* dgk_loc = reinterpret_cast<float*>(sE) + (size_t)i_lo * K + k;    // [64][128] fp32 over the (consumed) dAab slot
 #pragma unroll
-        for (int hb = 1; hb >= 0; --hb) {
-            uint32_t vq[8], vk[8], va[16], vb[16];
-            tmem_ld_x8(t8::taddr(tmem, warp, i_lo + hb * 8), vq);
-            tmem_ld_x8(t8::taddr(tmem, warp, 384 + i_lo + hb * 8), vk);
-            tmem_ld_x16(t8::taddr(tmem, warp, 128 + 2 * i_lo + hb * 16), va);
-            tmem_ld_x16(t8::taddr(tmem, warp, 256 + 2 * i_lo + hb * 16), vb);
+        for (int hb = 3; hb >= 0; --hb) {                 // four tokens per accumulator read: fewer live registers
+            uint32_t vq[4], vk[4], va[8], vb[8];
+            tmem_ld_x4(t8::taddr(tmem, warp, i_lo + hb * 4), vq);
+            tmem_ld_x4(t8::taddr(tmem, warp, 384 + i_lo + hb * 4), vk);
+            tmem_ld_x8(t8::taddr(tmem, warp, 128 + 2 * i_lo + hb * 8), va);
+            tmem_ld_x8(t8::taddr(tmem, warp, 256 + 2 * i_lo + hb * 8), vb);
             tmem_wait_ld();
 #pragma unroll
-            for (int j = 7; j >= 0; --j) {
-                const int jt = hb * 8 + j;
+            for (int j = 3; j >= 0; --j) {
+                const int jt = hb * 4 + j;
                 const bool ok = i_lo + jt < t_left;
                 const float em = __frcp_rn(eg[jt + 1]);
                 const float dqh = __uint_as_float(vq[j]), dkh = __uint_as_float(vk[j]);
