@@ -1369,12 +1369,6 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
             for (int j = 0; j < 17; ++j)
                 eg[j] = (i_lo + j - 1 >= 0) ? __uint_as_float((uint32_t)__ldg(egp + (size_t)(i_lo + j - 1) * K) << 16) : 0.f;
             if (i_lo == 0) eg[0] = __frcp_rn(e_half);        // e^{ge - half} of the chunk's first token
-            const unsigned short* bg = reinterpret_cast<const unsigned short*>(p.Bh + g * CH128 + (k >> 3) * 128) + (k & 7);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const uint32_t lo = __ldg(bg + (size_t)(2 * (i_lo + j)) * 8), hi = __ldg(bg + (size_t)(2 * (i_lo + j) + 1) * 8);
-                bhp[j] = lo | (hi << 16);
-            }
         }
         const float dgl = __ldg(p.dgl + (size_t)g * K + k);
         // ---- after P1, P2: dv (lane = value channel; group w writes tokens 16w..16w+15) and dq
@@ -1410,6 +1404,14 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
                     p.da[base_ab + (size_t)(2 * jt) * tok_stride] = __float2bfloat16_rn(eg[jt] * __uint_as_float(v[2 * j]));
                     p.da[base_ab + (size_t)(2 * jt + 1) * tok_stride] = __float2bfloat16_rn(eg[jt] * __uint_as_float(v[2 * j + 1]));
                 }
+            }
+        }
+        {   // this thread's Bh elements (L2-resident: the tile was loaded for P1), requested before the wait below
+            const unsigned short* bg = reinterpret_cast<const unsigned short*>(p.Bh + g * CH128 + (k >> 3) * 128) + (k & 7);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const uint32_t lo = __ldg(bg + (size_t)(2 * (i_lo + j)) * 8), hi = __ldg(bg + (size_t)(2 * (i_lo + j) + 1) * 8);
+                bhp[j] = lo | (hi << 16);
             }
         }
         // ---- after P4, P5: dk, db and the reverse running sum for dgk
