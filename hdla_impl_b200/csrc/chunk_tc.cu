@@ -1254,15 +1254,16 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         mbar_init(&mc1, 1); mbar_init(&mc5, 1); mbar_init(&mc6, 1); mbar_init(&mc7, 1); mbar_init(&mc9, 1);
         mbar_init(&m1, 1); mbar_init(&m2, 1); mbar_init(&m3, 1); mbar_init(&m4, 1);
         fence_mbar_init();
-        // first loads, in the order the chains need them
+        // first loads, in the order the chains need them (the chain that frees two slots for the next
+        // generation of tiles comes first)
+        mbar_expect_tx(&ld[T_dPAak], 32768 + 16384);
+        bulk_g2s(sD, p.dP + g * CH128, 32768, &ld[T_dPAak]);
+        bulk_g2s(sE, p.Aak + g * CH64, 16384, &ld[T_dPAak]);
         mbar_expect_tx(&ld[T_StdO], 32768 + 16384);
         bulk_g2s(sA, p.Hs + g * CH128, 32768, &ld[T_StdO]);
         bulk_g2s(sa, p.dOc + g * CH64, 16384, &ld[T_StdO]);
         mbar_expect_tx(&ld[T_Aqk], 8192);
         bulk_g2s(sy, p.Aqk + g * 512, 8192, &ld[T_Aqk]);
-        mbar_expect_tx(&ld[T_dPAak], 32768 + 16384);
-        bulk_g2s(sD, p.dP + g * CH128, 32768, &ld[T_dPAak]);
-        bulk_g2s(sE, p.Aak + g * CH64, 16384, &ld[T_dPAak]);
         mbar_expect_tx(&ld[T_KhdAqk], 16384 + 8192);
         bulk_g2s(sb, p.Kh + g * CH64, 16384, &ld[T_KhdAqk]);
         bulk_g2s(sx, p.dAqk + g * 512, 8192, &ld[T_KhdAqk]);
@@ -1281,15 +1282,20 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         // Chains are issued as soon as their own tiles have landed, and the chains that read a slot for the last
         // time are issued first and committed on their own, so that the slot is refilled while the rest of the
         // product still runs.
+        wait_or_flag(&ld[T_dPAak], 0, p.status, 72);
+        chain0<true, true>(tmem + 64, t8::tile(sD, 128), t8::tile(sE, 128), 64, 128, false);      // P2: dP^T Aak
+        umma_commit(&mc6);                                                                        // slots D, E free
         wait_or_flag(&ld[T_StdO], 0, p.status, 70);
         chain0<false, false>(tmem, t8::tile(sA, 128), t8::tile(sa, 64), 64, 128, false);          // P1: St dO^T
         umma_commit(&mc1);                                                                        // slot A free
         wait_or_flag(&ld[T_Aqk], 0, p.status, 71);
-        chain0<true, true>(tmem + 64, t8::tile(sa, 64), t8::tile(sy, 64), 64, 64, false);         // P2: dO^T Aqk
+        chain0<true, true>(tmem + 64, t8::tile(sa, 64), t8::tile(sy, 64), 64, 64, true);          // P2: dO^T Aqk
         umma_commit(&mc5);                                                                        // slots a, y free
-        wait_or_flag(&ld[T_dPAak], 0, p.status, 72);
-        chain0<true, true>(tmem + 64, t8::tile(sD, 128), t8::tile(sE, 128), 64, 128, true);       // P2: dP^T Aak
-        umma_commit(&mc6);                                                                        // slots D, E free
+        wait_or_flag(&mc6, 0, p.status, 77);
+        mbar_expect_tx(&ld[T_M], 32768);
+        bulk_g2s(sD, p.M + g * CH128, 32768, &ld[T_M]);
+        mbar_expect_tx(&ld[T_dAab], 32768);
+        bulk_g2s(sE, p.dAab + g * CH128, 32768, &ld[T_dAab]);
         wait_or_flag(&mc1, 0, p.status, 73);
         mbar_expect_tx(&ld[T_dW], 32768);
         bulk_g2s(sA, p.dW + g * CH128, 32768, &ld[T_dW]);
@@ -1301,11 +1307,6 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         wait_or_flag(&ld[T_BhdAqb], 0, p.status, 76);
         chain0<true, false>(tmem, t8::tile(sB, 128), t8::tile(sc, 64), 64, 128, true);            // P1: Bh^T dAqb^T
         umma_commit(&m1);
-        wait_or_flag(&mc6, 0, p.status, 77);
-        mbar_expect_tx(&ld[T_M], 32768);
-        bulk_g2s(sD, p.M + g * CH128, 32768, &ld[T_M]);
-        mbar_expect_tx(&ld[T_dAab], 32768);
-        bulk_g2s(sE, p.dAab + g * CH128, 32768, &ld[T_dAab]);
         wait_or_flag(&ld[T_dSt], 0, p.status, 78);
         chain0<true, false>(tmem + 64, t8::tile(sC, 128), t8::tile(sb, 64), 64, 128, true);       // P2: dSt^T Kh^T
         umma_commit(&m2);
