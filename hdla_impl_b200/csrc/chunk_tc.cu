@@ -1372,23 +1372,29 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
             if (i_lo == 0) eg[0] = __frcp_rn(e_half);        // e^{ge - half} of the chunk's first token
         }
         const float dgl = __ldg(p.dgl + (size_t)g * K + k);
-        // ---- after P1, P2: dv (lane = value channel; group w writes tokens 16w..16w+15) and dq
+        // ---- after P1: dq
         wait_idle_or_flag(&m1, 0, p.status, 89);
+        tc_fence_after();
+        {
+            uint32_t u[16];
+            tmem_ld_x16(t8::taddr(tmem, warp, i_lo), u);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (i_lo + j < t_left) p.dq[base_qk + (size_t)j * tok_stride] = __float2bfloat16_rn(p.scale * eg[j + 1] * __uint_as_float(u[j]));
+        }
+        // ---- after P2: dv (lane = value channel; group w writes tokens 16w..16w+15)
         wait_idle_or_flag(&m2, 0, p.status, 90);
         tc_fence_after();
         {
-            uint32_t v[16], u[16];
+            uint32_t v[16];
             tmem_ld_x16(t8::taddr(tmem, warp, 64 + wg * 16), v);
-            tmem_ld_x16(t8::taddr(tmem, warp, i_lo), u);
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const int t = n * C + wg * 16 + j;
                 if (t < p.T) p.dv[(((size_t)b * p.T + t) * p.H + h) * V + k] = __float2bfloat16_rn(__uint_as_float(v[j]));
             }
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if (i_lo + j < t_left) p.dq[base_qk + (size_t)j * tok_stride] = __float2bfloat16_rn(p.scale * eg[j + 1] * __uint_as_float(u[j]));
         }
         // ---- after P3: da = e^{ge-half} dAh
         wait_idle_or_flag(&m3, 0, p.status, 91);
