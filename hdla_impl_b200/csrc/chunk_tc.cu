@@ -1220,6 +1220,7 @@ struct GradP {
     float scale;
     int T, H, NT, gdt;
     int* status;
+    long long G;           // number of tiles; the grid is persistent
 };
 
 template <bool A_MN, bool B_MN>
@@ -1243,17 +1244,27 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
     __shared__ __align__(8) uint64_t ld[13], mc1, mc5, mc6, mc7, mc9, m1, m2, m3, m4;
     enum { T_StdO, T_Aqk, T_dPAak, T_KhdAqk, T_BhdAqb, T_dSt, T_dW, T_dAak, T_M, T_dAab, T_V2, T_QhVc, T_Ah };
     __shared__ uint32_t tmem_s;
-    const long long g = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5;
     const bool producer = tid == 512;                   // lane 0 of the seventeenth warp loads tiles and issues MMAs
     if (warp == 0) { tmem_alloc(&tmem_s, 512); tmem_relinquish(); }
     if (producer) {
-        TL(0);
 #pragma unroll
         for (int i = 0; i < 13; ++i) mbar_init(&ld[i], 1);
         mbar_init(&mc1, 1); mbar_init(&mc5, 1); mbar_init(&mc6, 1); mbar_init(&mc7, 1); mbar_init(&mc9, 1);
         mbar_init(&m1, 1); mbar_init(&m2, 1); mbar_init(&m3, 1); mbar_init(&m4, 1);
         fence_mbar_init();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_s;
+    // TMEM columns: dQh^T 0..63, dv^T 64..127, dAh^T 128..255, dBh^T 256..383, dKh^T 384..447
+    uint32_t it = 0;
+#pragma unroll 1
+    for (long long g = blockIdx.x; g < p.G; g += gridDim.x, ++it) {
+    const uint32_t ph = it & 1;
+    if (producer) {
+        TL(0);
         // first loads, in the order the chains need them (the chain that frees two slots for the next
         // generation of tiles comes first)
         mbar_expect_tx(&ld[T_dPAak], 32768 + 16384);
@@ -1272,77 +1283,70 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         bulk_g2s(sc, p.dAqb + g * CH64, 16384, &ld[T_BhdAqb]);
         mbar_expect_tx(&ld[T_dSt], 32768);
         bulk_g2s(sC, p.DE + g * CH128, 32768, &ld[T_dSt]);
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = tmem_s;
-    // TMEM columns: dQh^T 0..63, dv^T 64..127, dAh^T 128..255, dBh^T 256..383, dKh^T 384..447
-    if (producer) {
         // Chains are issued as soon as their own tiles have landed, and the chains that read a slot for the last
         // time are issued first and committed on their own, so that the slot is refilled while the rest of the
         // product still runs.
-        wait_or_flag(&ld[T_dPAak], 0, p.status, 72);
+        wait_or_flag(&ld[T_dPAak], ph, p.status, 72);
         chain0<true, true>(tmem + 64, t8::tile(sD, 128), t8::tile(sE, 128), 64, 128, false);      // P2: dP^T Aak
         umma_commit(&mc6);                                                                        // slots D, E free
-        wait_or_flag(&ld[T_StdO], 0, p.status, 70);
+        wait_or_flag(&ld[T_StdO], ph, p.status, 70);
         chain0<false, false>(tmem, t8::tile(sA, 128), t8::tile(sa, 64), 64, 128, false);          // P1: St dO^T
         umma_commit(&mc1);                                                                        // slot A free
-        wait_or_flag(&ld[T_Aqk], 0, p.status, 71);
+        wait_or_flag(&ld[T_Aqk], ph, p.status, 71);
         chain0<true, true>(tmem + 64, t8::tile(sa, 64), t8::tile(sy, 64), 64, 64, true);          // P2: dO^T Aqk
         umma_commit(&mc5);                                                                        // slots a, y free
-        wait_or_flag(&mc6, 0, p.status, 77);
+        wait_or_flag(&mc6, ph, p.status, 77);
         mbar_expect_tx(&ld[T_M], 32768);
         bulk_g2s(sD, p.M + g * CH128, 32768, &ld[T_M]);
         mbar_expect_tx(&ld[T_dAab], 32768);
         bulk_g2s(sE, p.dAab + g * CH128, 32768, &ld[T_dAab]);
-        wait_or_flag(&mc1, 0, p.status, 73);
+        wait_or_flag(&mc1, ph, p.status, 73);
         mbar_expect_tx(&ld[T_dW], 32768);
         bulk_g2s(sA, p.dW + g * CH128, 32768, &ld[T_dW]);
-        wait_or_flag(&ld[T_KhdAqk], 0, p.status, 74);
+        wait_or_flag(&ld[T_KhdAqk], ph, p.status, 74);
         chain0<true, false>(tmem, t8::tile(sb, 64), t8::tile(sx, 64), 64, 64, true);              // P1: Kh^T dAqk^T
-        wait_or_flag(&mc5, 0, p.status, 75);
+        wait_or_flag(&mc5, ph, p.status, 75);
         mbar_expect_tx(&ld[T_dAak], 16384);
         bulk_g2s(sa, p.dAak + g * CH64, 16384, &ld[T_dAak]);
-        wait_or_flag(&ld[T_BhdAqb], 0, p.status, 76);
+        wait_or_flag(&ld[T_BhdAqb], ph, p.status, 76);
         chain0<true, false>(tmem, t8::tile(sB, 128), t8::tile(sc, 64), 64, 128, true);            // P1: Bh^T dAqb^T
         umma_commit(&m1);
-        wait_or_flag(&ld[T_dSt], 0, p.status, 78);
+        wait_or_flag(&ld[T_dSt], ph, p.status, 78);
         chain0<true, false>(tmem + 64, t8::tile(sC, 128), t8::tile(sb, 64), 64, 128, true);       // P2: dSt^T Kh^T
         umma_commit(&m2);
         TL(4);
-        wait_or_flag(&ld[T_dAab], 0, p.status, 79);
+        wait_or_flag(&ld[T_dAab], ph, p.status, 79);
         chain0<true, false>(tmem + 128, t8::tile(sB, 128), t8::tile(sE, 128), 128, 128, false);   // P3: Bh^T dAab^T
         umma_commit(&mc9);                                                                        // slot B free
-        wait_or_flag(&ld[T_dW], 0, p.status, 80);
-        wait_or_flag(&ld[T_M], 0, p.status, 81);
+        wait_or_flag(&ld[T_dW], ph, p.status, 80);
+        wait_or_flag(&ld[T_M], ph, p.status, 81);
         chain0<true, true>(tmem + 128, t8::tile(sA, 128), t8::tile(sD, 128), 128, 128, true);     // P3: dWh^T M
         umma_commit(&mc7);                                                                        // slots A, D free
-        wait_or_flag(&ld[T_dAak], 0, p.status, 82);
+        wait_or_flag(&ld[T_dAak], ph, p.status, 82);
         chain0<true, false>(tmem + 128, t8::tile(sb, 64), t8::tile(sa, 128), 128, 64, true);      // P3: Kh^T dAak^T
         umma_commit(&m3);
-        wait_or_flag(&mc9, 0, p.status, 83);
+        wait_or_flag(&mc9, ph, p.status, 83);
         mbar_expect_tx(&ld[T_Ah], 32768);
         bulk_g2s(sB, p.Ah + g * CH128, 32768, &ld[T_Ah]);
-        wait_or_flag(&mc7, 0, p.status, 84);
+        wait_or_flag(&mc7, ph, p.status, 84);
         TL(6);
         mbar_expect_tx(&ld[T_V2], 32768);
         bulk_g2s(sA, p.V2 + g * CH128, 32768, &ld[T_V2]);
         mbar_expect_tx(&ld[T_QhVc], 16384 + 16384);
         bulk_g2s(sD, p.Qh + g * CH64, 16384, &ld[T_QhVc]);
         bulk_g2s(sD + CH64, p.Vc + g * CH64, 16384, &ld[T_QhVc]);
-        wait_or_flag(&ld[T_V2], 0, p.status, 85);
+        wait_or_flag(&ld[T_V2], ph, p.status, 85);
         chain0<false, false>(tmem + 256, t8::tile(sC, 128), t8::tile(sA, 128), 128, 128, false);  // P4: dSt V2^T
-        wait_or_flag(&ld[T_QhVc], 0, p.status, 86);
+        wait_or_flag(&ld[T_QhVc], ph, p.status, 86);
         chain0<false, false>(tmem + 384, t8::tile(sC, 128), t8::tile(sD + CH64, 64), 64, 128, false);  // P5: dSt v^T
         chain0<true, true>(tmem + 256, t8::tile(sD, 64), t8::tile(sc, 64), 128, 64, true);        // P4: Qh^T dAqb
         chain0<true, true>(tmem + 384, t8::tile(sD, 64), t8::tile(sx, 64), 64, 64, true);         // P5: Qh^T dAqk
-        wait_or_flag(&ld[T_Ah], 0, p.status, 87);
+        wait_or_flag(&ld[T_Ah], ph, p.status, 87);
         TL(7);
         chain0<true, true>(tmem + 256, t8::tile(sB, 128), t8::tile(sE, 128), 128, 128, true);     // P4: Ah^T dAab
         chain0<true, true>(tmem + 384, t8::tile(sB, 128), t8::tile(sa, 128), 64, 128, true);      // P5: Ah^T dAak
         umma_commit(&m4);
-        wait_or_flag(&m4, 0, p.status, 88);
+        wait_or_flag(&m4, ph, p.status, 88);
         TL(8);
     }
     if (warp < 16) {
@@ -1373,7 +1377,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         }
         const float dgl = __ldg(p.dgl + (size_t)g * K + k);
         // ---- after P1: dq
-        wait_idle_or_flag(&m1, 0, p.status, 89);
+        wait_idle_or_flag(&m1, ph, p.status, 89);
         tc_fence_after();
         {
             uint32_t u[16];
@@ -1384,7 +1388,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
                 if (i_lo + j < t_left) p.dq[base_qk + (size_t)j * tok_stride] = __float2bfloat16_rn(p.scale * eg[j + 1] * __uint_as_float(u[j]));
         }
         // ---- after P2: dv (lane = value channel; group w writes tokens 16w..16w+15)
-        wait_idle_or_flag(&m2, 0, p.status, 90);
+        wait_idle_or_flag(&m2, ph, p.status, 90);
         tc_fence_after();
         {
             uint32_t v[16];
@@ -1397,7 +1401,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
             }
         }
         // ---- after P3: da = e^{ge-half} dAh
-        wait_idle_or_flag(&m3, 0, p.status, 91);
+        wait_idle_or_flag(&m3, ph, p.status, 91);
         tc_fence_after();
 #pragma unroll
         for (int hb = 0; hb < 2; ++hb) {
@@ -1422,7 +1426,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
             }
         }
         // ---- after P4, P5: dk, db and the reverse running sum for dgk
-        wait_idle_or_flag(&m4, 0, p.status, 92);
+        wait_idle_or_flag(&m4, ph, p.status, 92);
         tc_fence_after();
         if (tid == 0) TL(9);
         // per-thread element pointers into the hat tiles still in shared memory (token i sits 16 bytes after token i-1)
@@ -1472,9 +1476,14 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
             if (t < p.T) st_elem(p.dgk, (((size_t)b * p.T + t) * p.H + h) * K + k, p.gdt, dgk_loc[jj * K] + add);
         }
     }
+    // every thread is done with this tile's slots and accumulators before the next tile's first loads and products
     tc_fence_before();
     __syncthreads();
+    tc_fence_after();
     if (tid == 0) TL(12);
+    }
+    tc_fence_before();
+    __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
@@ -1764,8 +1773,9 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     GradP gp{U4(pl.Hs), U4(pl.Bh), U4(pl.dOc), U4(pl.Kh), U4(pl.dAqb), U4(pl.dAqk), U4(pl.DE), U4(pl.dP), U4(pl.Aak),
              U4(pl.Aqk), U4(pl.dW), U4(pl.M), U4(pl.dAab), U4(pl.dAak), U4(pl.V2), U4(pl.Ah), U4(pl.Qh), U4(pl.Vc),
              (bp)(ws + pl.ghat), F(pl.E), F(pl.dgl), (bp)dq, (bp)dk, (bp)dv, (bp)da, (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype,
-             status};
-    grad_tc_kernel<<<G, 544, kGradSmem, st>>>(gp);
+             status, (long long)G};
+    const unsigned grad_grid = G < (unsigned)sm_count() ? G : (unsigned)sm_count();    // one persistent CTA per SM
+    grad_tc_kernel<<<grad_grid, 544, kGradSmem, st>>>(gp);
     HDLA_CHECK_LAUNCH("grad_tc_kernel");
     return HDLA_OK;
 }
