@@ -90,7 +90,7 @@ KERNEL_KIB = {
 KERNEL_NCU_TRAFFIC_GB = {
     "prep_hat_kernel": 2.09, "gram_tc_kernel": 1.20, "inverse_tc_kernel": 0.33, "wu_tc_kernel": 1.39,
     "scan_tc_kernel": (1.51 + 1.79) / 2, "out_tc_kernel": 1.08, "dau_tc_kernel": 1.06, "wy_bwd_tc_kernel": 2.25,
-    "grad_tc_kernel": 4.85,
+    "grad_tc_kernel": 4.62,
 }
 
 
