@@ -309,7 +309,9 @@ def run_ours(args, rank, world, local_rank):
                     out_host[i] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
                 out_host[i].copy_(t, non_blocking=True)
         else:
-            chunk_fwd_bwd_from_host(host, out_host, R, dev, scale=scale, chunk_size=C, slice_batch=1)
+            # enqueue only: successive steps stream through the copy engines (the copy-in of step s+1 runs under
+            # the copy-out of step s); the clock stops after the last copy-out has completed
+            chunk_fwd_bwd_from_host(host, out_host, R, dev, scale=scale, chunk_size=C, slice_batch=1, sync=False)
 
     with numa_local_to(dev) as numa:
         e2e_step()

@@ -74,12 +74,28 @@ _IN = ("q", "k", "v", "a", "b", "gk")
 _OUT = ("o", "dq", "dk", "dv", "da", "db", "dgk")
 
 
+_copy_streams: Dict[int, tuple] = {}
+
+
+def _streams(dev: torch.device):
+    """One copy-in and one copy-out stream per device, kept across calls so that the copies of successive
+    calls stay ordered among themselves."""
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx not in _copy_streams:
+        _copy_streams[idx] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    return _copy_streams[idx]
+
+
 def chunk_fwd_bwd_from_host(host_in: Dict[str, torch.Tensor], host_out: Optional[Dict[str, torch.Tensor]],
                             RANK_AB: int, device, scale: Optional[float] = None, chunk_size: int = 64,
-                            slice_batch: int = 1) -> Dict[str, torch.Tensor]:
+                            slice_batch: int = 1, sync: bool = True) -> Dict[str, torch.Tensor]:
     """``host_in``: pinned CPU tensors q,k,v,a,b,gk and ``do`` (gradient of o), layouts as in
     ``chunk_hrdplr_delta_rule``.  Returns (and fills, if given) ``host_out`` with pinned CPU tensors
-    o,dq,dk,dv,da,db,dgk.  Synchronises the device before returning."""
+    o,dq,dk,dv,da,db,dgk.  With ``sync`` (default) the device is synchronised before returning.  With
+    ``sync=False`` the call only enqueues: the current stream is made to wait for the last copy-out, so
+    work enqueued on it afterwards (or an event recorded on it) is ordered after the results, and the
+    copy-in of a following call overlaps this call's copy-out; the caller must not touch ``host_in`` /
+    ``host_out`` before synchronising."""
     dev = torch.device(device)
     B = host_in["q"].shape[0]
     if host_out is None:
@@ -94,7 +110,7 @@ def chunk_fwd_bwd_from_host(host_in: Dict[str, torch.Tensor], host_out: Optional
             src = host_in[ref[n]]
             host_out[n] = torch.empty(src.shape, dtype=src.dtype, pin_memory=True)
     cur = torch.cuda.current_stream(dev)
-    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    s_in, s_out = _streams(dev)
     s_in.wait_stream(cur)
     bounds = [(i, min(i + slice_batch, B)) for i in range(0, B, slice_batch)]
     stage = [None, None]                      # two sets of device input buffers
@@ -110,6 +126,7 @@ def chunk_fwd_bwd_from_host(host_in: Dict[str, torch.Tensor], host_out: Optional
                                                   device=dev) for n in names_in}
                 for n in names_in:
                     stage[slot][n].copy_(host_in[n][lo:hi], non_blocking=True)
+                    stage[slot][n].record_stream(cur)          # allocated on the copy stream, read by the kernels
                 ready = torch.cuda.Event()
                 ready.record(s_in)
             cur.wait_event(ready)
@@ -128,5 +145,6 @@ def chunk_fwd_bwd_from_host(host_in: Dict[str, torch.Tensor], host_out: Optional
                 stage[slot][n].requires_grad_(False)
         cur.wait_stream(s_out)
         cur.wait_stream(s_in)
-    torch.cuda.synchronize(dev)
+    if sync:
+        torch.cuda.synchronize(dev)
     return host_out

@@ -276,6 +276,24 @@ def test_host_pipeline_matches_device_call(dev):
         assert torch.equal(out[n], t.detach().cpu()), n
 
 
+def test_host_pipeline_streams_across_calls(dev):
+    """With sync=False successive calls only enqueue; after one synchronisation every call's results are there."""
+    from hdla_impl_b200.host import chunk_fwd_bwd_from_host
+    names = ("q", "k", "v", "a", "b", "gk")
+    hosts, outs, refs = [], [], []
+    for seed in (21, 22, 23):
+        x = make_inputs(2, 128, 2, 128, 128, R, seed=seed, dtype=torch.bfloat16)
+        hosts.append({n: x[n].pin_memory() for n in names + ("do",)})
+    for h in hosts:
+        refs.append({k: v.clone() for k, v in chunk_fwd_bwd_from_host(h, None, R, dev, chunk_size=64).items()})
+    for h in hosts:                                   # enqueue all three, synchronise once
+        outs.append(chunk_fwd_bwd_from_host(h, None, R, dev, chunk_size=64, sync=False))
+    torch.cuda.synchronize(dev)
+    for o, r in zip(outs, refs):
+        for n in r:
+            assert torch.equal(o[n], r[n]), n
+
+
 def _param_ab_torch(beta, k, log_f):
     """Restatement of the reference's parameterize_a_b (HRDPLR/hdla_custom.py:19-43) with the missing return."""
     a_t1 = -beta * k
