@@ -294,6 +294,30 @@ def test_host_pipeline_streams_across_calls(dev):
             assert torch.equal(o[n], r[n]), n
 
 
+@pytest.mark.parametrize("B,T,H", [(1, 200, 3), (2, 1000, 5), (3, 2048, 7)])
+def test_repeated_calls_are_bit_identical(dev, B, T, H):
+    """No kernel accumulates with atomics, so repeated calls on the same inputs must agree bit for bit: a
+    difference would mean a race between the loads, products and epilogues of the pipelined kernels (tile counts
+    below, above and not a multiple of the persistent grids; ragged last chunk; h0 and dht given)."""
+    import hdla_impl_b200 as H_
+    x = make_inputs(B, T, H, 128, 128, R, seed=B * 100 + H, dtype=torch.bfloat16)
+    names = ("q", "k", "v", "a", "b", "gk")
+    lv = [x[n].to(dev).requires_grad_(True) for n in names]
+    do = x["do"].to(dev)
+    h0 = (torch.randn(B, H, 128, 128, generator=torch.Generator().manual_seed(5)) * 0.02).to(dev)
+    ref = None
+    for _ in range(4):
+        o, ht = H_.chunk_hrdplr_delta_rule(*lv, R, chunk_size=64, initial_state=h0, output_final_state=True)
+        g = torch.autograd.grad([o, ht], lv, [do, torch.full_like(ht, 0.01)])
+        cur = [o.detach().clone(), ht.detach().clone()] + [t.clone() for t in g]
+        if ref is None:
+            ref = cur
+        else:
+            for i, (a_, b_) in enumerate(zip(cur, ref)):
+                assert torch.equal(a_, b_), f"tensor {i} differs between repeated calls"
+    H_.check_status()
+
+
 def _param_ab_torch(beta, k, log_f):
     """Restatement of the reference's parameterize_a_b (HRDPLR/hdla_custom.py:19-43) with the missing return."""
     a_t1 = -beta * k
