@@ -409,8 +409,10 @@ __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
     // One 32 KB tile holds L = Aab and, block by block, the inverse that replaces it: a block of L is read for the
     // last time at the level that produces the block of M at the same place (later levels read it only into
     // accumulator rows that are never used).
+    // The X blocks of a level (at most 64 x 64 in all) live in the tile's upper right quadrant (rows 0..63, columns
+    // 64..127), which is zero in L and in M and which the products read only into accumulator rows that are never
+    // used; it is cleared again before M is stored.  32 KB per CTA: seven CTAs per SM.
     uint4* sD = reinterpret_cast<uint4*>(smem);      // 32 KB: L, overwritten by M
-    uint4* sX = sD + CH128;                          //  8 KB: the X blocks of one level
     __shared__ __align__(8) uint64_t ld_bar, mma_bar;
     __shared__ uint32_t tmem_s;
     const long long g = blockIdx.x;
@@ -456,7 +458,6 @@ __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
 #pragma unroll 1
     for (int bs = 16; bs <= 64; bs <<= 1) {
         const int npair = 64 / bs;
-        const int xt_chunks = bs * bs / 8;                      // 16-byte chunks of one pair's X block
         if (tid == 0) {
             tc_fence_after();
             for (int pr = 0; pr < npair; ++pr) {
@@ -472,14 +473,14 @@ __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
         const bool odd = blk & 1;
         const int rr = tid - blk * bs;
         {
-            uint4* xt = sX + pr * xt_chunks;                    // C8 tile [bs x bs]
+            uint4* xt = sD + (8 + ((pr * bs) >> 3)) * 128;      // rows 0..bs-1, columns 64 + pr bs .. of the tile
             for (int cg = 0; cg < (bs >> 3); ++cg) {
                 uint32_t v[8]; float f[8];
                 tmem_ld_x8(t8::taddr(tmem, warp, pr * bs + cg * 8), v);
                 tmem_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(v[j]);
-                if (odd) xt[cg * bs + rr] = t8::pack8(f);
+                if (odd) xt[cg * 128 + rr] = t8::pack8(f);
             }
         }
         fence_proxy_async();
@@ -489,8 +490,7 @@ __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
             tc_fence_after();
             for (int pr2 = 0; pr2 < npair; ++pr2) {
                 const int I = (2 * pr2 + 1) * bs;
-                const Tile tX = t8::tile(sX + pr2 * xt_chunks, bs);
-                t8::mma_chain<false, true>(tmem + pr2 * bs, tD, I, 0, tX, 0, 0, bs, bs, false);    // Y = D[:, I] X
+                t8::mma_chain<false, true>(tmem + pr2 * bs, tD, I, 0, tD, 0, 64 + pr2 * bs, bs, bs, false);   // Y = D[:, I] X
             }
             umma_commit(&mma_bar);
         }
@@ -512,6 +512,9 @@ __global__ void __launch_bounds__(128) inverse_tc_kernel(InvP p) {
         tc_fence_before();
         __syncthreads();
     }
+    for (int e = tid; e < 512; e += 128) sD[(8 + (e >> 6)) * 128 + (e & 63)] = make_uint4(0, 0, 0, 0);    // the quadrant
+    fence_proxy_async();
+    __syncthreads();
     if (tid == 0) {
         bulk_s2g(p.M + g * CH128, sD, 32768);
         bulk_commit();
@@ -1582,7 +1585,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     cudaGetDevice(&dev);
     if (attr_dev != dev) {
         TRY(set_smem(gram_tc_kernel, 98304 + 1024));
-        TRY(set_smem(inverse_tc_kernel, 40960));
+        TRY(set_smem(inverse_tc_kernel, 32768));
         TRY(set_smem(wu_tc_kernel, 98304));
         TRY(set_smem(scan_tc_kernel, 196608));
         TRY(set_smem(out_tc_kernel, 73728));
@@ -1609,7 +1612,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         gram_tc_kernel<<<G, 128, 98304 + 1024, st>>>(gp);
         HDLA_CHECK_LAUNCH("gram_tc_kernel");
         InvP ivp{U4(pl.Aab), U4(pl.M), status};
-        inverse_tc_kernel<<<G, 128, 40960, st>>>(ivp);
+        inverse_tc_kernel<<<G, 128, 32768, st>>>(ivp);
         HDLA_CHECK_LAUNCH("inverse_tc_kernel");
         WuP wp{U4(pl.M), U4(pl.Ah), U4(pl.Aak), U4(pl.Vc), U4(pl.P), U4(pl.U), U4(pl.W), status};
         wu_tc_kernel<<<G, 128, 98304, st>>>(wp);
