@@ -118,25 +118,26 @@ class _CPChunkFunction(torch.autograd.Function):
 
         with torch.cuda.device(dev):
             fwd(_lib.PHASE_PRE, None, None, None)
-            Tr = torch.empty(B, H, K, K, **f32)
-            Fr = torch.empty(B, H, K, V, **f32)
-            fwd(_lib.PHASE_TRANSITION, None, None, Tr)
-            fwd(_lib.PHASE_STATE, None, None, Fr)
-            Ts = [torch.empty_like(Tr) for _ in range(world)]
-            Fs = [torch.empty_like(Fr) for _ in range(world)]
-            dist.all_gather(Ts, Tr, group=group)
-            dist.all_gather(Fs, Fr, group=group)
-            S = torch.zeros(B, H, K, V, **f32) if initial_state is None else initial_state.to(torch.float32).clone()
-            src0 = dist.get_global_rank(group, 0) if group is not None else 0
-            if initial_state is not None or world > 1:
-                dist.broadcast(S, src=src0, group=group)           # the initial state lives on rank 0
+            # one collective per direction: every rank contributes its transition map, its state-from-zero map and
+            # (rank 0 only) the sequence's initial state, packed as [3, B, H, K, V] (K == V on this path)
+            pack = torch.empty(3, B, H, K, V, **f32)
+            fwd(_lib.PHASE_TRANSITION, None, None, pack[0])
+            fwd(_lib.PHASE_STATE, None, None, pack[1])
+            if rank == 0 and initial_state is not None:
+                pack[2].copy_(initial_state)
+            else:
+                pack[2].zero_()
+            maps = torch.empty(world, 3, B, H, K, V, **f32)
+            dist.all_gather_into_tensor(maps, pack, group=group)
+            Ts, Fs = maps[:, 0], maps[:, 1]
+            S = maps[0, 2].clone()                                 # the initial state lives on rank 0
             for j in range(rank):
                 S = torch.matmul(Ts[j], S) + Fs[j]
             o = torch.empty_like(v)
             ht = torch.empty(B, H, K, V, **f32)
             fwd(_lib.PHASE_POST, S, o, ht)
             _post_status(ws, dev)
-        ctx.save_for_backward(q, k, v, a, b, gk, S, *Ts)
+        ctx.save_for_backward(q, k, v, a, b, gk, S, maps)
         ctx.ws, ctx.scale, ctx.R, ctx.chunk, ctx.group = ws, scale, RANK_AB, chunk_size, group
         ctx.has_h0 = initial_state is not None
         return o, ht
@@ -146,7 +147,8 @@ class _CPChunkFunction(torch.autograd.Function):
         import ctypes as C
         from . import _lib
         from .hrdplr import _dims, check_status
-        q, k, v, a, b, gk, S_in, *Ts = ctx.saved_tensors
+        q, k, v, a, b, gk, S_in, maps = ctx.saved_tensors
+        Ts = maps[:, 0]
         group = ctx.group
         dev = q.device
         rank, world = dist.get_rank(group), dist.get_world_size(group)
@@ -170,15 +172,17 @@ class _CPChunkFunction(torch.autograd.Function):
 
         with torch.cuda.device(dev):
             bwd(_lib.PHASE_PRE, None, None, False)
-            Gr = torch.empty(B, H, K, V, **f32)
-            bwd(_lib.PHASE_STATE, None, Gr, False)
-            Gs = [torch.empty_like(Gr) for _ in range(world)]
-            dist.all_gather(Gs, Gr, group=group)
-            D = torch.zeros(B, H, K, V, **f32)
+            # mirror image: gradient-from-zero maps and (last rank only) the gradient of the sequence's final state
+            pack = torch.empty(2, B, H, K, V, **f32)
+            bwd(_lib.PHASE_STATE, None, pack[0], False)
             if rank == world - 1 and dht is not None:
-                D = dht.to(torch.float32).contiguous().clone()
-            last = dist.get_global_rank(group, world - 1) if group is not None else world - 1
-            dist.broadcast(D, src=last, group=group)               # gradient of the sequence's final state
+                pack[1].copy_(dht)
+            else:
+                pack[1].zero_()
+            gmaps = torch.empty(world, 2, B, H, K, V, **f32)
+            dist.all_gather_into_tensor(gmaps, pack, group=group)
+            Gs = gmaps[:, 0]
+            D = gmaps[world - 1, 1].clone()
             for j in range(world - 1, rank, -1):
                 D = torch.matmul(Ts[j].transpose(-1, -2), D) + Gs[j]
             dh0 = torch.empty(B, H, K, V, **f32)
