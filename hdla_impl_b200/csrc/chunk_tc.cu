@@ -35,6 +35,7 @@ struct TcPlan {
     long long G;
     size_t status, Qh, Kh, Ah, Bh, Vc, E, ghat, Aqk, Aqb, Aak, Aab, M, W, P, U, Hs, V2, HT, zero;
     int nseg, seg_len;                 // two-level scan: segments per sequence, chunks per segment
+    int lead_real;                     // the first segment in scan order is scanned for real in the first pass
     size_t Tseg, Fseg, Sin;            // per (b, h, segment): transition [K,K], state from zero [K,V], entering state [K,V]
     size_t dOc, dAqk, dAqb, DV2, DE, dgl, dW, dP, dAak, dM, tmp, dAab, dQh, dKh, dAh, dBh;
     size_t total_fwd, total;
@@ -61,14 +62,30 @@ TcPlan make_tc_plan(const HdlaDims& d) {
     p.zero = off; off += 32768;
     // Few (batch, head) pairs leave most SMs idle during the serial scan: cut each sequence into segments that
     // are scanned concurrently (transition + state-from-zero per segment, composed, then the real scan).
-    p.nseg = 1;
-    while (p.nseg < 8 && 2 * p.BH * (p.nseg * 2) <= 148 && p.NT / (p.nseg * 2) >= 4) p.nseg *= 2;
+    // Two plans.  Phased calls (context parallelism) do not know the state entering the first segment, so every
+    // segment needs both twins: nseg * 2 CTAs per (batch, head) in the first pass.  A complete call scans its
+    // first segment for real in the first pass (from the given initial state), needs no twins for the last one,
+    // and so fits more, shorter segments: 2 nseg - 3 CTAs per (batch, head).
+    auto fit = [&](int nseg) {                           // -> no empty segment when NT is not a multiple
+        const int len = (p.NT + nseg - 1) / nseg;
+        return (p.NT + len - 1) / len;
+    };
+    int nseg_phased = 1;
+    while (nseg_phased < 8 && 2 * p.BH * (nseg_phased * 2) <= 148 && p.NT / (nseg_phased * 2) >= 4) nseg_phased *= 2;
+    nseg_phased = fit(nseg_phased);
+    int nseg_all = 1;
+    for (int n = 3; n <= 8; ++n)
+        if (p.BH * (2 * n - 3) <= 148 && p.NT / n >= 4) nseg_all = n;
+    nseg_all = fit(nseg_all);
+    if (nseg_all < 3) nseg_all = 1;
+    p.lead_real = (d.flags & HDLA_PHASE_MASK) == HDLA_PHASE_ALL && nseg_all > 1;
+    p.nseg = (d.flags & HDLA_PHASE_MASK) == HDLA_PHASE_ALL ? nseg_all : nseg_phased;
     p.seg_len = (p.NT + p.nseg - 1) / p.nseg;
-    p.nseg = (p.NT + p.seg_len - 1) / p.seg_len;      // no empty segment when NT is not a multiple
-    const size_t slots = (size_t)p.BH * p.nseg;
-    p.Tseg = off; off += p.nseg > 1 ? slots * K * K * 4 : 0;
-    p.Fseg = off; off += p.nseg > 1 ? slots * K * V * 4 : 0;
-    p.Sin = off; off += p.nseg > 1 ? slots * K * V * 4 : 0;
+    const int nseg_max = nseg_all > nseg_phased ? nseg_all : nseg_phased;     // same offsets for both kinds of call
+    const size_t slots = (size_t)p.BH * nseg_max;
+    p.Tseg = off; off += nseg_max > 1 ? slots * K * K * 4 : 0;
+    p.Fseg = off; off += nseg_max > 1 ? slots * K * V * 4 : 0;
+    p.Sin = off; off += nseg_max > 1 ? slots * K * V * 4 : 0;
     p.total_fwd = off;
     p.dOc = take(16384); p.dAqk = take(8192); p.dAqb = take(16384); p.DV2 = take(32768); p.DE = take(32768);
     p.dgl = take(K * 4); p.dW = take(32768); p.dP = take(32768); p.dAak = take(16384); p.dM = take(32768);
@@ -647,6 +664,12 @@ struct ScanTcP {
     // inputs) and write their result to fin_transition[slot]
     const uint4* zero_tile;
     float* fin_transition;
+    // a launch may cover the segments [seg_off, seg_off + seg_cnt) only (seg_cnt == 0: all of them)
+    int seg_off, seg_cnt;
+    // lead_real: the CTA of the first segment in scan order (0 forward, nseg-1 reverse) runs the real scan from
+    // lead_init (indexed by batch*head, may be null) with stores; its transition twin exits at once
+    int lead_real;
+    const float* lead_init;
 };
 
 __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
@@ -661,8 +684,13 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     __shared__ __align__(8) uint64_t ldA, ldB, barA, barB;
     __shared__ uint32_t tmem_s;
     __shared__ float red[K];
-    const int bh = blockIdx.x / p.nseg, seg = blockIdx.x % p.nseg;
-    const long long slot = blockIdx.x;
+    const int seg_cnt = p.seg_cnt ? p.seg_cnt : p.nseg;
+    const int bh = blockIdx.x / seg_cnt, seg = p.seg_off + blockIdx.x % seg_cnt;
+    const long long slot = (long long)bh * p.nseg + seg;
+    if (p.lead_real && seg == (p.reverse ? p.nseg - 1 : 0)) {
+        if (blockIdx.y == 1) return;         // no transition is needed where the entering state is known
+        p.init = p.lead_init; p.init_by_slot = 0; p.no_store = 0;
+    } else
     if (blockIdx.y == 1) {                   // transition twin of this segment
         p.ADD = p.zero_tile; p.R1 = p.zero_tile; p.L1 = p.zero_tile; p.add_stride = 0; p.r1_stride = 0;
         p.init_identity = 1; p.init = nullptr; p.fin = p.fin_transition; p.fin2 = nullptr;
@@ -1497,10 +1525,11 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
 // fp32 CUDA-core products, one CTA per (batch*head, 32 columns); the chain over segments is serial but short.
 // ------------------------------------------------------------------------------------------
 // With s0_identity the start is the identity and F is ignored (composition of the transitions themselves); `fin`
-// (optional) receives the state after the last segment.
+// (optional) receives the state after the last segment.  With lead_final the first segment in scan order was scanned
+// for real: F of that segment is the state entering the next one, and the chain starts there.
 __global__ void __launch_bounds__(128) compose_segments_kernel(const float* T, const float* F, const float* S0,
                                                                float* Sin, float* fin, int nseg, int reverse,
-                                                               int s0_identity) {
+                                                               int s0_identity, int lead_final) {
     __shared__ float cur[K][33];
     const int bh = blockIdx.x, c0 = blockIdx.y * 32, k = threadIdx.x;
     float x[32];
@@ -1508,7 +1537,12 @@ __global__ void __launch_bounds__(128) compose_segments_kernel(const float* T, c
     for (int c = 0; c < 32; ++c)
         x[c] = s0_identity ? (c0 + c == k ? 1.f : 0.f) : (S0 ? S0[((size_t)bh * K + k) * V + c0 + c] : 0.f);
     const int first = reverse ? nseg - 1 : 0, step = reverse ? -1 : 1;
-    for (int i = 0; i < nseg; ++i) {
+    if (lead_final) {          // F of the first segment in scan order IS the state leaving it (it was scanned for real)
+        const size_t slot = (size_t)bh * nseg + first;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) x[c] = F[(slot * K + k) * V + c0 + c];
+    }
+    for (int i = lead_final ? 1 : 0; i < nseg; ++i) {
         const int sgm = first + i * step;
         const size_t slot = (size_t)bh * nseg + sgm;
 #pragma unroll
@@ -1639,7 +1673,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             scan_tc_kernel<<<dim3(pl.BH * pl.nseg, 2), 256, 196608, st>>>(s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
             compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, nullptr, ht,
-                                                                         pl.nseg, 0, 1);
+                                                                         pl.nseg, 0, 1, 0);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
         }
@@ -1654,7 +1688,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         if (!ht) return fail(HDLA_ERR_INVALID, "state pass needs the output pointer (ht)");
         if (pl.nseg > 1) {                    // affine maps of the segments are in the workspace (TRANSITION phase)
             compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), h0, nullptr, ht,
-                                                                         pl.nseg, 0, 0);
+                                                                         pl.nseg, 0, 0, 0);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
         }
@@ -1663,7 +1697,25 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         return HDLA_OK;
     }
-    if (pl.nseg > 1) {
+    if (pl.nseg > 1 && pl.lead_real) {
+        // two-level scan of a complete call: the first segment is scanned for real from h0 (checkpoints and v2
+        // stored), next to the transition and state-from-zero twins of the segments between it and the last ...
+        ScanTcP s1 = scan_params(nullptr, U4(pl.Hs), U4(pl.V2), F(pl.Fseg), nullptr, 1);
+        s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1; s1.fin_transition = F(pl.Tseg);
+        s1.seg_off = 0; s1.seg_cnt = pl.nseg - 1; s1.lead_real = 1; s1.lead_init = h0;
+        scan_tc_kernel<<<dim3(pl.BH * (pl.nseg - 1), 2), 256, 196608, st>>>(s1);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+        // ... the state entering every later segment follows from the first segment's final state ...
+        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
+                                                                     pl.nseg, 0, 0, 1);
+        HDLA_CHECK_LAUNCH("compose_segments_kernel");
+        // ... and the remaining segments are scanned for real at once
+        ScanTcP s2 = scan_params(F(pl.Sin), U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
+        s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;
+        s2.seg_off = 1; s2.seg_cnt = pl.nseg - 1;
+        scan_tc_kernel<<<pl.BH * (pl.nseg - 1), 256, 196608, st>>>(s2);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+    } else     if (pl.nseg > 1) {
         // two-level scan: per segment, transition and state-from-zero side by side (grid.y = 2) ...
         if (phase == HDLA_PHASE_ALL) {        // (a phased POST call finds them in the workspace)
             ScanTcP s1 = scan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
@@ -1672,7 +1724,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
         }
         // ... composed into the state entering every segment ...
-        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), nullptr, pl.nseg, 0, 0);
+        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), nullptr, pl.nseg, 0, 0, 0);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         // ... and the real scan of all segments at once
         ScanTcP s2 = scan_params(F(pl.Sin), U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
@@ -1737,7 +1789,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
             compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), dht, nullptr, dh0,
-                                                                         pl.nseg, 1, 0);
+                                                                         pl.nseg, 1, 0, 0);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
         }
@@ -1747,7 +1799,23 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         return HDLA_OK;
     }
     // --- dhu: reverse scan (dv2 is accumulated in place over dv2_intra)
-    if (pl.nseg > 1) {
+    if (pl.nseg > 1 && pl.lead_real) {
+        // mirror image of the forward pass of a complete call: the last segment is scanned for real from dht next to
+        // the gradient-from-zero twins of the segments 1 .. nseg-2 (their transitions are in the workspace) ...
+        ScanTcP s1 = rscan_params(nullptr, U4(pl.DE), U4(pl.DV2), F(pl.Fseg), F(pl.dgl), 1);
+        s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1;
+        s1.seg_off = 1; s1.seg_cnt = pl.nseg - 1; s1.lead_real = 1; s1.lead_init = dht;
+        scan_tc_kernel<<<pl.BH * (pl.nseg - 1), 256, 196608, st>>>(s1);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
+                                                                     pl.nseg, 1, 0, 1);
+        HDLA_CHECK_LAUNCH("compose_segments_kernel");
+        ScanTcP s2 = rscan_params(F(pl.Sin), U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
+        s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;
+        s2.seg_off = 0; s2.seg_cnt = pl.nseg - 1;
+        scan_tc_kernel<<<pl.BH * (pl.nseg - 1), 256, 196608, st>>>(s2);
+        HDLA_CHECK_LAUNCH("scan_tc_kernel");
+    } else     if (pl.nseg > 1) {
         // two-level reverse scan; the segment transitions were left in the workspace by the forward pass
         if (phase == HDLA_PHASE_ALL) {        // (a phased POST call finds the per-segment gradients in the workspace)
             ScanTcP s1 = rscan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
@@ -1755,7 +1823,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
         }
-        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), nullptr, pl.nseg, 1, 0);
+        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), nullptr, pl.nseg, 1, 0, 0);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         ScanTcP s2 = rscan_params(F(pl.Sin), U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
         s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;

@@ -35,13 +35,22 @@ def test_cfg1_full_size_slice_against_oracle():
         if not e < 2e-2:
             bad.append(f"{name}: {e:.3e}")
     assert not bad, "; ".join(bad)
-    # independence of the batch cut: the first two sequences alone give bit-identical results
-    lv2 = [x[n][:2].to(dev).requires_grad_(True) for n in NAMES]
+    # independence of the batch cut: the first five sequences alone (80 (batch, head) pairs: still the one-level scan)
+    # give bit-identical results
+    lv2 = [x[n][:5].to(dev).requires_grad_(True) for n in NAMES]
     o2, _ = H.chunk_hrdplr_delta_rule(*lv2, R, chunk_size=64)
-    g2 = torch.autograd.grad(o2, lv2, x["do"][:2].to(dev))
-    assert torch.equal(o2, o[:2])
+    g2 = torch.autograd.grad(o2, lv2, x["do"][:5].to(dev))
+    assert torch.equal(o2, o[:5])
     for a_, b_ in zip(g2, grads):
-        assert torch.equal(a_, b_[:2])
+        assert torch.equal(a_, b_[:5])
+    # the first two alone run the two-level scan (states composed from per-segment maps in fp32): same results to
+    # well within the bf16 tolerance, not bit for bit
+    lv3 = [x[n][:2].to(dev).requires_grad_(True) for n in NAMES]
+    o3, _ = H.chunk_hrdplr_delta_rule(*lv3, R, chunk_size=64)
+    g3 = torch.autograd.grad(o3, lv3, x["do"][:2].to(dev))
+    assert orc.rel_err(o3, o[:2]) < 5e-3
+    for a_, b_ in zip(g3, grads):
+        assert orc.rel_err(a_, b_[:2]) < 5e-3
 
 
 def test_cfg2_full_size_decode_against_oracle():
