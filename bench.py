@@ -1,27 +1,33 @@
 #!/usr/bin/env python
 """Benchmark of the chunked HDLA operator, forward + backward.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg1|cfg0|cfg3]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg1|...]
 
-One step = one forward + backward of the operator over one synthetic batch.  At N = 1 the
-workload is B8 T4096 H16 K=V=128, bf16 inputs, fp32 accumulation/state, chunk 64 ("cfg1").  At
-N > 1 (launched with torch.distributed.run, one rank per GPU) every rank processes its own cfg1
-batch -- the (batch, head) pairs are independent, so the job shards with no collective on the
-data path (weak scaling); ``--scaling strong`` shards the single cfg1 batch over the ranks instead.
+One step = one forward + backward of the operator over one synthetic batch.  The workload is
+B8 T4096 H16 K=V=128, bf16 inputs, fp32 accumulation/state, chunk 64 ("cfg1").  At N > 1 (launched
+with torch.distributed.run, one rank per GPU) that ONE batch is sharded over the ranks by
+(batch, head) pairs -- they are independent, so there is no collective on the data path -- and the
+line reports ``"scaling": "strong"``; ``--scaling weak`` gives every rank its own cfg1 batch instead
+(also reported under ``secondary.weak``).
 
 The printed JSON line carries
   value / ms_per_step : tokens/s with the inputs resident in HBM, CUDA-event timed, max over ranks
-  e2e                 : the same through the public entry point with pinned HOST buffers, the
-                        host->device copies of all inputs and device->host copies of o and all
+  e2e                 : the same through the package's host-tensor entry point with pinned HOST buffers,
+                        the host->device copies of all inputs and device->host copies of o and all
                         gradients inside the timed region
-  roofline            : algorithmic FLOPs of one step / measured step time against the measured
-                        bf16 tensor peak (MEASURED_PEAKS.json), with the HBM view beside it
-  cpu_baseline        : the CPU oracle (a port of the reference algorithm) timed on this host
+  roofline            : whole-step fractions -- the minimal HBM traffic of one step (8704 B per token
+                        and head) / step time against the measured copy bandwidth, the algorithmic FLOPs
+                        against the measured bf16 peak -- and, under ``kernels``, every kernel's own
+                        CUDA-event time with the bytes the PIPELINE moves through it
+  cpu_baseline        : the reference's own CPU implementation (HRDPLR/naive.py, installed under
+                        oracle/_ref by oracle/install_ref.py; else the oracle port) on a bounded sample
+  secondary           : decode (cfg2) and the fp32 CPU configuration (cfg0) on the GPU; at N > 1 the
+                        weak-scaling number, the long-context configuration (cfg3) with context
+                        parallelism, and ``cp_check``, the parity of the context-parallel path against
+                        the single-GPU operator on the same inputs
   clocks              : SM clocks and throttle reasons sampled with nvidia-smi during the timed region
 
-``--impl reference`` times the reference algorithm's CPU implementation (the oracle port of
-HRDPLR/naive.py plus explicit backward; the reference itself ships Triton-only kernels and a
-torch "naive" path, and its checkout is not available on the GPU host) on all host threads.
+``--impl reference`` times that CPU implementation alone (rank 0; the other ranks exit).
 """
 from __future__ import annotations
 
@@ -54,6 +60,7 @@ WORKLOADS = {
 }
 DECODE_METRIC = "HDLA fused-recurrent decode tokens/s (B256 H32 D128 bf16, fp32 state)"
 R = 2
+NAMES = ("q", "k", "v", "a", "b", "gk")
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -77,16 +84,18 @@ def bytes_per_token_head(C: int, D: int, elt: int) -> float:
     return (8 * D + D) * elt + (9 * D + 8 * D) * elt + 4 * (D * D * 2 / C)
 
 
-# Algorithmic HBM bytes per (chunk, head) of each kernel of the bf16 pipeline: every operand tile it
-# needs read once, every result written once (KiB; bf16 tiles and un-gating factors, fp32 E; K = V = 128, chunk 64, R = 2).
+# Bytes the PIPELINE moves through each kernel per (chunk, head): every operand tile the kernel reads, read once,
+# every result it writes, written once -- inter-kernel intermediates included, which is why their sum is a multiple
+# of the algorithmic minimum above (KiB; bf16 tiles and un-gating factors, fp32 E; K = V = 128, chunk 64, R = 2).
 # scan_tc_kernel is launched twice per step (forward 192.5, reverse 225).
 KERNEL_KIB = {
+    "chunk_prep_tc_kernel": 424.5,
     "prep_hat_kernel": 256.5, "gram_tc_kernel": 168.0, "inverse_tc_kernel": 64.0, "wu_tc_kernel": 192.0,
     "scan_tc_kernel": (192.5 + 225.0) / 2, "out_tc_kernel": 136.0, "dau_tc_kernel": 152.0,
     "wy_bwd_tc_kernel": 288.0, "grad_tc_kernel": 560.5,
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch (GB) at cfg 1: one ncu capture at B=2 (a quarter of
-# cfg 1; traffic is proportional to the number of chunks), scaled by 4 -- see profiles/chunk_tc_pipeline_traffic.md
+# cfg 1; traffic is proportional to the number of chunks), scaled by 4 -- see profiles/
 KERNEL_NCU_TRAFFIC_GB = {
     "prep_hat_kernel": 2.09, "gram_tc_kernel": 1.20, "inverse_tc_kernel": 0.33, "wu_tc_kernel": 1.39,
     "scan_tc_kernel": (1.51 + 1.79) / 2, "out_tc_kernel": 1.08, "dau_tc_kernel": 1.06, "wy_bwd_tc_kernel": 2.25,
@@ -152,56 +161,112 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-# ------------------------------------------------------------------------------ CPU oracle timing
-def time_cpu_port(T_sample: int, H: int, K: int, V: int, C: int, repeats: int = 1):
-    """Forward + explicit backward of the oracle port in fp32 on all host threads; tokens/s."""
-    from oracle import hdla_oracle as orc
+# ------------------------------------------------------------------------------ CPU reference timing
+def cpu_reference_pass(H: int, K: int, V: int, C: int, T_sample: int, B_sample: int = 1, repeats: int = 1):
+    """One sample definition for every CPU number this file prints: forward + backward in fp32 on all host
+    threads over B_sample x T_sample tokens of the workload's head shape.  The reference's own naive.py
+    (autograd backward, as its test_integrated.py does) when it is installed under oracle/_ref, else the oracle
+    port (explicit backward).  Returns (tokens/s, seconds of the best pass, kind)."""
     from hdla_impl_b200.synthetic import make_inputs
     torch.set_num_threads(os.cpu_count() or 1)
-    x = make_inputs(1, T_sample, H, K, V, R, seed=0)
-    best = None
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        st = orc.staged_forward(x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], R, K ** -0.5, None, C,
-                                dtype=torch.float32)
-        orc.staged_backward(st, x["do"], None)
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return T_sample / best, best
+    x = make_inputs(B_sample, T_sample, H, K, V, R, seed=0)
+    from oracle import ref_naive
+    if ref_naive.available():
+        sec = ref_naive.time_fwd_bwd(x, R, C, repeats=repeats)
+        kind = "reference"
+    else:
+        from oracle import hdla_oracle as orc
+        sec = None
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            st = orc.staged_forward(x["q"], x["k"], x["v"], x["a"], x["b"], x["gk"], R, K ** -0.5, None, C,
+                                    dtype=torch.float32)
+            orc.staged_backward(st, x["do"], None)
+            dt = time.perf_counter() - t0
+            sec = dt if sec is None else min(sec, dt)
+        kind = "port"
+    return B_sample * T_sample / sec, sec, kind
+
+
+def cpu_baseline_block(workload: str):
+    """cpu_baseline of the JSON line: a bounded sample of the benchmark's own workload, best of 3, plus the
+    CPU configuration (cfg0, B2 T256 H4 K=V=64) in full."""
+    B, T, H, K, V, C, dt = WORKLOADS[workload]
+    T_s = min(T, 512)
+    val, sec, kind = cpu_reference_pass(H, K, V, C, T_s, 1, repeats=3)
+    B0, T0, H0, K0, V0, C0, _ = WORKLOADS["cfg0"]
+    val0, sec0, _ = cpu_reference_pass(H0, K0, V0, C0, T0, B0, repeats=3)
+    what = "HRDPLR/naive.py (reference, autograd backward)" if kind == "reference" else "oracle port of HRDPLR/naive.py"
+    return {"value": val, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": kind,
+            "sample": f"{what}: B=1 T={T_s} of {workload} (H={H} K={K} V={V} chunk {C}) fp32 fwd+bwd, "
+                      f"best of 3 passes, {sec:.2f} s per pass",
+            "cfg0": {"value": val0, "unit": "tokens/s", "seconds_per_pass": sec0,
+                     "sample": f"B={B0} T={T0} H={H0} K=V={K0} fp32 chunk {C0}, whole configuration, best of 3"}}
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    B, T, H, K, V, C, dt = WORKLOADS[args.workload]
+    wl = "cfg1" if args.workload == "cfg2" else args.workload
+    B, T, H, K, V, C, dt = WORKLOADS[wl]
     T_s = min(T, 256)
-    times = []
+    times, kind = [], "port"
     for i in range(args.warmup + args.steps):
-        _, sec = time_cpu_port(T_s, H, K, V, C)
+        _, sec, kind = cpu_reference_pass(H, K, V, C, T_s, 1, repeats=1)
         if i >= args.warmup:
             times.append(sec)
     total = sum(times)
     val = T_s * args.steps / total
     cores = os.cpu_count() or 1
-    sample = f"B=1 T={T_s} of {args.workload} (H={H} K={K} V={V} chunk {C}), fp32, per step"
+    what = "HRDPLR/naive.py (reference, autograd backward)" if kind == "reference" else "oracle port of HRDPLR/naive.py"
+    sample = f"{what}: B=1 T={T_s} of {wl} (H={H} K={K} V={V} chunk {C}) fp32 fwd+bwd per step"
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "B": B, "T": T, "H": H, "K": K, "V": V, "chunk": C, "sample": sample},
-        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl, "B": B, "T": T, "H": H, "K": K, "V": V, "chunk": C, "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
-# ------------------------------------------------------------------------------ our arm
+# ------------------------------------------------------------------------------ helpers of our arm
+def timed_steps(step, steps, barrier):
+    """K steps bracketed by barrier + synchronize on both sides; CUDA-event milliseconds of this rank."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier()
+    return e0.elapsed_time(e1)
+
+
+def kernel_table(ktimes, passes, G):
+    """Per-kernel CUDA-event times of `passes` steps -> table with the pipeline bytes each kernel moves."""
+    tot = sum(v[1] for v in ktimes.values())
+    table = {}
+    for name, (cnt, tms) in sorted(ktimes.items(), key=lambda kv: -kv[1][1]):
+        avg = tms / cnt
+        kib = KERNEL_KIB.get(name)
+        table[name] = {"launches_per_step": cnt / passes, "avg_ms": avg, "ms_per_step": tms / passes,
+                       "share": tms / tot if tot else None,
+                       "pipeline_KiB_per_chunk_head": kib,
+                       "pipeline_GBps": (kib * 1024 * G / (avg / 1e3) / 1e9) if kib else None,
+                       "ncu_dram_GB_per_launch_cfg1": KERNEL_NCU_TRAFFIC_GB.get(name)}
+    return table
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     import hdla_impl_b200 as HD
     from hdla_impl_b200 import _lib
-    from hdla_impl_b200.sharding import shard_batch_heads
+    from hdla_impl_b200.context_parallel import cp_chunk_hrdplr_delta_rule
+    from hdla_impl_b200.host import chunk_fwd_bwd_from_host, join_host_streams, numa_local_to
+    from hdla_impl_b200.sharding import shard_batch_heads, shard_time
     from hdla_impl_b200.synthetic import make_inputs
 
     if not torch.cuda.is_available():
@@ -213,117 +278,100 @@ def run_ours(args, rank, world, local_rank):
     B, T, H, K, V, C, dt = WORKLOADS[args.workload]
     dtype = torch.bfloat16 if dt == "bf16" else torch.float32
     elt = 2 if dt == "bf16" else 4
-
-    # this rank's units
-    cp = args.workload == "cfg3" and world > 1           # long context: shard T, exchange boundary states
-    if args.workload == "cfg4":
-        args.scaling = "strong"                          # one B32 batch, sharded by batch over the ranks
-    if cp:
-        args.scaling = "strong"
-    Tl = T // world if cp else T
-    if cp:
-        Bl, Hl = B, H
-    elif args.scaling == "strong" and world > 1:
-        b_lo, b_hi, h_lo, h_hi = shard_batch_heads(B, H, rank, world)
-        Bl, Hl = b_hi - b_lo, h_hi - h_lo
-    else:
-        Bl, Hl = B, H
-    x = make_inputs(Bl, Tl, Hl, K, V, R, seed=rank, dtype=dtype)
-    names = ("q", "k", "v", "a", "b", "gk")
-    from hdla_impl_b200.host import numa_local_to
-    with numa_local_to(dev):                             # pinned buffers on the GPU's own NUMA node
-        host = {n: x[n].pin_memory() for n in names + ("do",)}
-    dev_in = {n: host[n].to(dev) for n in host}
-    leaves = [dev_in[n].requires_grad_(True) for n in names]
     scale = K ** -0.5
-
-    from hdla_impl_b200.context_parallel import cp_chunk_hrdplr_delta_rule
-
-    def step(lv, do):
-        if cp:
-            o, _ = cp_chunk_hrdplr_delta_rule(*lv, R, scale=scale, chunk_size=C)
-        else:
-            o, _ = HD.chunk_hrdplr_delta_rule(*lv, R, scale=scale, chunk_size=C)
-        grads = torch.autograd.grad(o, lv, do)
-        return o, grads
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    def op_step(lv, do, use_cp=False):
+        if use_cp:
+            o, _ = cp_chunk_hrdplr_delta_rule(*lv, R, scale=scale, chunk_size=C)
+        else:
+            o, _ = HD.chunk_hrdplr_delta_rule(*lv, R, scale=scale, chunk_size=C)
+        return o, torch.autograd.grad(o, lv, do)
+
+    # ---- this rank's units
+    cp = args.workload == "cfg3" and world > 1           # long context: shard T, exchange boundary states
+    scaling = args.scaling
+    if cp or args.workload == "cfg4":
+        scaling = "strong"
+    if cp:
+        Bl, Hl, Tl = B, H, T // world
+    elif scaling == "strong" and world > 1:
+        b_lo, b_hi, h_lo, h_hi = shard_batch_heads(B, H, rank, world)
+        Bl, Hl, Tl = b_hi - b_lo, h_hi - h_lo, T
+    else:
+        Bl, Hl, Tl = B, H, T
+    x = make_inputs(Bl, Tl, Hl, K, V, R, seed=rank, dtype=dtype)
+    with numa_local_to(dev) as numa:                     # pinned buffers on the GPU's own NUMA node
+        host = {n: x[n].pin_memory() for n in NAMES + ("do",)}
+    dev_in = {n: host[n].to(dev) for n in host}
+    leaves = [dev_in[n].requires_grad_(True) for n in NAMES]
+    step = lambda: op_step(leaves, dev_in["do"], cp)
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    for _ in range(max(args.warmup, 3)):
-        step(leaves, dev_in["do"])
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        step()
     barrier()
     l0 = _lib.kernel_launches()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step(leaves, dev_in["do"])
-    e1.record()
-    barrier()
+    ms = timed_steps(step, args.steps, barrier)
     launches = _lib.kernel_launches() - l0
-    ms = e0.elapsed_time(e1)
     # per-kernel durations, live: the library brackets every launch with CUDA events on its stream
-    ktimes = {}
-    if rank == 0 or cp:                                  # with context parallelism every step is collective
-        if rank == 0:
-            _lib.timing_enable(True)
-        for _ in range(3):
-            step(leaves, dev_in["do"])
-        torch.cuda.synchronize(dev)
-        if rank == 0:
-            _lib.timing_enable(False)
-            ktimes = _lib.timing_report()
-    if rank == 0 and not cp:
-        # the timed region can be shorter than nvidia-smi's sampling period: keep the same load running
-        # (untimed) until a few samples exist, so the clocks reported are clocks under this load
-        t_end = time.time() + 5.0
-        while len(sampler.rows) < 5 and time.time() < t_end:
-            step(leaves, dev_in["do"])
+    ktimes, kpasses = {}, 3
+    if rank == 0:
+        _lib.timing_enable(True)
+    for _ in range(kpasses):                             # (with context parallelism every step is collective)
+        step()
+    torch.cuda.synchronize(dev)
+    if rank == 0:
+        _lib.timing_enable(False)
+        ktimes = _lib.timing_report()
+    # the timed region can be shorter than nvidia-smi's sampling period: keep the same load running (untimed)
+    # until a few samples exist, so the clocks reported are clocks under this load
+    for _ in range(60 if world > 1 else 400):
+        if world == 1 and len(sampler.rows) >= 5:
+            break
+        step()
+        if world == 1:
             torch.cuda.synchronize(dev)
-    elif cp:
-        for _ in range(20):                              # same number of collective steps on every rank
-            step(leaves, dev_in["do"])
-        torch.cuda.synchronize(dev)
+    torch.cuda.synchronize(dev)
     clocks = sampler.stop() if rank == 0 else None
 
-    # end to end: pinned host buffers in, host buffers out, through the package's host-tensor entry point
-    # (slices of the batch pipelined over copy-in / compute / copy-out streams)
-    from hdla_impl_b200.host import chunk_fwd_bwd_from_host
+    # ---- end to end: pinned host buffers in, host buffers out, through the package's host-tensor entry point
+    # (slices of the batch pipelined over copy-in / compute / copy-out streams; successive steps only enqueue, so
+    # the copy-in of step s+1 runs under the copy-out of step s; the clock stops after the last copy-out)
     out_host = {}
-    e2e_steps = args.steps
 
     def e2e_step():
         if cp:                                           # sequence-sharded: one slice, collective step
-            lv = [host[n].to(dev, non_blocking=True).requires_grad_(True) for n in names]
+            lv = [host[n].to(dev, non_blocking=True).requires_grad_(True) for n in NAMES]
             do = host["do"].to(dev, non_blocking=True)
-            o, grads = step(lv, do)
-            outs = (o,) + tuple(grads)
-            for i, t in enumerate(outs):
+            o, grads = op_step(lv, do, True)
+            for i, t in enumerate((o,) + tuple(grads)):
                 if i not in out_host:
                     out_host[i] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
                 out_host[i].copy_(t, non_blocking=True)
         else:
-            # enqueue only: successive steps stream through the copy engines (the copy-in of step s+1 runs under
-            # the copy-out of step s); the clock stops after the last copy-out has completed
             chunk_fwd_bwd_from_host(host, out_host, R, dev, scale=scale, chunk_size=C, slice_batch=1, sync=False)
 
-    with numa_local_to(dev) as numa:
+    with numa_local_to(dev):
         e2e_step()
-        barrier()
+        torch.cuda.synchronize(dev)
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
         f0.record()
-        for _ in range(e2e_steps):
+        for _ in range(args.steps):
             e2e_step()
+        if not cp:
+            join_host_streams(dev)
         f1.record()
         barrier()
         ms_e2e = f0.elapsed_time(f1)
-    numa_node = numa.node
     h2d = sum(host[n].numel() * host[n].element_size() for n in host)
     d2h = sum(t.numel() * t.element_size() for t in out_host.values())
 
@@ -331,10 +379,25 @@ def run_ours(args, rank, world, local_rank):
         tt = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms, ms_e2e = tt.tolist()
-    tokens_step = B * T * (world if args.scaling == "weak" else 1)
+    tokens_step = B * T * (world if scaling == "weak" else 1)
     ms_step = ms / args.steps
     value = tokens_step / (ms_step / 1e3)
-    e2e_val = tokens_step / (ms_e2e / e2e_steps / 1e3)
+    e2e_val = tokens_step / (ms_e2e / args.steps / 1e3)
+
+    # ---- secondary measurements (all ranks take part in the collective ones)
+    secondary = {}
+    if not args.no_secondary and args.workload == "cfg1":
+        del leaves, dev_in, host, out_host, x
+        torch.cuda.empty_cache()
+        if world > 1:
+            secondary["cp_check"] = cp_parity_check(dev, rank, world)
+            secondary["cfg3"] = bench_cfg3(dev, rank, world, barrier)
+            if scaling == "strong":
+                secondary["weak"] = bench_weak(dev, rank, world, barrier)
+        else:
+            secondary["cfg3"] = bench_cfg3(dev, rank, world, barrier)
+            secondary["cfg2_decode"] = bench_decode_small(dev)
+            secondary["cfg0_fp32_gpu"] = bench_cfg0_gpu(dev)
 
     if rank == 0:
         peaks, how = load_peaks()
@@ -345,61 +408,242 @@ def run_ours(args, rank, world, local_rank):
         tf = flops / sec / 1e12
         gbs = byts / sec / 1e9
         peak_tf = peaks.get("bf16_tflops_sustained") or peaks.get("bf16_tflops")
+        G = Bl * Hl * ((Tl + C - 1) // C)
+        table = kernel_table(ktimes, kpasses, G) if (ktimes and dt == "bf16") else {}
+        pipeline_kib = sum(v["pipeline_KiB_per_chunk_head"] * v["launches_per_step"] for v in table.values()
+                           if v["pipeline_KiB_per_chunk_head"])
+        alg_kib = bytes_per_token_head(C, K, elt) * C / 1024.0
         roof = {
-            "bound": "tensor", "kernel": "chunked fwd+bwd pipeline (all launches of one step)",
-            "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf, "traffic": None,
-            "peak_source": f"{how} (bf16 sustained)", "flops_per_launch": flops,
-            "hbm": {"achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
-                    "algorithmic_bytes": byts},
+            "bound": "hbm", "kernel": "all launches of one fwd+bwd step",
+            "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+            "traffic": None,
+            "peak_source": f"{how} (copy)",
+            "algorithmic_bytes_per_step": byts,
+            "algorithmic_KiB_per_chunk_head": alg_kib,
+            "pipeline_KiB_per_chunk_head": pipeline_kib or None,
+            "traffic_over_algorithmic": (pipeline_kib / alg_kib) if pipeline_kib else None,
+            "tensor": {"achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf,
+                       "flops_per_step": flops, "peak_source": f"{how} (bf16 sustained)",
+                       "frac_of_burst_peak": tf / peaks["bf16_tflops"] if peaks.get("bf16_tflops") else None},
+            "kernels_note": "per-kernel CUDA-event times of rank 0 with PIPELINE bytes (they include the "
+                            "inter-kernel intermediates); event bracketing removes launch overlap, so their "
+                            "sum can exceed ms_per_step slightly",
+            "kernels": table,
         }
-        if ktimes and dt == "bf16":
-            G = (B if (args.scaling == "weak" or cp) else B // world) * H * ((Tl + C - 1) // C)
-            tot = sum(v[1] for v in ktimes.values())
-            table = {}
-            for name, (cnt, tms) in sorted(ktimes.items(), key=lambda kv: -kv[1][1]):
-                avg = tms / cnt
-                kib = KERNEL_KIB.get(name)
-                table[name] = {"launches_per_step": cnt // 3, "avg_ms": avg, "share": tms / tot,
-                               "algorithmic_GBps": (kib * 1024 * G / (avg / 1e3) / 1e9) if kib else None}
-            top = next(iter(table))
-            if KERNEL_KIB.get(top):
-                a = table[top]["algorithmic_GBps"]
-                roof = {
-                    "bound": "hbm", "kernel": top, "achieved": a, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": a / peaks["hbm_gbs"], "traffic": KERNEL_NCU_TRAFFIC_GB.get(top),
-                    "peak_source": f"{how} (copy)", "avg_launch_ms": table[top]["avg_ms"],
-                    "algorithmic_bytes_per_launch": KERNEL_KIB[top] * 1024 * G,
-                    "step": {"tensor": {"achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf,
-                                        "flops_per_step": flops},
-                             "hbm": {"achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                     "frac": gbs / peaks["hbm_gbs"], "algorithmic_bytes_per_step": byts}},
-                    "kernels": table,
-                }
+        ncu_total = sum((v["ncu_dram_GB_per_launch_cfg1"] or 0) * v["launches_per_step"] for v in table.values())
+        if ncu_total and args.workload == "cfg1" and (world == 1 or scaling == "weak"):
+            roof["traffic"] = ncu_total                   # GB per step, summed over the kernels' ncu captures
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
-            T_s = min(T, 1024)
-            val, sec_cpu = time_cpu_port(T_s, H, K, V, C)
-            cpu = {"value": val, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
-                   "sample": f"B=1 T={T_s} of {args.workload} (H={H} K={K} V={V} chunk {C}) fp32, one pass, "
-                             f"{sec_cpu:.1f} s"}
+            cpu = cpu_baseline_block(args.workload)
         line = {
             "metric": METRIC if args.workload == "cfg1" else
             f"HDLA fwd+bwd tokens/s (B{B} T{T} H{H} D{K} {dt})", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling,
-            "vs_baseline": None, "dtype": dt, "data": "synthetic",
-            "config": {"workload": args.workload, "B_per_step": B * (world if args.scaling == "weak" else 1), "T": T,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": scaling, "vs_baseline": None, "dtype": dt, "data": "synthetic",
+            "config": {"workload": args.workload, "B_per_step": B * (world if scaling == "weak" else 1), "T": T,
                        "H": H, "K": K, "V": V, "R": R, "chunk": C,
+                       "per_rank": {"B": Bl, "H": Hl, "T": Tl},
                        "sharding": ("context parallel: T/N per rank, all-gather of affine state maps (NCCL)" if cp
                                     else "batch x head, no collective"),
                        "backward": "saved forward intermediates" if HD.hrdplr.save_workspace_default() else "recompute",
-                       "l2": "inputs (>1 GB per step) are larger than the 126 MB L2"},
+                       "l2": "inputs (>1 GB per step) are larger than the 126 MB L2" if world == 1 or scaling == "weak"
+                             else "each step rewrites a workspace larger than the 126 MB L2 between reuses of any input"},
             "e2e": {"value": e2e_val, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "host_numa_node": numa_node},
+                    "host_numa_node": numa.node},
             "gpu_launches": int(launches), "roofline": roof, "cpu_baseline": cpu, "clocks": clocks,
+            "secondary": secondary or None,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def cp_parity_check(dev, rank, world):
+    """The context-parallel operator (T = 4096 * world cut over the ranks, B1 H2, initial state and a loss on
+    every rank's final state) against the single-GPU operator on the same inputs, forward and every gradient;
+    max relative error over all tensors and ranks."""
+    import torch.distributed as dist
+    import hdla_impl_b200 as HD
+    from hdla_impl_b200.context_parallel import cp_chunk_hrdplr_delta_rule
+    from hdla_impl_b200.sharding import shard_time
+    from hdla_impl_b200.synthetic import make_inputs
+    C, K = 64, 128
+    T = 4096 * world
+    x = make_inputs(1, T, 2, K, K, R, seed=1234, dtype=torch.bfloat16, h0_std=0.1, with_dht=True)
+    rr = lambda n: R if n in ("a", "b") else 1
+    lo, hi = shard_time(T, rank, world, C)
+    lv = [x[n][:, lo * rr(n):hi * rr(n)].to(dev).requires_grad_(True) for n in NAMES]
+    h0 = x["h0"].to(dev).requires_grad_(True)
+    o, ht = cp_chunk_hrdplr_delta_rule(*lv, R, initial_state=h0, output_final_state=True, chunk_size=C)
+    dht = x["dht"].to(dev)
+    loss = (o.float() * x["do"][:, lo:hi].to(dev).float()).sum() + (ht * dht * (0.5 + rank)).sum()
+    grads = torch.autograd.grad(loss, lv + [h0], allow_unused=True)
+    # truth: the same slices chained on this rank's GPU alone
+    full = [x[n].to(dev).requires_grad_(True) for n in NAMES]
+    h0f = x["h0"].to(dev).requires_grad_(True)
+    state, lf, parts, ht_true = h0f, 0.0, [], None
+    for r_ in range(world):
+        l_, h_ = shard_time(T, r_, world, C)
+        part = [t[:, l_ * rr(n):h_ * rr(n)] for t, n in zip(full, NAMES)]
+        o_r, state = HD.chunk_hrdplr_delta_rule(*part, R, initial_state=state, output_final_state=True, chunk_size=C)
+        lf = lf + (o_r.float() * x["do"][:, l_:h_].to(dev).float()).sum() + (state * dht * (0.5 + r_)).sum()
+        parts.append(o_r)
+        if r_ == rank:
+            ht_true = state
+    gf = torch.autograd.grad(lf, full + [h0f])
+    of = torch.cat(parts, 1)
+
+    def rel(a, b):
+        return float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
+    errs = [rel(o, of[:, lo:hi]), rel(ht, ht_true)]
+    for g, gg, n in zip(grads[:6], gf[:6], NAMES):
+        errs.append(rel(g, gg[:, lo * rr(n):hi * rr(n)]))
+    if rank == 0:
+        errs.append(rel(grads[6], gf[6]))
+    e = torch.tensor([max(errs)], device=dev, dtype=torch.float64)
+    dist.all_reduce(e, op=dist.ReduceOp.MAX)
+    HD.check_status(dev, wait=True)
+    err = float(e.item())
+    assert err < 2e-2, f"context-parallel parity check failed: max relative error {err}"
+    return {"max_rel_err": err, "world": world, "T": T, "tolerance": 2e-2,
+            "what": "cp_chunk_hrdplr_delta_rule vs the single-GPU operator: o, final states, dq dk dv da db dgk, dh0"}
+
+
+def bench_cfg3(dev, rank, world, barrier, steps=5):
+    """Long context (B1 T65536 H16): one GPU, or T cut over the ranks with context parallelism."""
+    import torch.distributed as dist
+    import hdla_impl_b200 as HD
+    from hdla_impl_b200.context_parallel import cp_chunk_hrdplr_delta_rule
+    from hdla_impl_b200.synthetic import make_inputs
+    B, T, H, K, V, C, _ = WORKLOADS["cfg3"]
+    Tl = T // world
+    x = make_inputs(B, Tl, H, K, V, R, seed=100 + rank, dtype=torch.bfloat16)
+    lv = [x[n].to(dev).requires_grad_(True) for n in NAMES]
+    do = x["do"].to(dev)
+    del x
+
+    def step():
+        if world > 1:
+            o, _ = cp_chunk_hrdplr_delta_rule(*lv, R, chunk_size=C)
+        else:
+            o, _ = HD.chunk_hrdplr_delta_rule(*lv, R, chunk_size=C)
+        torch.autograd.grad(o, lv, do)
+    for _ in range(3):
+        step()
+    ms = timed_steps(step, steps, barrier)
+    coll_ms = None
+    if world > 1:
+        # the collective alone, same sizes: forward packs [3,B,H,K,V], backward [2,B,H,K,V] fp32 per rank
+        f32 = dict(dtype=torch.float32, device=dev)
+        p3, p2 = torch.empty(3, B, H, K, V, **f32), torch.empty(2, B, H, K, V, **f32)
+        g3, g2 = torch.empty(world, 3, B, H, K, V, **f32), torch.empty(world, 2, B, H, K, V, **f32)
+
+        def coll():
+            dist.all_gather_into_tensor(g3, p3)
+            dist.all_gather_into_tensor(g2, p2)
+        for _ in range(3):
+            coll()
+        coll_ms = timed_steps(coll, steps, barrier) / steps
+        tt = torch.tensor([ms, coll_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, coll_ms = tt.tolist()
+    ms_step = ms / steps
+    HD.check_status(dev, wait=True)
+    return {"workload": "cfg3: B1 T65536 H16 K=V=128 bf16 chunk 64, fwd+bwd", "n_gpus": world,
+            "ms_per_step": ms_step, "value": B * T / (ms_step / 1e3), "unit": "tokens/s", "steps": steps,
+            "collective": "all_gather (one per direction)" if world > 1 else None,
+            "collective_bytes_per_rank_per_step": (5 * B * H * K * V * 4) if world > 1 else 0,
+            "collective_ms_per_step": coll_ms}
+
+
+def bench_weak(dev, rank, world, barrier, steps=5):
+    """Every rank its own cfg1 batch: no sharding, no communication (the ceiling strong scaling is compared with)."""
+    import torch.distributed as dist
+    import hdla_impl_b200 as HD
+    from hdla_impl_b200.synthetic import make_inputs
+    B, T, H, K, V, C, _ = WORKLOADS["cfg1"]
+    x = make_inputs(B, T, H, K, V, R, seed=200 + rank, dtype=torch.bfloat16)
+    lv = [x[n].to(dev).requires_grad_(True) for n in NAMES]
+    do = x["do"].to(dev)
+    del x
+
+    def step():
+        o, _ = HD.chunk_hrdplr_delta_rule(*lv, R, chunk_size=C)
+        torch.autograd.grad(o, lv, do)
+    for _ in range(3):
+        step()
+    ms = timed_steps(step, steps, barrier)
+    tt = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    ms_step = tt.item() / steps
+    return {"scaling": "weak", "ms_per_step": ms_step, "value": B * T * world / (ms_step / 1e3), "unit": "tokens/s",
+            "B_per_step": B * world, "steps": steps}
+
+
+def bench_decode_small(dev, steps=128):
+    """cfg2 on this GPU: 128 decode steps of B256 H32, state updated in place; tokens/s and HBM fraction."""
+    import hdla_impl_b200 as HD
+    from hdla_impl_b200.synthetic import make_inputs
+    B, _, H, K, V, _, _ = WORKLOADS["cfg2"]
+    ntok = 8
+    x = make_inputs(B, ntok, H, K, V, R, seed=7, dtype=torch.bfloat16, h0_std=0.02)
+    dv = {n: x[n].to(dev) for n in NAMES}
+    S = x["h0"].to(dev)
+    scale = K ** -0.5
+    tok = lambda t, n, r=1: dv[n][:, (t % ntok) * r:(t % ntok + 1) * r]
+
+    def step(t):
+        nonlocal S
+        _, S = HD.fused_recurrent_dplr_delta_rule_fwd(tok(t, "q"), tok(t, "k"), tok(t, "v"), tok(t, "a", R),
+                                                      tok(t, "b", R), tok(t, "gk"), R, scale, S, True,
+                                                      inplace_state=True)
+    for t in range(5):
+        step(t)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for t in range(steps):
+        step(t)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    sec = e0.elapsed_time(e1) / steps / 1e3
+    peaks, how = load_peaks()
+    byts = 2.0 * B * H * K * V * 4 + B * H * (7 * K + 2 * V) * 2
+    gbs = byts / sec / 1e9
+    del S, dv
+    torch.cuda.empty_cache()
+    return {"workload": "cfg2: B256 H32 K=V=128 decode, one token per step, fp32 state in place", "steps": steps,
+            "us_per_step": sec * 1e6, "value": B / sec, "unit": "tokens/s",
+            "roofline": {"bound": "hbm", "kernel": "recurrent_bulk_kernel", "achieved": gbs, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"], "algorithmic_bytes_per_step": byts,
+                         "peak_source": f"{how} (copy)", "l2": "state (537 MB) is larger than the 126 MB L2"}}
+
+
+def bench_cfg0_gpu(dev, steps=20):
+    """The CPU configuration (B2 T256 H4 K=V=64 fp32) on the GPU: fp32 CUDA-core pipeline, fwd+bwd."""
+    import hdla_impl_b200 as HD
+    from hdla_impl_b200.synthetic import make_inputs
+    B, T, H, K, V, C, _ = WORKLOADS["cfg0"]
+    x = make_inputs(B, T, H, K, V, R, seed=0)
+    lv = [x[n].to(dev).requires_grad_(True) for n in NAMES]
+    do = x["do"].to(dev)
+
+    def step():
+        o, _ = HD.chunk_hrdplr_delta_rule(*lv, R, chunk_size=C)
+        torch.autograd.grad(o, lv, do)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / steps
+    return {"workload": "cfg0: B2 T256 H4 K=V=64 fp32 chunk 64, fwd+bwd (fp32 CUDA-core pipeline; launch bound)",
+            "ms_per_step": ms, "value": B * T / (ms / 1e3), "unit": "tokens/s", "steps": steps}
 
 
 def run_decode(args, rank, world, local_rank):
@@ -416,9 +660,8 @@ def run_decode(args, rank, world, local_rank):
     steps, warm = args.steps, max(args.warmup, 3)
     ntok = 16                                            # distinct token inputs, cycled
     x = make_inputs(B, ntok, H, K, V, R, seed=rank, dtype=torch.bfloat16, h0_std=0.02)
-    names = ("q", "k", "v", "a", "b", "gk")
-    host = {n: x[n].pin_memory() for n in names}
-    dv = {n: host[n].to(dev) for n in names}
+    host = {n: x[n].pin_memory() for n in NAMES}
+    dv = {n: host[n].to(dev) for n in NAMES}
     S = x["h0"].to(dev)
     scale = K ** -0.5
 
@@ -464,7 +707,7 @@ def run_decode(args, rank, world, local_rank):
     barrier()
     f0.record()
     for t in range(steps):
-        cur = {n: tok(host, t, n, R if n in ("a", "b") else 1).contiguous().to(dev, non_blocking=True) for n in names}
+        cur = {n: tok(host, t, n, R if n in ("a", "b") else 1).contiguous().to(dev, non_blocking=True) for n in NAMES}
         o, S2 = HD.fused_recurrent_dplr_delta_rule_fwd(cur["q"], cur["k"], cur["v"], cur["a"], cur["b"], cur["gk"], R,
                                                        scale, S, True, inplace_state=True)
         o_host.copy_(o, non_blocking=True)
@@ -477,6 +720,8 @@ def run_decode(args, rank, world, local_rank):
         tt = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms, ms_e2e = tt.tolist()
+    from hdla_impl_b200.recurrent import check_recurrent_status
+    check_recurrent_status(dev)
     if rank == 0:
         peaks, how = load_peaks()
         sec = ms / steps / 1e3
@@ -505,23 +750,22 @@ def run_decode(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg1", choices=sorted(WORKLOADS))
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.workload == "cfg2" and args.impl == "ours":
-        if args.steps == 10:
+        if args.steps == 20:
             args.steps = 128
         run_decode(args, rank, world, local_rank)
     elif args.impl == "reference":
-        if args.workload == "cfg2":
-            args.workload = "cfg1"
         run_reference(args, rank, world)
     else:
         run_ours(args, rank, world, local_rank)

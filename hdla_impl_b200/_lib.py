@@ -19,7 +19,12 @@ PHASE_ALL, PHASE_PRE, PHASE_TRANSITION, PHASE_STATE, PHASE_POST = 0x00, 0x10, 0x
 
 EXPORTS = (
     "hdla_version", "hdla_last_error", "hdla_chunk_workspace_bytes", "hdla_chunk_fwd", "hdla_chunk_bwd",
-    "hdla_recurrent_fwd", "hdla_kernel_launches", "hdla_debug_tc_buffer", "hdla_chunk_uses_tensor_cores", "hdla_chunk_fwd_noalloc", "hdla_timing_enable", "hdla_timing_report", "hdla_param_ab_fwd", "hdla_param_ab_bwd", "hdla_norm_gate_fwd", "hdla_norm_gate_bwd",
+    "hdla_recurrent_fwd", "hdla_chunk_uses_tensor_cores", "hdla_chunk_fwd_noalloc", "hdla_noalloc_read_status",
+    "hdla_recurrent_read_status", "hdla_compose_states", "hdla_param_ab_fwd", "hdla_param_ab_bwd",
+    "hdla_norm_gate_fwd", "hdla_norm_gate_bwd",
+    # include/hdla_debug.h
+    "hdla_kernel_launches", "hdla_timing_enable", "hdla_timing_report", "hdla_debug_tc_buffer",
+    "hdla_debug_wait_timeout",
 )
 
 
@@ -78,6 +83,14 @@ def load() -> C.CDLL:
         lib.hdla_chunk_fwd.argtypes = [dp, vp, vp, vp, vp, vp, vp, C.c_float, f32p, vp, f32p, vp, C.c_size_t, vp]
         lib.hdla_chunk_fwd_noalloc.restype = C.c_int
         lib.hdla_chunk_fwd_noalloc.argtypes = [dp, vp, vp, vp, vp, vp, vp, C.c_float, f32p, vp, f32p, vp]
+        lib.hdla_noalloc_read_status.restype = C.c_int
+        lib.hdla_noalloc_read_status.argtypes = [vp, vp]
+        lib.hdla_recurrent_read_status.restype = C.c_int
+        lib.hdla_recurrent_read_status.argtypes = [vp, vp]
+        lib.hdla_compose_states.restype = C.c_int
+        lib.hdla_compose_states.argtypes = [dp, vp, vp, vp, vp, vp, vp, C.c_int32, C.c_int64, C.c_int64, C.c_int32, vp]
+        lib.hdla_debug_wait_timeout.restype = C.c_int
+        lib.hdla_debug_wait_timeout.argtypes = [vp, C.c_uint64, vp]
         lib.hdla_chunk_bwd.restype = C.c_int
         lib.hdla_chunk_bwd.argtypes = [dp, vp, vp, vp, vp, vp, vp, C.c_float, f32p, vp, f32p,
                                        vp, vp, vp, vp, vp, vp, f32p, vp, C.c_size_t, vp]

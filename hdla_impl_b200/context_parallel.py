@@ -81,6 +81,15 @@ class _Attach(torch.autograd.Function):
         return go, torch.zeros(ctx.shape, dtype=ctx.dtype, device=ctx.device)
 
 
+def _compose(lib, dims, T, F, S0, pre, post, out, count, t_stride, f_stride, reverse, dev):
+    import ctypes as C
+    from . import _lib
+    rc = lib.hdla_compose_states(C.byref(dims), _lib.ptr(T), _lib.ptr(F), _lib.ptr(S0), _lib.ptr(pre), _lib.ptr(post),
+                                 _lib.ptr(out), int(count), int(t_stride), int(f_stride), int(reverse),
+                                 _lib.stream_ptr(dev))
+    _lib.check(rc, "hdla_compose_states")
+
+
 class _CPChunkFunction(torch.autograd.Function):
     """Context-parallel chunked operator on the CUDA library, with the scans of all ranks running
     concurrently.
@@ -89,8 +98,9 @@ class _CPChunkFunction(torch.autograd.Function):
     product of the chunk transition matrices (one scan of a K x K identity, ``HDLA_PHASE_TRANSITION``)
     and ``F`` the state reached from zero (``HDLA_PHASE_STATE``).  Every rank computes its ``(T, F)``
     at the same time, one all-gather distributes them, each rank composes the state entering its slice
-    locally and only then runs the real scan (``HDLA_PHASE_POST``).  Backward is the mirror image with
-    ``T^T``.  Per rank the scan work is three passes over T/world chunks instead of one pass over T.
+    locally (``hdla_compose_states``, one launch) and only then runs the real scan (``HDLA_PHASE_POST``).
+    Backward is the mirror image with ``T^T``; every rank contributes the gradient of its own returned
+    final state.  Per rank the scan work is three passes over T/world chunks instead of one pass over T.
     """
 
     @staticmethod
@@ -129,10 +139,9 @@ class _CPChunkFunction(torch.autograd.Function):
                 pack[2].zero_()
             maps = torch.empty(world, 3, B, H, K, V, **f32)
             dist.all_gather_into_tensor(maps, pack, group=group)
-            Ts, Fs = maps[:, 0], maps[:, 1]
-            S = maps[0, 2].clone()                                 # the initial state lives on rank 0
-            for j in range(rank):
-                S = torch.matmul(Ts[j], S) + Fs[j]
+            # state entering this rank's slice: the maps of ranks 0 .. rank-1 applied to the initial state
+            S = torch.empty(B, H, K, V, **f32)
+            _compose(lib, mk(0), maps[0, 0], maps[0, 1], maps[0, 2], None, None, S, rank, 3 * B * H, 3 * B * H, 0, dev)
             o = torch.empty_like(v)
             ht = torch.empty(B, H, K, V, **f32)
             fwd(_lib.PHASE_POST, S, o, ht)
@@ -146,9 +155,8 @@ class _CPChunkFunction(torch.autograd.Function):
     def backward(ctx, do, dht):
         import ctypes as C
         from . import _lib
-        from .hrdplr import _dims, check_status
+        from .hrdplr import _dims, _post_status, check_status
         q, k, v, a, b, gk, S_in, maps = ctx.saved_tensors
-        Ts = maps[:, 0]
         group = ctx.group
         dev = q.device
         rank, world = dist.get_rank(group), dist.get_world_size(group)
@@ -161,9 +169,10 @@ class _CPChunkFunction(torch.autograd.Function):
         do = do.contiguous().to(q.dtype)
         f32 = dict(dtype=torch.float32, device=dev)
         grads = [torch.empty_like(t) for t in (q, k, v, a, b, gk)]
+        mk = lambda phase: _dims(q, v, a, gk, ctx.R, ctx.chunk, phase | _lib.FLAG_WS_HOLDS_FWD)
 
         def bwd(phase, dht_, dh0_, with_grads):
-            d = _dims(q, v, a, gk, ctx.R, ctx.chunk, phase | _lib.FLAG_WS_HOLDS_FWD)
+            d = mk(phase)
             g = [_lib.ptr(t) for t in grads] if with_grads else [None] * 6
             rc = lib.hdla_chunk_bwd(C.byref(d), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(a), _lib.ptr(b),
                                     _lib.ptr(gk), float(ctx.scale), _lib.ptr(S_in), _lib.ptr(do), _lib.ptr(dht_),
@@ -172,23 +181,34 @@ class _CPChunkFunction(torch.autograd.Function):
 
         with torch.cuda.device(dev):
             bwd(_lib.PHASE_PRE, None, None, False)
-            # mirror image: gradient-from-zero maps and (last rank only) the gradient of the sequence's final state
+            # mirror image: every rank contributes its gradient-from-zero map G and the gradient of the final
+            # state IT returned (rank j's final state is the state entering rank j+1)
             pack = torch.empty(2, B, H, K, V, **f32)
             bwd(_lib.PHASE_STATE, None, pack[0], False)
-            if rank == world - 1 and dht is not None:
+            if dht is not None:
                 pack[1].copy_(dht)
             else:
                 pack[1].zero_()
             gmaps = torch.empty(world, 2, B, H, K, V, **f32)
             dist.all_gather_into_tensor(gmaps, pack, group=group)
-            Gs = gmaps[:, 0]
-            D = gmaps[world - 1, 1].clone()
-            for j in range(world - 1, rank, -1):
-                D = torch.matmul(Ts[j].transpose(-1, -2), D) + Gs[j]
+            # gradient of the state leaving this rank: dht_rank + E_{rank+1}, with E_j = T_j^T (dht_j + E_{j+1}) + G_j
+            # the gradient of the state entering rank j (E_world = 0)
+            D = torch.empty(B, H, K, V, **f32)
+            n_after = world - 1 - rank
+            nxt = min(rank + 1, world - 1)
+            _compose(lib, mk(0), maps[nxt, 0], gmaps[nxt, 0], None, gmaps[nxt, 1], gmaps[rank, 1], D, n_after,
+                     3 * B * H, 2 * B * H, 1, dev)
             dh0 = torch.empty(B, H, K, V, **f32)
             bwd(_lib.PHASE_POST, D, dh0, True)
+            _post_status(ws, dev)
         dq, dk, dv, da, db, dgk = grads
-        return dq, dk, dv, da, db, dgk, None, (dh0 if ctx.has_h0 else None), None, None, None
+        # the gradient of the state entering this slice is the sequence's dh0 on rank 0 only (initial_state is
+        # used there alone); elsewhere the argument was ignored and gets a zero gradient
+        if not ctx.has_h0:
+            dh0 = None
+        elif rank != 0:
+            dh0 = torch.zeros_like(dh0)
+        return dq, dk, dv, da, db, dgk, None, dh0, None, None, None
 
 
 def _fused_supported(q, v, gk, RANK_AB, chunk_size) -> bool:

@@ -1,49 +1,13 @@
 // extern "C" boundary of libhdla (declared in include/hdla.h): argument validation, dispatch,
-// thread-local error text.  Nothing here allocates, frees or synchronises device memory.
+// thread-local error text.  Nothing here allocates, frees or synchronises device memory, and the only
+// state kept between calls is the calling thread's last error text (instrumentation lives in debug.cu).
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
 
-#include <atomic>
-#include <map>
-#include <mutex>
-#include <string>
-#include <vector>
-
 #include "common.cuh"
 
 namespace hdla {
-
-static std::atomic<unsigned long long> g_launches{0};
-
-// ---- optional per-kernel timing (benchmark instrumentation) -------------------------------------
-// With timing on, an event is recorded on the call's stream at entry and after every launch; the
-// time between consecutive events of one call is attributed to the kernel launched in between.
-namespace {
-struct Mark { const char* name; cudaEvent_t ev; };
-std::mutex g_tmu;
-bool g_timing = false;
-std::vector<Mark> g_marks;
-thread_local cudaStream_t g_cur_stream = nullptr;
-
-void timing_mark(const char* name) {
-    std::lock_guard<std::mutex> lock(g_tmu);
-    if (!g_timing || g_marks.size() > (1u << 20)) return;
-    cudaEvent_t ev;
-    if (cudaEventCreate(&ev) != cudaSuccess) return;
-    cudaEventRecord(ev, g_cur_stream);
-    g_marks.push_back(Mark{name, ev});
-}
-}  // namespace
-
-void count_launch(const char* what) {
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    if (g_timing) timing_mark(what);
-}
-static void begin_call(void* stream) {
-    g_cur_stream = static_cast<cudaStream_t>(stream);
-    if (g_timing) timing_mark(nullptr);
-}
 
 static thread_local char g_err[512] = "";
 
@@ -55,7 +19,7 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-static int check_common(const HdlaDims* d, bool chunked) {
+int check_common(const HdlaDims* d, bool chunked) {
     if (!d) return fail(HDLA_ERR_INVALID, "dims is null");
     if (d->B <= 0 || d->T <= 0 || d->H <= 0 || d->K <= 0 || d->V <= 0 || d->R <= 0)
         return fail(HDLA_ERR_INVALID, "non-positive dimension: B=%d T=%d H=%d K=%d V=%d R=%d", d->B, d->T, d->H,
@@ -86,43 +50,6 @@ int hdla_version(void) { return HDLA_VERSION; }
 
 const char* hdla_last_error(void) { return g_err; }
 
-unsigned long long hdla_kernel_launches(void) { return g_launches.load(std::memory_order_relaxed); }
-
-void hdla_timing_enable(int on) {
-    std::lock_guard<std::mutex> lock(g_tmu);
-    g_timing = on != 0;
-}
-
-size_t hdla_timing_report(char* buf, size_t size) {
-    std::lock_guard<std::mutex> lock(g_tmu);
-    std::map<std::string, std::pair<long long, double>> acc;
-    for (size_t i = 0; i < g_marks.size(); ++i) {
-        cudaEventSynchronize(g_marks[i].ev);
-        if (g_marks[i].name && i > 0) {
-            float ms = 0.f;
-            if (cudaEventElapsedTime(&ms, g_marks[i - 1].ev, g_marks[i].ev) == cudaSuccess) {
-                auto& e = acc[g_marks[i].name];
-                e.first += 1;
-                e.second += ms;
-            }
-        }
-    }
-    for (auto& m : g_marks) cudaEventDestroy(m.ev);
-    g_marks.clear();
-    std::string out;
-    for (auto& kv : acc) {
-        char line[256];
-        snprintf(line, sizeof(line), "%s %lld %.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
-        out += line;
-    }
-    if (buf && size) {
-        const size_t n = out.size() < size - 1 ? out.size() : size - 1;
-        memcpy(buf, out.data(), n);
-        buf[n] = 0;
-    }
-    return out.size();
-}
-
 // bf16 problems the tensor-core pipeline supports use its workspace plan, everything else the fp32 one.
 static size_t tc_region_bytes(const HdlaDims& d, int with_backward) {
     return tc_supported(d) ? tc_workspace_bytes(d, with_backward) : 0;
@@ -141,22 +68,12 @@ int hdla_chunk_uses_tensor_cores(const HdlaDims* dims) {
     return tc_supported(*dims) ? 1 : 0;
 }
 
-int hdla_debug_tc_buffer(const HdlaDims* dims, const void* workspace, const char* name, float* out,
-                         void* cuda_stream) {
-    int rc = check_common(dims, true);
-    if (rc != HDLA_OK) return rc;
-    if (!tc_supported(*dims)) return fail(HDLA_ERR_UNSUPPORTED, "no tensor-core workspace for these dims");
-    if (!workspace || !name || !out) return fail(HDLA_ERR_INVALID, "debug_tc_buffer: null argument");
-    return tc_debug_buffer(*dims, static_cast<const unsigned char*>(workspace), name, out,
-                           static_cast<cudaStream_t>(cuda_stream));
-}
-
 int hdla_chunk_fwd(const HdlaDims* dims, const void* q, const void* k, const void* v, const void* a, const void* b,
                    const void* gk, float scale, const float* h0, void* o, float* ht, void* workspace,
                    size_t workspace_bytes, void* cuda_stream) {
     int rc = check_common(dims, true);
     if (rc != HDLA_OK) return rc;
-    begin_call(cuda_stream);
+    begin_call(static_cast<cudaStream_t>(cuda_stream));
     const int phase = dims->flags & HDLA_PHASE_MASK;
     const bool needs_o = phase == HDLA_PHASE_ALL || phase == HDLA_PHASE_POST;
     if (!q || !k || !v || !a || !b || !gk || (needs_o && !o))
@@ -166,8 +83,8 @@ int hdla_chunk_fwd(const HdlaDims* dims, const void* q, const void* k, const voi
     if (phase != HDLA_PHASE_ALL && !tc_supported(*dims))
         return fail(HDLA_ERR_UNSUPPORTED, "phased calls need the bf16 tensor-core pipeline (bf16, chunk 64, R=2, K=V=128)");
     if (tc_supported(*dims))
-        return tc_chunk_fwd(*dims, q, k, v, a, b, gk, scale, h0, o, ht, static_cast<unsigned char*>(workspace), true,
-                            static_cast<cudaStream_t>(cuda_stream));
+        return tc_chunk_fwd(*dims, q, k, v, a, b, gk, scale, h0, o, ht, static_cast<unsigned char*>(workspace),
+                            workspace_bytes, true, static_cast<cudaStream_t>(cuda_stream));
     return simt_chunk_fwd(*dims, q, k, v, a, b, gk, scale, h0, o, ht, static_cast<float*>(workspace), true,
                           static_cast<cudaStream_t>(cuda_stream));
 }
@@ -178,7 +95,7 @@ int hdla_chunk_bwd(const HdlaDims* dims, const void* q, const void* k, const voi
                    void* cuda_stream) {
     int rc = check_common(dims, true);
     if (rc != HDLA_OK) return rc;
-    begin_call(cuda_stream);
+    begin_call(static_cast<cudaStream_t>(cuda_stream));
     const int phase = dims->flags & HDLA_PHASE_MASK;
     const bool needs_grads = phase == HDLA_PHASE_ALL || phase == HDLA_PHASE_POST;
     if (!q || !k || !v || !a || !b || !gk || (phase != HDLA_PHASE_STATE && !d_o) ||
@@ -200,10 +117,29 @@ int hdla_recurrent_fwd(const HdlaDims* dims, const void* q, const void* k, const
                        const int64_t* cu_seqlens, int32_t n_seqs, int32_t reverse, void* cuda_stream) {
     int rc = check_common(dims, false);
     if (rc != HDLA_OK) return rc;
-    begin_call(cuda_stream);
+    begin_call(static_cast<cudaStream_t>(cuda_stream));
     if (!q || !k || !v || !a || !b || !gk || !o) return fail(HDLA_ERR_INVALID, "recurrent_fwd: null tensor pointer");
     return recurrent_fwd_launch(*dims, q, k, v, a, b, gk, scale, h0, o, ht, cu_seqlens, n_seqs, reverse,
                                 static_cast<cudaStream_t>(cuda_stream));
+}
+
+int hdla_recurrent_read_status(int32_t* dst, void* cuda_stream) {
+    if (!dst) return fail(HDLA_ERR_INVALID, "recurrent_read_status: dst is null");
+    return recurrent_read_status(dst, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int hdla_compose_states(const HdlaDims* dims, const float* T, const float* F, const float* S0, const float* pre,
+                        const float* post, float* out, int32_t count, int64_t t_stride, int64_t f_stride,
+                        int32_t reverse, void* cuda_stream) {
+    int rc = check_common(dims, false);
+    if (rc != HDLA_OK) return rc;
+    if (dims->K != 128 || dims->V != 128)
+        return fail(HDLA_ERR_UNSUPPORTED, "compose_states: K=%d V=%d (only K = V = 128)", dims->K, dims->V);
+    if (count < 0 || !out || (count > 0 && (!T || !F)))
+        return fail(HDLA_ERR_INVALID, "compose_states: null pointer or negative count");
+    begin_call(static_cast<cudaStream_t>(cuda_stream));
+    return tc_compose_states(T, F, S0, pre, post, out, dims->B * dims->H, count, f_stride, t_stride, reverse,
+                             static_cast<cudaStream_t>(cuda_stream));
 }
 
 int hdla_param_ab_fwd(const void* beta, const void* k, const void* log_f, void* a, void* b, int32_t B, int32_t T,
@@ -211,7 +147,7 @@ int hdla_param_ab_fwd(const void* beta, const void* k, const void* log_f, void* 
     if (!beta || !k || !log_f || !a || !b) return fail(HDLA_ERR_INVALID, "param_ab_fwd: null tensor pointer");
     if (B <= 0 || T <= 0 || H <= 0 || K <= 0) return fail(HDLA_ERR_INVALID, "param_ab_fwd: non-positive dimension");
     if (dtype != HDLA_F32 && dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", dtype);
-    begin_call(cuda_stream);
+    begin_call(static_cast<cudaStream_t>(cuda_stream));
     return param_ab_launch(false, beta, k, log_f, a, b, nullptr, nullptr, nullptr, B, T, H, K, dtype,
                            static_cast<cudaStream_t>(cuda_stream));
 }
@@ -223,7 +159,7 @@ int hdla_param_ab_bwd(const void* beta, const void* k, const void* log_f, const 
         return fail(HDLA_ERR_INVALID, "param_ab_bwd: null tensor pointer");
     if (B <= 0 || T <= 0 || H <= 0 || K <= 0) return fail(HDLA_ERR_INVALID, "param_ab_bwd: non-positive dimension");
     if (dtype != HDLA_F32 && dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", dtype);
-    begin_call(cuda_stream);
+    begin_call(static_cast<cudaStream_t>(cuda_stream));
     return param_ab_launch(true, beta, k, log_f, const_cast<void*>(da), const_cast<void*>(db), dbeta, dk, dlog_f, B, T,
                            H, K, dtype, static_cast<cudaStream_t>(cuda_stream));
 }
@@ -233,7 +169,7 @@ int hdla_norm_gate_fwd(const void* x, const void* gate, const void* weight, void
     if (!x || !gate || !weight || !o) return fail(HDLA_ERR_INVALID, "norm_gate_fwd: null tensor pointer");
     if (rows <= 0 || D <= 0 || rows > 0x7fffffffLL) return fail(HDLA_ERR_INVALID, "norm_gate_fwd: bad size");
     if (dtype != HDLA_F32 && dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", dtype);
-    begin_call(cuda_stream);
+    begin_call(static_cast<cudaStream_t>(cuda_stream));
     return norm_gate_launch(false, x, gate, weight, nullptr, o, nullptr, nullptr, nullptr, rows, D, eps, dtype,
                             static_cast<cudaStream_t>(cuda_stream));
 }
@@ -244,7 +180,7 @@ int hdla_norm_gate_bwd(const void* x, const void* gate, const void* weight, cons
         return fail(HDLA_ERR_INVALID, "norm_gate_bwd: null tensor pointer");
     if (rows <= 0 || D <= 0 || rows > 0x7fffffffLL) return fail(HDLA_ERR_INVALID, "norm_gate_bwd: bad size");
     if (dtype != HDLA_F32 && dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", dtype);
-    begin_call(cuda_stream);
+    begin_call(static_cast<cudaStream_t>(cuda_stream));
     return norm_gate_launch(true, x, gate, weight, d_o, nullptr, dx, dgate, dweight, rows, D, eps, dtype,
                             static_cast<cudaStream_t>(cuda_stream));
 }

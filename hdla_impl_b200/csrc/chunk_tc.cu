@@ -13,120 +13,17 @@
 //
 // All matrices between kernels are bf16 in the C8 blocked layout (tc_tiles.cuh) and move with
 // bulk asynchronous copies; all products run on tcgen05.mma with fp32 accumulation in TMEM.
+#include <cstdlib>
 #include <cstring>
 
-#include "tc_tiles.cuh"
+#include "tc_plan.cuh"
 
 namespace hdla {
 namespace {
 
 using namespace sm100;
+using namespace tc;
 using t8::Tile;
-
-constexpr int C = 64, K = 128, V = 128, R = 2;
-constexpr int CH64 = 16 * 64;      // chunks (16 B) of a [64 x 128] tile
-constexpr int CH128 = 16 * 128;    // chunks of a [128 x 128] tile
-
-// ------------------------------------------------------------------------------------------
-// workspace plan (byte offsets)
-// ------------------------------------------------------------------------------------------
-struct TcPlan {
-    int B, T, H, NT, BH;
-    long long G;
-    size_t status, Qh, Kh, Ah, Bh, Vc, E, ghat, Aqk, Aqb, Aak, Aab, M, W, P, U, Hs, V2, HT, zero;
-    int nseg, seg_len;                 // two-level scan: segments per sequence, chunks per segment
-    int lead_real;                     // the first segment in scan order is scanned for real in the first pass
-    size_t Tseg, Fseg, Sin;            // per (b, h, segment): transition [K,K], state from zero [K,V], entering state [K,V]
-    size_t dOc, dAqk, dAqb, DV2, DE, dgl, dW, dP, dAak, dM, tmp, dAab, dQh, dKh, dAh, dBh;
-    size_t total_fwd, total;
-};
-
-TcPlan make_tc_plan(const HdlaDims& d) {
-    TcPlan p{};
-    p.B = d.B; p.T = d.T; p.H = d.H;
-    p.NT = (d.T + C - 1) / C;
-    p.BH = d.B * d.H;
-    p.G = (long long)p.BH * p.NT;
-    size_t off = 0;
-    auto take = [&](size_t bytes_per_chunk) {
-        size_t o = off;
-        off += ((bytes_per_chunk * (size_t)p.G + 255) / 256) * 256;
-        return o;
-    };
-    p.status = off; off += 256;
-    p.Qh = take(16384); p.Kh = take(16384); p.Ah = take(32768); p.Bh = take(32768); p.Vc = take(16384);
-    p.E = take(K * 4); p.ghat = take(C * K * 2);
-    p.Aqk = take(8192); p.Aqb = take(16384); p.Aak = take(16384); p.Aab = take(32768); p.M = take(32768);
-    p.W = take(32768); p.P = take(32768); p.U = take(32768); p.Hs = take(32768); p.V2 = take(32768);
-    p.HT = off; off += (((size_t)p.BH * K * V * 4 + 255) / 256) * 256;
-    p.zero = off; off += 32768;
-    // Few (batch, head) pairs leave most SMs idle during the serial scan: cut each sequence into segments that
-    // are scanned concurrently (transition + state-from-zero per segment, composed, then the real scan).
-    // Two plans.  Phased calls (context parallelism) do not know the state entering the first segment, so every
-    // segment needs both twins: nseg * 2 CTAs per (batch, head) in the first pass.  A complete call scans its
-    // first segment for real in the first pass (from the given initial state), needs no twins for the last one,
-    // and so fits more, shorter segments: 2 nseg - 3 CTAs per (batch, head).
-    auto fit = [&](int nseg) {                           // -> no empty segment when NT is not a multiple
-        const int len = (p.NT + nseg - 1) / nseg;
-        return (p.NT + len - 1) / len;
-    };
-    int nseg_phased = 1;
-    while (nseg_phased < 8 && 2 * p.BH * (nseg_phased * 2) <= 148 && p.NT / (nseg_phased * 2) >= 4) nseg_phased *= 2;
-    nseg_phased = fit(nseg_phased);
-    int nseg_all = 1;
-    for (int n = 3; n <= 8; ++n)
-        if (p.BH * (2 * n - 3) <= 148 && p.NT / n >= 4) nseg_all = n;
-    nseg_all = fit(nseg_all);
-    if (nseg_all < 3) nseg_all = 1;
-    p.lead_real = (d.flags & HDLA_PHASE_MASK) == HDLA_PHASE_ALL && nseg_all > 1;
-    p.nseg = (d.flags & HDLA_PHASE_MASK) == HDLA_PHASE_ALL ? nseg_all : nseg_phased;
-    p.seg_len = (p.NT + p.nseg - 1) / p.nseg;
-    const int nseg_max = nseg_all > nseg_phased ? nseg_all : nseg_phased;     // same offsets for both kinds of call
-    const size_t slots = (size_t)p.BH * nseg_max;
-    p.Tseg = off; off += nseg_max > 1 ? slots * K * K * 4 : 0;
-    p.Fseg = off; off += nseg_max > 1 ? slots * K * V * 4 : 0;
-    p.Sin = off; off += nseg_max > 1 ? slots * K * V * 4 : 0;
-    p.total_fwd = off;
-    p.dOc = take(16384); p.dAqk = take(8192); p.dAqb = take(16384); p.DV2 = take(32768); p.DE = take(32768);
-    p.dgl = take(K * 4); p.dW = take(32768); p.dP = take(32768); p.dAak = take(16384); p.dM = take(32768);
-    p.tmp = take(32768); p.dAab = take(32768); p.dQh = take(16384); p.dKh = take(16384); p.dAh = take(32768);
-    p.dBh = take(32768);
-    p.total = off;
-    return p;
-}
-
-// bounded wait on an mbarrier; records a failure in the device status word and carries on
-__device__ __forceinline__ void wait_or_flag(uint64_t* bar, uint32_t parity, int* status, int code) {
-    if (!mbar_wait(bar, parity)) {
-        if (status) atomicExch(status, code);
-    }
-}
-
-__device__ __forceinline__ void wait_idle_or_flag(uint64_t* bar, uint32_t parity, int* status, int code) {
-    if (!mbar_wait_backoff(bar, parity)) {
-        if (status) atomicExch(status, code);
-    }
-}
-
-#ifdef HDLA_TIMELINE
-// Optional tracing build (-DHDLA_TIMELINE): per-CTA time stamps of the last backward kernel's stages.
-__device__ unsigned long long g_timeline[16384 * 16];
-__device__ __forceinline__ void tl_mark(long long g, int i) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    if (g < 16384) {
-        g_timeline[g * 16 + i] = t;
-        if (i == 0) {
-            unsigned sm;
-            asm volatile("mov.u32 %0, %smid;" : "=r"(sm));
-            g_timeline[g * 16 + 15] = sm;
-        }
-    }
-}
-#define TL(i) tl_mark(g, i)
-#else
-#define TL(i)
-#endif
 
 // ------------------------------------------------------------------------------------------
 // K1: cumulative decay and hat operands (CUDA cores, streaming)
@@ -143,10 +40,6 @@ struct PrepP {
     int T, H, NT, gdt;
     int* status;
 };
-
-// The hat operands are scaled by up to e^{|g_last|/2}; beyond this total log decay per chunk and
-// channel they leave the bf16/fp32 exponent range and the caller must use the fp32 pipeline.
-constexpr float kMaxChunkDecay = 150.f;
 
 // the seven 16-byte input pieces one thread handles per step: (row r, column group kc) of q, k, v, a0, a1, b0, b1
 struct PrepIn { uint4 q, k, v, a0, a1, b0, b1; };
@@ -232,7 +125,7 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
     if (tid < K) {
         const float gl = gis[C - 1][tid];
         p.E[(size_t)g * K + tid] = __expf(0.5f * gl);
-        if (!(fabsf(gl) <= kMaxChunkDecay)) atomicExch(p.status + 1, 1);      // also catches NaN
+        if (!(fabsf(gl) <= kMaxChunkDecay)) atomicExch(p.status + kStatusDecay, 1);      // also catches NaN
     }
     // hat operands: per instruction a warp covers 8 rows x 4 column groups, so every global access
     // is a run of full 32-byte sectors (64 B per row in, 128 B per column group out)
@@ -1527,9 +1420,17 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
 // With s0_identity the start is the identity and F is ignored (composition of the transitions themselves); `fin`
 // (optional) receives the state after the last segment.  With lead_final the first segment in scan order was scanned
 // for real: F of that segment is the state entering the next one, and the chain starts there.
+// The maps of (pair bh, segment s) are matrix number bh * bh_stride + s * seg_stride of F, Sin (K x V) and matrix
+// number bh * t_bh_stride + s * t_seg_stride of T (K x K).
+// `pre` (optional, indexed like F) is added to the running state before a segment's map is applied, `post` (optional,
+// one K x V matrix per pair) to the final value: with them the same chain serves the gradient of a sequence that is
+// cut over ranks, where every rank contributes the gradient of its own final state.
 __global__ void __launch_bounds__(128) compose_segments_kernel(const float* T, const float* F, const float* S0,
                                                                float* Sin, float* fin, int nseg, int reverse,
-                                                               int s0_identity, int lead_final) {
+                                                               int s0_identity, int lead_final, long long bh_stride,
+                                                               long long seg_stride, long long t_bh_stride,
+                                                               long long t_seg_stride, const float* pre,
+                                                               const float* post) {
     __shared__ float cur[K][33];
     const int bh = blockIdx.x, c0 = blockIdx.y * 32, k = threadIdx.x;
     float x[32];
@@ -1538,21 +1439,22 @@ __global__ void __launch_bounds__(128) compose_segments_kernel(const float* T, c
         x[c] = s0_identity ? (c0 + c == k ? 1.f : 0.f) : (S0 ? S0[((size_t)bh * K + k) * V + c0 + c] : 0.f);
     const int first = reverse ? nseg - 1 : 0, step = reverse ? -1 : 1;
     if (lead_final) {          // F of the first segment in scan order IS the state leaving it (it was scanned for real)
-        const size_t slot = (size_t)bh * nseg + first;
+        const size_t slot = (size_t)(bh * bh_stride + first * seg_stride);
 #pragma unroll
         for (int c = 0; c < 32; ++c) x[c] = F[(slot * K + k) * V + c0 + c];
     }
     for (int i = lead_final ? 1 : 0; i < nseg; ++i) {
         const int sgm = first + i * step;
-        const size_t slot = (size_t)bh * nseg + sgm;
+        const size_t slot = (size_t)(bh * bh_stride + sgm * seg_stride);
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
+            if (pre) x[c] += pre[(slot * K + k) * V + c0 + c];
             if (Sin) Sin[(slot * K + k) * V + c0 + c] = x[c];
             cur[k][c] = x[c];
         }
         __syncthreads();
         if (i + 1 < nseg || fin) {
-            const float* Tm = T + slot * K * K;
+            const float* Tm = T + (size_t)(bh * t_bh_stride + sgm * t_seg_stride) * K * K;
             float acc[32];
 #pragma unroll
             for (int c = 0; c < 32; ++c) acc[c] = s0_identity ? 0.f : F[(slot * K + k) * V + c0 + c];
@@ -1568,8 +1470,19 @@ __global__ void __launch_bounds__(128) compose_segments_kernel(const float* T, c
     }
     if (fin) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) fin[((size_t)bh * K + k) * V + c0 + c] = x[c];
+        for (int c = 0; c < 32; ++c)
+            fin[((size_t)bh * K + k) * V + c0 + c] = x[c] + (post ? post[((size_t)bh * K + k) * V + c0 + c] : 0.f);
     }
+}
+
+// A kernel whose only act is a wait that cannot succeed: one CTA waits on an mbarrier nobody arrives at, with a
+// budget of `budget_ns`, and records the failure in the status word like every other kernel of the pipeline.
+// It exists so that the path from a device-side timeout to the host-side error can be tested without a fault.
+__global__ void wait_timeout_probe_kernel(int* status, unsigned long long budget_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) { mbar_init(&bar, 1); fence_mbar_init(); }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait(&bar, 0, budget_ns)) atomicExch(status + kStatusWait, 99);
 }
 
 constexpr int kGradSmem = 5 * 32768 + 3 * 16384 + 2 * 8192;
@@ -1598,6 +1511,21 @@ int sm_count() {
 
 }  // namespace
 
+int tc_compose_states(const float* T, const float* F, const float* S0, const float* pre, const float* post,
+                      float* out, int BH, int count, long long f_stride, long long t_stride, int reverse,
+                      cudaStream_t st) {
+    compose_segments_kernel<<<dim3(BH, V / 32), 128, 0, st>>>(T, F, S0, nullptr, out, count, reverse, 0, 0, 1, f_stride,
+                                                              1, t_stride, pre, post);
+    HDLA_CHECK_LAUNCH("compose_segments_kernel");
+    return HDLA_OK;
+}
+
+int tc_wait_timeout_probe(int* status, unsigned long long budget_ns, cudaStream_t st) {
+    wait_timeout_probe_kernel<<<1, 32, 0, st>>>(status, budget_ns);
+    HDLA_CHECK_LAUNCH("wait_timeout_probe_kernel");
+    return HDLA_OK;
+}
+
 bool tc_supported(const HdlaDims& d) {
     return d.dtype == HDLA_BF16 && !(d.flags & HDLA_FLAG_FORCE_SIMT) && effective_chunk(d.T, d.C) == C && d.R == R &&
            d.K == K && d.V == V && (long long)d.B * d.H * ((d.T + C - 1) / C) < 0x7fffffffLL;
@@ -1611,9 +1539,12 @@ size_t tc_workspace_bytes(const HdlaDims& d, int with_backward) {
 #define TRY(x) do { int rc__ = (x); if (rc__ != HDLA_OK) return rc__; } while (0)
 
 int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a, const void* b,
-                 const void* gk, float scale, const float* h0, void* o, float* ht, unsigned char* ws, bool need_o,
-                 cudaStream_t st) {
+                 const void* gk, float scale, const float* h0, void* o, float* ht, unsigned char* ws, size_t ws_bytes,
+                 bool need_o, cudaStream_t st) {
     const TcPlan pl = make_tc_plan(d);
+    // a workspace sized for the backward pass also receives what only the backward kernels read
+    const bool save_bwd = ws_bytes >= pl.total;
+    static const bool unfused = getenv("HDLA_UNFUSED_PREP") != nullptr;
     static thread_local int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1638,19 +1569,24 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         cudaError_t e = cudaMemsetAsync(ws + pl.status, 0, 256, st);
         if (e == cudaSuccess) e = cudaMemsetAsync(ws + pl.zero, 0, 32768, st);
         if (e != cudaSuccess) return fail(HDLA_ERR_CUDA, "workspace clear: %s", cudaGetErrorString(e));
-        PrepP pp{(bp)q, (bp)k, (bp)v, (bp)a, (bp)b, gk, U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc),
-                 F(pl.E), (__nv_bfloat16*)(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status};
-        prep_hat_kernel<<<G, 128, 0, st>>>(pp);
-        HDLA_CHECK_LAUNCH("prep_hat_kernel");
-        GramP gp{U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Aak), U4(pl.Aab), status};
-        gram_tc_kernel<<<G, 128, 98304 + 1024, st>>>(gp);
-        HDLA_CHECK_LAUNCH("gram_tc_kernel");
-        InvP ivp{U4(pl.Aab), U4(pl.M), status};
-        inverse_tc_kernel<<<G, 128, 32768, st>>>(ivp);
-        HDLA_CHECK_LAUNCH("inverse_tc_kernel");
-        WuP wp{U4(pl.M), U4(pl.Ah), U4(pl.Aak), U4(pl.Vc), U4(pl.P), U4(pl.U), U4(pl.W), status};
-        wu_tc_kernel<<<G, 128, 98304, st>>>(wp);
-        HDLA_CHECK_LAUNCH("wu_tc_kernel");
+        if (!unfused) {
+            TRY(tc_launch_chunk_prep(pl, d, q, k, v, a, b, gk, scale, ws, save_bwd, st));
+        } else {
+            if (!save_bwd) return fail(HDLA_ERR_WORKSPACE, "the unfused preparation needs the backward-sized workspace");
+            PrepP pp{(bp)q, (bp)k, (bp)v, (bp)a, (bp)b, gk, U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc),
+                     F(pl.E), (__nv_bfloat16*)(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status};
+            prep_hat_kernel<<<G, 128, 0, st>>>(pp);
+            HDLA_CHECK_LAUNCH("prep_hat_kernel");
+            GramP gp{U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Aak), U4(pl.Aab), status};
+            gram_tc_kernel<<<G, 128, 98304 + 1024, st>>>(gp);
+            HDLA_CHECK_LAUNCH("gram_tc_kernel");
+            InvP ivp{U4(pl.Aab), U4(pl.M), status};
+            inverse_tc_kernel<<<G, 128, 32768, st>>>(ivp);
+            HDLA_CHECK_LAUNCH("inverse_tc_kernel");
+            WuP wp{U4(pl.M), U4(pl.Ah), U4(pl.Aak), U4(pl.Vc), U4(pl.P), U4(pl.U), U4(pl.W), status};
+            wu_tc_kernel<<<G, 128, 98304, st>>>(wp);
+            HDLA_CHECK_LAUNCH("wu_tc_kernel");
+        }
         if (phase == HDLA_PHASE_PRE) return HDLA_OK;
     }
     auto scan_params = [&](const float* init, uint4* ck, uint4* y, float* fin, float* fin2, int no_store) {
@@ -1673,7 +1609,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             scan_tc_kernel<<<dim3(pl.BH * pl.nseg, 2), 256, 196608, st>>>(s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
             compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, nullptr, ht,
-                                                                         pl.nseg, 0, 1, 0);
+                                                                         pl.nseg, 0, 1, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
         }
@@ -1688,7 +1624,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         if (!ht) return fail(HDLA_ERR_INVALID, "state pass needs the output pointer (ht)");
         if (pl.nseg > 1) {                    // affine maps of the segments are in the workspace (TRANSITION phase)
             compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), h0, nullptr, ht,
-                                                                         pl.nseg, 0, 0, 0);
+                                                                         pl.nseg, 0, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
         }
@@ -1707,7 +1643,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         // ... the state entering every later segment follows from the first segment's final state ...
         compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
-                                                                     pl.nseg, 0, 0, 1);
+                                                                     pl.nseg, 0, 0, 1, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         // ... and the remaining segments are scanned for real at once
         ScanTcP s2 = scan_params(F(pl.Sin), U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
@@ -1724,7 +1660,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
         }
         // ... composed into the state entering every segment ...
-        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), nullptr, pl.nseg, 0, 0, 0);
+        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), nullptr, pl.nseg, 0, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         // ... and the real scan of all segments at once
         ScanTcP s2 = scan_params(F(pl.Sin), U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
@@ -1754,7 +1690,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     if (!(d.flags & HDLA_FLAG_WS_HOLDS_FWD)) {
         HdlaDims df = d;
         df.flags &= ~HDLA_PHASE_MASK;
-        TRY(tc_chunk_fwd(df, q, k, v, a, b, gk, scale, h0, nullptr, nullptr, ws, false, st));
+        TRY(tc_chunk_fwd(df, q, k, v, a, b, gk, scale, h0, nullptr, nullptr, ws, make_tc_plan(df).total, false, st));
     }
     const TcPlan pl = make_tc_plan(d);
     auto U4 = [&](size_t off) { return reinterpret_cast<uint4*>(ws + off); };
@@ -1789,7 +1725,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
             compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), dht, nullptr, dh0,
-                                                                         pl.nseg, 1, 0, 0);
+                                                                         pl.nseg, 1, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
         }
@@ -1808,7 +1744,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         scan_tc_kernel<<<pl.BH * (pl.nseg - 1), 256, 196608, st>>>(s1);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
-                                                                     pl.nseg, 1, 0, 1);
+                                                                     pl.nseg, 1, 0, 1, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         ScanTcP s2 = rscan_params(F(pl.Sin), U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
         s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;
@@ -1823,7 +1759,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
         }
-        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), nullptr, pl.nseg, 1, 0, 0);
+        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), nullptr, pl.nseg, 1, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         ScanTcP s2 = rscan_params(F(pl.Sin), U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
         s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;
@@ -1862,9 +1798,7 @@ int tc_debug_buffer(const HdlaDims& d, const unsigned char* ws, const char* name
                        {"V2", pl.V2, 128, 128},
                        {"dOc", pl.dOc, 64, 128}, {"dAqk", pl.dAqk, 64, 64}, {"dAqb", pl.dAqb, 64, 128},
                        {"DV2", pl.DV2, 128, 128}, {"DE", pl.DE, 128, 128}, {"dW", pl.dW, 128, 128},
-                       {"dP", pl.dP, 128, 128}, {"dAak", pl.dAak, 128, 64}, {"dM", pl.dM, 128, 128},
-                       {"tmp", pl.tmp, 128, 128}, {"dAab", pl.dAab, 128, 128}, {"dQh", pl.dQh, 64, 128},
-                       {"dKh", pl.dKh, 64, 128}, {"dAh", pl.dAh, 128, 128}, {"dBh", pl.dBh, 128, 128}};
+                       {"dP", pl.dP, 128, 128}, {"dAak", pl.dAak, 128, 64}, {"dAab", pl.dAab, 128, 128}};
     for (const Ent& e : tab)
         if (!strcmp(e.n, name)) {
             c8_to_rowmajor_kernel<<<(unsigned)pl.G, 128, 0, st>>>(reinterpret_cast<const uint4*>(ws + e.off), out,

@@ -14,6 +14,10 @@ int fail(int code, const char* fmt, ...);
 // Process-wide count of kernel launches (see hdla_kernel_launches()); when kernel timing is on
 // (hdla_timing_enable) it also records a CUDA event after the launch on the call's stream.
 void count_launch(const char* what);
+// Tells the instrumentation which stream the calling thread's current entry point launches on.
+void begin_call(cudaStream_t stream);
+// Validation shared by all entry points (api.cu).
+int check_common(const HdlaDims* d, bool chunked);
 
 #define HDLA_CHECK_LAUNCH(what)                                                       \
     do {                                                                              \
@@ -64,11 +68,16 @@ int norm_gate_launch(bool backward, const void* x, const void* gate, const void*
 bool tc_supported(const HdlaDims& d);
 size_t tc_workspace_bytes(const HdlaDims& d, int with_backward);
 int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a, const void* b,
-                 const void* gk, float scale, const float* h0, void* o, float* ht, unsigned char* ws, bool need_o,
-                 cudaStream_t st);
+                 const void* gk, float scale, const float* h0, void* o, float* ht, unsigned char* ws, size_t ws_bytes,
+                 bool need_o, cudaStream_t st);
 int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a, const void* b,
                  const void* gk, float scale, const float* h0, const void* d_o, const float* dht, void* dq, void* dk,
                  void* dv, void* da, void* db, void* dgk, float* dh0, unsigned char* ws, cudaStream_t st);
+int tc_compose_states(const float* T, const float* F, const float* S0, const float* pre, const float* post,
+                      float* out, int BH, int count, long long f_stride, long long t_stride, int reverse,
+                      cudaStream_t st);
+int tc_wait_timeout_probe(int* status, unsigned long long budget_ns, cudaStream_t st);
+int recurrent_read_status(int* dst, cudaStream_t st);
 int tc_debug_buffer(const HdlaDims& d, const unsigned char* ws, const char* name, float* out, cudaStream_t st);
 
 }  // namespace hdla

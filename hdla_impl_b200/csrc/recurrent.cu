@@ -21,6 +21,10 @@
 namespace hdla {
 namespace {
 
+// Set to 1 by the decode kernel when its (time-bounded) wait for the state tile ran out: the call's
+// outputs are invalid and the final state was not written.  Read with hdla_recurrent_read_status().
+__device__ int g_recurrent_status;
+
 struct RecParams {
     const void *q, *k, *v, *a, *b, *gk;
     const float* h0;
@@ -189,6 +193,7 @@ __global__ void __launch_bounds__(256) recurrent_bulk_kernel(RecParams p) {
     long long bos, len;
     if (p.cu) { bos = p.cu[n]; len = p.cu[n + 1] - bos; }
     else      { bos = (long long)n * p.T; len = p.T; }
+    bool state_ok = true;                                        // false once the wait for the state tile ran out
 
     if (threadIdx.x == 0) {
         sm100::mbar_init(&bar, 1);
@@ -219,7 +224,10 @@ __global__ void __launch_bounds__(256) recurrent_bulk_kernel(RecParams p) {
         for (int i = threadIdx.x; i < V; i += blockDim.x)
             s_v[i] = ld_elem(p.v, ((size_t)t * H + h) * V + i, p.dt);
         __syncthreads();
-        if (step == 0 && p.h0) sm100::mbar_wait(&bar, 0);       // bounded; the tile is in shared memory after it
+        if (step == 0 && p.h0) {                                 // bounded; the tile is in shared memory after it
+            state_ok = __syncthreads_and(sm100::mbar_wait(&bar, 0) ? 1 : 0) != 0;
+            if (!state_ok && threadIdx.x == 0) atomicExch(&g_recurrent_status, 1);
+        }
 
         float sa[R][4];
 #pragma unroll
@@ -280,8 +288,11 @@ __global__ void __launch_bounds__(256) recurrent_bulk_kernel(RecParams p) {
         }
         __syncthreads();                                         // vectors are single buffered
     }
-    if (len == 0 && p.h0) sm100::mbar_wait(&bar, 0);
-    if (p.ht) {
+    if (len == 0 && p.h0) {
+        state_ok = __syncthreads_and(sm100::mbar_wait(&bar, 0) ? 1 : 0) != 0;
+        if (!state_ok && threadIdx.x == 0) atomicExch(&g_recurrent_status, 1);
+    }
+    if (p.ht && state_ok) {                                      // a state that never arrived is not written back
         sm100::fence_proxy_async();
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -306,6 +317,14 @@ int launch_r(const RecParams& p, int R, int blocks, int threads, size_t smem, cu
 
 }  // namespace
 
+int recurrent_read_status(int* dst, cudaStream_t st) {
+    void* sym = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&sym, g_recurrent_status);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dst, sym, sizeof(int), cudaMemcpyDefault, st);
+    if (e != cudaSuccess) return fail(HDLA_ERR_CUDA, "recurrent status: %s", cudaGetErrorString(e));
+    return HDLA_OK;
+}
+
 int recurrent_fwd_launch(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a,
                          const void* b, const void* gk, float scale, const float* h0, void* o, float* ht,
                          const int64_t* cu_seqlens, int n_seqs, int reverse, cudaStream_t st) {
@@ -327,10 +346,11 @@ int recurrent_fwd_launch(const HdlaDims& d, const void* q, const void* k, const 
         int dev = 0;
         cudaGetDevice(&dev);
         if (attr_dev != dev) {
-            cudaFuncSetAttribute(recurrent_bulk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 + 16384);
-            cudaFuncSetAttribute(recurrent_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 + 16384);
-            cudaFuncSetAttribute(recurrent_bulk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 + 16384);
-            cudaFuncSetAttribute(recurrent_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 + 16384);
+            cudaError_t e = cudaFuncSetAttribute(recurrent_bulk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 + 16384);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(recurrent_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 + 16384);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(recurrent_bulk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 + 16384);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(recurrent_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536 + 16384);
+            if (e != cudaSuccess) return fail(HDLA_ERR_CUDA, "recurrent: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
             attr_dev = dev;
         }
         switch (d.R) {

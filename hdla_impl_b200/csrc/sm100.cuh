@@ -36,22 +36,43 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls and returns false (the caller records an error and
-// carries on to its clean-up path); never spins forever.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = 1u << 24) {
-    for (uint32_t i = 0; i < limit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Longest time a thread waits on an mbarrier before it gives up.  A copy or an MMA that has not
+// completed after this long never will; the limit is in TIME (the global nanosecond timer), so it
+// does not depend on the clock or on how long one poll takes.
+constexpr uint64_t kWaitBudgetNs = 2000000000ull;
+
+// Bounded wait: gives up when `budget_ns` have passed and returns false (the caller records an error
+// and carries on to its clean-up path); never spins forever.  The timer is read once per 64 polls.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64_t budget_ns = kWaitBudgetNs) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (globaltimer_ns() - t0 > budget_ns) return false;
+    }
 }
 
 // Same, for long waits by threads that have nothing else to do: sleeps between polls so the
 // polling warps do not take issue slots from the warp that is producing what they wait for.
-__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, uint32_t limit = 1u << 22) {
-    for (uint32_t i = 0; i < limit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(200);
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t* bar, uint32_t parity, uint64_t budget_ns = kWaitBudgetNs) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+            __nanosleep(200);
+        }
+        if (globaltimer_ns() - t0 > budget_ns) return false;
     }
-    return false;
 }
 
 // ------------------------------------------------------------------------------ bulk async copy

@@ -1,0 +1,137 @@
+// Shared declarations of the tensor-core (bf16) pipeline: tile constants, the workspace plan and
+// the bounded-wait helpers.  Included by the kernel files of that pipeline only.
+#pragma once
+#include "tc_tiles.cuh"
+
+namespace hdla {
+namespace tc {
+
+using namespace sm100;
+using t8::Tile;
+
+constexpr int C = 64, K = 128, V = 128, R = 2;
+constexpr int CH64 = 16 * 64;      // chunks (16 B) of a [64 x 128] tile
+constexpr int CH128 = 16 * 128;    // chunks of a [128 x 128] tile
+
+// ------------------------------------------------------------------------------------------
+// workspace plan (byte offsets)
+// ------------------------------------------------------------------------------------------
+struct TcPlan {
+    int B, T, H, NT, BH;
+    long long G;
+    size_t status, Qh, Kh, Ah, Bh, Vc, E, ghat, Aqk, Aqb, Aak, Aab, M, W, P, U, Hs, V2, HT, zero;
+    int nseg, seg_len;                 // two-level scan: segments per sequence, chunks per segment
+    int lead_real;                     // the first segment in scan order is scanned for real in the first pass
+    size_t Tseg, Fseg, Sin;            // per (b, h, segment): transition [K,K], state from zero [K,V], entering state [K,V]
+    size_t dOc, dAqk, dAqb, DV2, DE, dgl, dW, dP, dAak, dAab;
+    size_t total_fwd, total;
+};
+
+inline TcPlan make_tc_plan(const HdlaDims& d) {
+    TcPlan p{};
+    p.B = d.B; p.T = d.T; p.H = d.H;
+    p.NT = (d.T + C - 1) / C;
+    p.BH = d.B * d.H;
+    p.G = (long long)p.BH * p.NT;
+    size_t off = 0;
+    auto take = [&](size_t bytes_per_chunk) {
+        size_t o = off;
+        off += ((bytes_per_chunk * (size_t)p.G + 255) / 256) * 256;
+        return o;
+    };
+    p.status = off; off += 256;
+    // forward region: what the scan and the output kernel read
+    p.Qh = take(16384); p.Kh = take(16384); p.Bh = take(32768); p.Vc = take(16384);
+    p.E = take(K * 4);
+    p.Aqk = take(8192); p.Aqb = take(16384);
+    p.W = take(32768); p.U = take(32768); p.Hs = take(32768); p.V2 = take(32768);
+    p.HT = off; off += (((size_t)p.BH * K * V * 4 + 255) / 256) * 256;
+    p.zero = off; off += 32768;
+    // Few (batch, head) pairs leave most SMs idle during the serial scan: cut each sequence into segments that
+    // are scanned concurrently (transition + state-from-zero per segment, composed, then the real scan).
+    // Two plans.  Phased calls (context parallelism) do not know the state entering the first segment, so every
+    // segment needs both twins: nseg * 2 CTAs per (batch, head) in the first pass.  A complete call scans its
+    // first segment for real in the first pass (from the given initial state), needs no twins for the last one,
+    // and so fits more, shorter segments: 2 nseg - 3 CTAs per (batch, head).
+    auto fit = [&](int nseg) {                           // -> no empty segment when NT is not a multiple
+        const int len = (p.NT + nseg - 1) / nseg;
+        return (p.NT + len - 1) / len;
+    };
+    int nseg_phased = 1;
+    while (nseg_phased < 8 && 2 * p.BH * (nseg_phased * 2) <= 148 && p.NT / (nseg_phased * 2) >= 4) nseg_phased *= 2;
+    nseg_phased = fit(nseg_phased);
+    int nseg_all = 1;
+    for (int n = 3; n <= 8; ++n)
+        if (p.BH * (2 * n - 3) <= 148 && p.NT / n >= 4) nseg_all = n;
+    nseg_all = fit(nseg_all);
+    if (nseg_all < 3) nseg_all = 1;
+    p.lead_real = (d.flags & HDLA_PHASE_MASK) == HDLA_PHASE_ALL && nseg_all > 1;
+    p.nseg = (d.flags & HDLA_PHASE_MASK) == HDLA_PHASE_ALL ? nseg_all : nseg_phased;
+    p.seg_len = (p.NT + p.nseg - 1) / p.nseg;
+    const int nseg_max = nseg_all > nseg_phased ? nseg_all : nseg_phased;     // same offsets for both kinds of call
+    const size_t slots = (size_t)p.BH * nseg_max;
+    p.Tseg = off; off += nseg_max > 1 ? slots * K * K * 4 : 0;
+    p.Fseg = off; off += nseg_max > 1 ? slots * K * V * 4 : 0;
+    p.Sin = off; off += nseg_max > 1 ? slots * K * V * 4 : 0;
+    p.total_fwd = off;
+    // backward region: forward intermediates that only the backward kernels read, then the backward's own
+    p.Ah = take(32768); p.ghat = take(C * K * 2); p.Aak = take(16384); p.M = take(32768); p.P = take(32768);
+    p.Aab = take(32768);
+    p.dOc = take(16384); p.dAqk = take(8192); p.dAqb = take(16384); p.DV2 = take(32768); p.DE = take(32768);
+    p.dgl = take(K * 4); p.dW = take(32768); p.dP = take(32768); p.dAak = take(16384); p.dAab = take(32768);
+    p.total = off;
+    return p;
+}
+
+// The workspace starts with a 256-byte status block of int32 words written by the kernels:
+//   word 0  code of a device-side wait that ran out (0 = none)
+//   word 1  1 if some chunk's total log decay exceeds kMaxChunkDecay in some channel
+//   word 2  the largest |total log decay of a chunk| seen, as the bit pattern of a non-negative float
+constexpr int kStatusWait = 0, kStatusDecay = 1, kStatusMaxDecay = 2;
+
+// The hat operands are scaled by up to e^{|g_last|/2}; beyond this total log decay per chunk and
+// channel they leave the bf16/fp32 exponent range and the caller must use the fp32 pipeline.
+constexpr float kMaxChunkDecay = 150.f;
+
+// bounded wait on an mbarrier; records a failure in the device status word and carries on
+__device__ __forceinline__ void wait_or_flag(uint64_t* bar, uint32_t parity, int* status, int code) {
+    if (!mbar_wait(bar, parity)) {
+        if (status) atomicExch(status, code);
+    }
+}
+
+__device__ __forceinline__ void wait_idle_or_flag(uint64_t* bar, uint32_t parity, int* status, int code) {
+    if (!mbar_wait_backoff(bar, parity)) {
+        if (status) atomicExch(status, code);
+    }
+}
+
+#ifdef HDLA_TIMELINE
+// Optional tracing build (-DHDLA_TIMELINE): per-CTA time stamps of the last backward kernel's stages.
+static __device__ unsigned long long g_timeline[16384 * 16];
+__device__ __forceinline__ void tl_mark(long long g, int i) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    if (g < 16384) {
+        g_timeline[g * 16 + i] = t;
+        if (i == 0) {
+            unsigned sm;
+            asm volatile("mov.u32 %0, %smid;" : "=r"(sm));
+            g_timeline[g * 16 + 15] = sm;
+        }
+    }
+}
+#define TL(i) tl_mark(g, i)
+#else
+#define TL(i)
+#endif
+
+
+}  // namespace tc
+
+// chunk_prep.cu: cumulative decay, hat operands, score matrices, inverse, Wh / u in one launch
+int tc_launch_chunk_prep(const tc::TcPlan& pl, const HdlaDims& d, const void* q, const void* k, const void* v,
+                         const void* a, const void* b, const void* gk, float scale, unsigned char* ws, bool save_bwd,
+                         cudaStream_t st);
+
+}  // namespace hdla

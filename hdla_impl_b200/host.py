@@ -75,6 +75,7 @@ _OUT = ("o", "dq", "dk", "dv", "da", "db", "dgk")
 
 
 _copy_streams: Dict[int, tuple] = {}
+_stages: Dict[tuple, list] = {}      # (device index, slice shape key) -> [slot0, slot1], each dict(bufs=..., done=Event|None)
 
 
 def _streams(dev: torch.device):
@@ -86,16 +87,28 @@ def _streams(dev: torch.device):
     return _copy_streams[idx]
 
 
+def join_host_streams(device) -> None:
+    """Make the current stream of ``device`` wait for every copy that ``chunk_fwd_bwd_from_host(sync=False)`` has
+    enqueued so far: work enqueued (or an event recorded) on the current stream afterwards is ordered after the
+    results have reached host memory."""
+    dev = torch.device(device)
+    s_in, s_out = _streams(dev)
+    cur = torch.cuda.current_stream(dev)
+    cur.wait_stream(s_out)
+    cur.wait_stream(s_in)
+
+
 def chunk_fwd_bwd_from_host(host_in: Dict[str, torch.Tensor], host_out: Optional[Dict[str, torch.Tensor]],
                             RANK_AB: int, device, scale: Optional[float] = None, chunk_size: int = 64,
                             slice_batch: int = 1, sync: bool = True) -> Dict[str, torch.Tensor]:
     """``host_in``: pinned CPU tensors q,k,v,a,b,gk and ``do`` (gradient of o), layouts as in
     ``chunk_hrdplr_delta_rule``.  Returns (and fills, if given) ``host_out`` with pinned CPU tensors
     o,dq,dk,dv,da,db,dgk.  With ``sync`` (default) the device is synchronised before returning.  With
-    ``sync=False`` the call only enqueues: the current stream is made to wait for the last copy-out, so
-    work enqueued on it afterwards (or an event recorded on it) is ordered after the results, and the
-    copy-in of a following call overlaps this call's copy-out; the caller must not touch ``host_in`` /
-    ``host_out`` before synchronising."""
+    ``sync=False`` the call only enqueues and nothing waits for the copy-out: the copy-in and the kernels of a
+    following call run under this call's copy-out (the device buffers of a slice are reused as soon as the
+    kernels that read them are done, which an event tracks across calls).  The caller must not touch
+    ``host_in`` / ``host_out`` before ``join_host_streams(device)`` plus a synchronisation of the current
+    stream, or ``torch.cuda.synchronize(device)``."""
     dev = torch.device(device)
     B = host_in["q"].shape[0]
     if host_out is None:
@@ -111,40 +124,38 @@ def chunk_fwd_bwd_from_host(host_in: Dict[str, torch.Tensor], host_out: Optional
             host_out[n] = torch.empty(src.shape, dtype=src.dtype, pin_memory=True)
     cur = torch.cuda.current_stream(dev)
     s_in, s_out = _streams(dev)
-    s_in.wait_stream(cur)
     bounds = [(i, min(i + slice_batch, B)) for i in range(0, B, slice_batch)]
-    stage = [None, None]                      # two sets of device input buffers
-    done_compute = [None, None]
     with torch.cuda.device(dev):
         for idx, (lo, hi) in enumerate(bounds):
-            slot = idx & 1
+            key = (dev.index, hi - lo) + tuple((n, tuple(host_in[n].shape[1:]), host_in[n].dtype) for n in names_in)
+            slots = _stages.setdefault(key, [dict(bufs=None, done=None), dict(bufs=None, done=None)])
+            slot = slots[idx & 1]                  # two sets of device input buffers, alternating
             with torch.cuda.stream(s_in):
-                if done_compute[slot] is not None:
-                    s_in.wait_event(done_compute[slot])        # the buffers of slice idx-2 are free again
-                if stage[slot] is None or stage[slot]["q"].shape[0] != hi - lo:
-                    stage[slot] = {n: torch.empty((hi - lo,) + tuple(host_in[n].shape[1:]), dtype=host_in[n].dtype,
-                                                  device=dev) for n in names_in}
+                if slot["done"] is not None:
+                    s_in.wait_event(slot["done"])              # the kernels that last read these buffers are done
+                if slot["bufs"] is None:
+                    slot["bufs"] = {n: torch.empty((hi - lo,) + tuple(host_in[n].shape[1:]), dtype=host_in[n].dtype,
+                                                   device=dev) for n in names_in}
+                    for t in slot["bufs"].values():
+                        t.record_stream(cur)                   # allocated on the copy stream, read by the kernels
                 for n in names_in:
-                    stage[slot][n].copy_(host_in[n][lo:hi], non_blocking=True)
-                    stage[slot][n].record_stream(cur)          # allocated on the copy stream, read by the kernels
+                    slot["bufs"][n].copy_(host_in[n][lo:hi], non_blocking=True)
                 ready = torch.cuda.Event()
                 ready.record(s_in)
             cur.wait_event(ready)
-            lv = [stage[slot][n].requires_grad_(True) for n in _IN]
+            lv = [slot["bufs"][n].requires_grad_(True) for n in _IN]
             o, _ = chunk_hrdplr_delta_rule(*lv, RANK_AB, scale=scale, chunk_size=chunk_size)
-            grads = torch.autograd.grad(o, lv, stage[slot]["do"])
+            grads = torch.autograd.grad(o, lv, slot["bufs"]["do"])
             ev = torch.cuda.Event()
             ev.record(cur)
-            done_compute[slot] = ev
+            slot["done"] = ev
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev)
                 for n, t in zip(_OUT, (o.detach(),) + tuple(grads)):
                     t.record_stream(s_out)
                     host_out[n][lo:hi].copy_(t, non_blocking=True)
             for n in _IN:
-                stage[slot][n].requires_grad_(False)
-        cur.wait_stream(s_out)
-        cur.wait_stream(s_in)
+                slot["bufs"][n].requires_grad_(False)
     if sync:
         torch.cuda.synchronize(dev)
     return host_out

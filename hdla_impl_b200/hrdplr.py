@@ -9,6 +9,7 @@ from __future__ import annotations
 import ctypes as C
 import functools
 import os
+import warnings
 from typing import Optional, Tuple
 
 import torch
@@ -73,21 +74,39 @@ def workspace_bytes(dims: _lib.HdlaDims, with_backward: bool) -> int:
 
 
 # ---- device status words ----------------------------------------------------------------------
-# The bf16 tensor-core kernels report two conditions in the first 8 bytes of the workspace (see
-# include/hdla.h).  They are copied to pinned host memory right after the forward launch, without
-# blocking, and inspected the next time this module is entered on that device (or at once with
-# HDLA_STRICT=1, which synchronises): a problem never stays silent, and the hot path never waits.
+# The bf16 tensor-core kernels report in the first bytes of the workspace (see include/hdla.h):
+# word 0 a device-side wait that ran out, word 1 a chunk whose total log decay is beyond what the
+# pipeline represents, word 2 the largest chunk decay of the call.  After every launch the words are
+# copied to pinned host memory without blocking and inspected the next time this module is entered on
+# that device, so a problem never stays silent and the hot path never waits.
+#
+# A decay overflow is different from the other conditions: the call's results are wrong but the fp32
+# pipeline would have computed them correctly (the reference layer feeds undivided logsigmoid decays,
+# HRDPLR/hdla_custom.py:219, which can exceed the limit for fast-forgetting channels).  Forward
+# therefore WAITS for its own status words -- and reruns the call on the fp32 pipeline when word 1 is
+# set -- whenever an overflow is plausible: on the first call on a device, and from then on while the
+# largest chunk decay seen on that device is above half the limit.  Workloads far from the limit (all
+# benchmark configurations: <= 22 of 150) pay for one synchronisation in their first call only.
+# HDLA_STRICT=1 always waits; HDLA_ASYNC_STATUS=1 never does (an overflow then raises at the next entry).
 _RING = 64
-_status = {}      # device index -> dict(host=pinned [RING,2] int32, events=[...], next=int, pending=[slots])
+_DECAY_LIMIT = 150.0
+_status = {}      # device index -> dict(host=pinned [RING,4] int32, events=[...], next=int, pending=[slots], decay=float|None)
+_warned_fallback = False
 
 
 def _status_state(dev):
     st = _status.get(dev.index)
     if st is None:
-        st = dict(host=torch.zeros(_RING, 2, dtype=torch.int32).pin_memory(),
-                  events=[torch.cuda.Event() for _ in range(_RING)], next=0, pending=[])
+        st = dict(host=torch.zeros(_RING, 4, dtype=torch.int32).pin_memory(),
+                  events=[torch.cuda.Event() for _ in range(_RING)], next=0, pending=[], decay=None)
         _status[dev.index] = st
     return st
+
+
+def _note_decay(st, words) -> None:
+    seen = float(torch.tensor(int(words[2]), dtype=torch.int32).view(torch.float32))
+    if seen == seen:
+        st["decay"] = seen if st["decay"] is None else max(st["decay"], seen)
 
 
 def _raise_status(words):
@@ -114,6 +133,7 @@ def check_status(dev=None, wait: bool = False) -> None:
                 ev.synchronize()
             if ev.query():
                 words = st["host"][slot].tolist()
+                _note_decay(st, words)
                 if words[0] or words[1]:
                     st["pending"] = [s_ for s_ in st["pending"] if s_ != slot]
                     _raise_status(words)
@@ -122,18 +142,37 @@ def check_status(dev=None, wait: bool = False) -> None:
         st["pending"] = keep
 
 
-def _post_status(ws: torch.Tensor, dev) -> None:
+def _post_status(ws: torch.Tensor, dev) -> int:
+    """Enqueue the copy of the status words of the call that just used ``ws``; returns the ring slot."""
     st = _status_state(dev)
     slot = st["next"]
     st["next"] = (slot + 1) % _RING
     if slot in st["pending"]:                       # ring wrapped: that copy finished long ago
         st["events"][slot].synchronize()
         check_status(dev)
-    st["host"][slot].copy_(ws[:8].view(torch.int32), non_blocking=True)
+    st["host"][slot].copy_(ws[:16].view(torch.int32), non_blocking=True)
     st["events"][slot].record(torch.cuda.current_stream(dev))
     st["pending"].append(slot)
-    if os.environ.get("HDLA_STRICT", "0") == "1":
+    if os.environ.get("HDLA_STRICT", "0") == "1" and not torch.cuda.is_current_stream_capturing():
         check_status(dev, wait=True)
+    return slot
+
+
+def _overflow_plausible(dev) -> bool:
+    if os.environ.get("HDLA_ASYNC_STATUS", "0") == "1" or torch.cuda.is_current_stream_capturing():
+        return False
+    st = _status_state(dev)
+    return st["decay"] is None or st["decay"] > 0.5 * _DECAY_LIMIT or os.environ.get("HDLA_STRICT", "0") == "1"
+
+
+def _wait_words(dev, slot):
+    """Wait for the status copy in ``slot`` and take it off the pending list; returns its words."""
+    st = _status_state(dev)
+    st["events"][slot].synchronize()
+    words = st["host"][slot].tolist()
+    st["pending"] = [s_ for s_ in st["pending"] if s_ != slot]
+    _note_decay(st, words)
+    return words
 
 
 def _alloc_ws(nbytes: int, device) -> torch.Tensor:
@@ -146,16 +185,24 @@ def save_workspace_default() -> bool:
     return os.environ.get("HDLA_RECOMPUTE", "0") != "1"
 
 
-def chunk_hrdplr_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB, head_first,
-                     chunk_size, _keep_ws: bool = False):
-    """Forward stage sequence (reference: HRDPLR/hrdplr.py:25-99). Returns ``(o, final_state)``
-    (and the workspace tensor when ``_keep_ws``)."""
+def chunk_hrdplr_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB, head_first, chunk_size):
+    """Forward stage sequence (reference: HRDPLR/hrdplr.py:25-99). Returns ``(o, final_state)``."""
+    o, ht, _, _ = _chunk_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB, head_first,
+                             chunk_size)
+    return o, ht
+
+
+def _chunk_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB, head_first, chunk_size,
+               _keep_ws: bool = False, _force_simt: bool = False):
+    """``chunk_hrdplr_fwd`` returning ``(o, final_state, workspace, used_fp32_pipeline)``; with ``_keep_ws`` the
+    workspace is sized for, and keeps what, ``hdla_chunk_bwd(HDLA_FLAG_WS_HOLDS_FWD)`` needs."""
+    global _warned_fallback
     assert head_first is False, "head_first=True is not supported (as in the reference)"
     dev = _lib.require_cuda(q, k, v, a, b, gk, initial_state)
     _check_shapes(q, k, v, a, b, gk, RANK_AB, initial_state)
     check_status(dev)
     lib = _lib.load()
-    dims = _dims(q, v, a, gk, RANK_AB, chunk_size)
+    dims = _dims(q, v, a, gk, RANK_AB, chunk_size, _lib.FLAG_FORCE_SIMT if _force_simt else 0)
     B, T, H, K = q.shape
     V = v.shape[-1]
     h0 = None if initial_state is None else initial_state.to(torch.float32).contiguous()
@@ -166,13 +213,23 @@ def chunk_hrdplr_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state
         rc = lib.hdla_chunk_fwd(C.byref(dims), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(a), _lib.ptr(b),
                                 _lib.ptr(gk), float(scale), _lib.ptr(h0), _lib.ptr(o), _lib.ptr(ht),
                                 _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
-    _lib.check(rc, "hdla_chunk_fwd")
-    if lib.hdla_chunk_uses_tensor_cores(C.byref(dims)):
-        with torch.cuda.device(dev):
-            _post_status(ws, dev)
-    if _keep_ws:
-        return o, ht, ws
-    return o, ht
+        _lib.check(rc, "hdla_chunk_fwd")
+        if lib.hdla_chunk_uses_tensor_cores(C.byref(dims)):
+            slot = _post_status(ws, dev)
+            if _overflow_plausible(dev):
+                words = _wait_words(dev, slot)
+                if words[1] and not words[0]:
+                    if not _warned_fallback:
+                        _warned_fallback = True
+                        warnings.warn("hdla_impl_b200: a chunk's total log decay exceeds what the bf16 tensor-core "
+                                      "pipeline represents; such calls are rerun on the fp32 CUDA-core pipeline "
+                                      "(correct, much slower)", RuntimeWarning, stacklevel=3)
+                    del ws, o, ht
+                    return _chunk_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB,
+                                      head_first, chunk_size, _keep_ws=_keep_ws, _force_simt=True)
+                if words[0] or words[1]:
+                    _raise_status(words)
+    return o, ht, (ws if _keep_ws else None), _force_simt
 
 
 class ChunkDPLRDeltaRuleFunction(torch.autograd.Function):
@@ -185,11 +242,9 @@ class ChunkDPLRDeltaRuleFunction(torch.autograd.Function):
     def forward(ctx, q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB, head_first, chunk_size):
         keep = save_workspace_default() and any(
             isinstance(t, torch.Tensor) and t.requires_grad for t in (q, k, v, a, b, gk, initial_state))
-        res = chunk_hrdplr_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB, head_first,
-                               chunk_size, _keep_ws=keep)
-        o, final_state = res[0], res[1]
+        o, final_state, ctx.ws, ctx.force_simt = _chunk_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state,
+                                                            RANK_AB, head_first, chunk_size, _keep_ws=keep)
         ctx.save_for_backward(q, k, v, a, b, gk, initial_state)
-        ctx.ws = res[2] if keep else None
         ctx.head_first = head_first
         ctx.scale = scale
         ctx.chunk_size = chunk_size
@@ -208,6 +263,8 @@ class ChunkDPLRDeltaRuleFunction(torch.autograd.Function):
         ws = ctx.ws
         ctx.ws = None
         flags = _lib.FLAG_WS_HOLDS_FWD if ws is not None else 0
+        if ctx.force_simt:                          # forward had to fall back to the fp32 pipeline: so does backward
+            flags |= _lib.FLAG_FORCE_SIMT
         dims = _dims(q, v, a, gk, ctx.RANK_AB, ctx.chunk_size, flags)
         h0 = None if initial_state is None else initial_state.to(torch.float32).contiguous()
         if do.dtype != q.dtype:
@@ -224,7 +281,9 @@ class ChunkDPLRDeltaRuleFunction(torch.autograd.Function):
                                     _lib.ptr(gk), float(ctx.scale), _lib.ptr(h0), _lib.ptr(do), _lib.ptr(dht),
                                     _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(da), _lib.ptr(db),
                                     _lib.ptr(dgk), _lib.ptr(dh0), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
-        _lib.check(rc, "hdla_chunk_bwd")
+            _lib.check(rc, "hdla_chunk_bwd")
+            if lib.hdla_chunk_uses_tensor_cores(C.byref(dims)):
+                _post_status(ws, dev)                # waits that ran out in the backward kernels surface too
         if dh0 is not None and initial_state.dtype != torch.float32:
             dh0 = dh0.to(initial_state.dtype)
         return dq, dk, dv, da, db, dgk, None, dh0, None, None, None, None

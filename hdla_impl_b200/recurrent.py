@@ -20,13 +20,14 @@ def fused_recurrent_dplr_delta_rule_fwd(q, k, v, a, b, gk, rank_ab, scale=1.0, i
     """Reference: HRDPLR/recurrent.py:121-177. ``inplace_state`` writes the final state over
     ``initial_state`` (an fp32 tensor) instead of allocating a new one."""
     B, TR, H, K = a.shape
-    T = TR // rank_ab
-    assert TR == T * rank_ab, f"Merged dimension TR={TR} must be divisible by rank_ab={rank_ab}"
-    assert b.shape == (B, TR, H, K), f"b shape {b.shape} doesn't match a shape {a.shape}"
-    assert k.shape == (B, T, H, K), f"k shape {k.shape} should be (B, T, H, K)"
-    assert v.shape == (B, T, H, v.shape[-1]), f"v shape {v.shape} should be (B, T, H, V)"
-    assert q.shape == (B, T, H, K), f"q shape {q.shape} should be (B, T, H, K)"
-    assert gk.shape == (B, T, H, K), f"gk shape {gk.shape} should be (B, T, H, K)"
+    T = _tokens_of_merged(TR, rank_ab)
+    # same conditions and messages as the reference's wrapper (HRDPLR/recurrent.py:136-145)
+    for name, t, want, text in (("b", b, (B, TR, H, K), f"doesn't match a shape {a.shape}"),
+                                ("k", k, (B, T, H, K), "should be (B, T, H, K)"),
+                                ("v", v, (B, T, H, v.shape[-1]), "should be (B, T, H, V)"),
+                                ("q", q, (B, T, H, K), "should be (B, T, H, K)"),
+                                ("gk", gk, (B, T, H, K), "should be (B, T, H, K)")):
+        assert t.shape == want, f"{name} shape {t.shape} {text}"
     dev = _lib.require_cuda(q, k, v, a, b, gk, initial_state, cu_seqlens)
     if not (q.dtype == k.dtype == v.dtype == a.dtype == b.dtype):
         raise TypeError("q, k, v, a, b must share one dtype")
@@ -49,8 +50,64 @@ def fused_recurrent_dplr_delta_rule_fwd(q, k, v, a, b, gk, rank_ab, scale=1.0, i
         rc = lib.hdla_recurrent_fwd(C.byref(dims), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(a), _lib.ptr(b),
                                     _lib.ptr(gk), float(scale), _lib.ptr(h0), _lib.ptr(o), _lib.ptr(ht),
                                     _lib.ptr(cu), N, int(bool(reverse)), _lib.stream_ptr(dev))
-    _lib.check(rc, "hdla_recurrent_fwd")
+        _lib.check(rc, "hdla_recurrent_fwd")
+        _poll_status(lib, dev)
     return o, ht
+
+
+def _tokens_of_merged(TR: int, rank_ab: int) -> int:
+    T = TR // rank_ab
+    assert TR == T * rank_ab, f"Merged dimension TR={TR} must be divisible by rank_ab={rank_ab}"
+    return T
+
+
+# The decode kernel stages the state tile with an asynchronous copy and waits for it with a time limit; if
+# that wait ever ran out it says so in a device word (hdla_recurrent_read_status).  Decode steps are short,
+# so the word is fetched (without blocking) only every _POLL_EVERY calls and looked at when the copy has
+# landed; check_recurrent_status(wait=True) fetches and inspects it at once.
+_POLL_EVERY = 256
+_poll = {}        # device index -> dict(calls=int, host=pinned int32[1], event=Event|None)
+
+
+def _poll_state(dev):
+    st = _poll.get(dev.index)
+    if st is None:
+        st = dict(calls=0, host=torch.zeros(1, dtype=torch.int32).pin_memory(), event=None)
+        _poll[dev.index] = st
+    return st
+
+
+def _poll_status(lib, dev) -> None:
+    st = _poll_state(dev)
+    if st["event"] is not None and st["event"].query():
+        st["event"] = None
+        if int(st["host"][0]):
+            raise RuntimeError("libhdla: a device-side wait ran out in the decode kernel; the results of that call "
+                               "are invalid and its final state was not written")
+    st["calls"] += 1
+    if st["calls"] % _POLL_EVERY == 0 and st["event"] is None and not torch.cuda.is_current_stream_capturing():
+        _lib.check(lib.hdla_recurrent_read_status(_lib.ptr(st["host"]), _lib.stream_ptr(dev)),
+                   "hdla_recurrent_read_status")
+        st["event"] = torch.cuda.Event()
+        st["event"].record(torch.cuda.current_stream(dev))
+
+
+def check_recurrent_status(dev, wait: bool = True) -> None:
+    """Fetch the decode kernel's status word for ``dev`` now and raise if a wait ever ran out there."""
+    dev = torch.device(dev)
+    lib = _lib.load()
+    st = _poll_state(dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.hdla_recurrent_read_status(_lib.ptr(st["host"]), _lib.stream_ptr(dev)),
+                   "hdla_recurrent_read_status")
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(dev))
+    st["event"] = ev
+    if wait:
+        ev.synchronize()
+        st["event"] = None
+        if int(st["host"][0]):
+            raise RuntimeError("libhdla: a device-side wait ran out in the decode kernel")
 
 
 class FusedRecurrentDPLRDeltaRuleFunction(torch.autograd.Function):
@@ -102,13 +159,10 @@ def fused_recurrent_dplr_delta_rule(
             raise ValueError(
                 f"The number of initial states is expected to be equal to the number of input sequences, "
                 f"i.e., {len(cu_seqlens) - 1} rather than {initial_state.shape[0]}.")
-    if len(a.shape) != 4:
-        raise ValueError(f"a must have 4 dimensions [B, T*RANK_AB, H, K], got {len(a.shape)}")
-    if len(b.shape) != 4:
-        raise ValueError(f"b must have 4 dimensions [B, T*RANK_AB, H, K], got {len(b.shape)}")
-    B, TR, _, _ = a.shape
-    T_expected = TR // rank_ab
-    assert TR == T_expected * rank_ab, f"Merged dimension TR={TR} must be divisible by rank_ab={rank_ab}"
+    for name, t in (("a", a), ("b", b)):
+        if t.dim() != 4:
+            raise ValueError(f"{name} must have 4 dimensions [B, T*RANK_AB, H, K], got {t.dim()}")
+    T_expected = _tokens_of_merged(a.shape[1], rank_ab)
     assert q.shape[1] == T_expected, f"q time dimension {q.shape[1]} must match T={T_expected} from merged dimension"
     if scale is None:
         scale = q.shape[-1] ** -0.5

@@ -94,18 +94,6 @@ HDLA_API int hdla_version(void);
  * the same thread's next failing call. */
 HDLA_API const char* hdla_last_error(void);
 
-/* Number of kernels this library has launched in the calling process so far (all threads).
- * Instrumentation for benchmarks; it has no counterpart in the reference, whose launches are
- * issued by the Triton runtime. */
-HDLA_API unsigned long long hdla_kernel_launches(void);
-
-/* Per-kernel timing for benchmarks (no counterpart in the reference).  While enabled, every call
- * records a CUDA event on its stream at entry and after each kernel launch.  hdla_timing_report()
- * WAITS for those events, writes one line "kernel_name launches total_ms" per kernel into buf (at most
- * size-1 characters, NUL terminated), forgets the events and returns the length of the full report. */
-HDLA_API void hdla_timing_enable(int on);
-HDLA_API size_t hdla_timing_report(char* buf, size_t size);
-
 /* Bytes of device workspace hdla_chunk_fwd (with_backward = 0) or the pair hdla_chunk_fwd +
  * hdla_chunk_bwd (with_backward = 1) needs for these dims; 0 if the dims are unsupported (see
  * hdla_last_error).  Replaces the torch.empty(...) intermediates the reference's stage
@@ -117,18 +105,16 @@ HDLA_API size_t hdla_chunk_workspace_bytes(const HdlaDims* dims, int with_backwa
  * words described below), 0 if on the fp32 CUDA-core pipeline.  No counterpart in the reference. */
 HDLA_API int hdla_chunk_uses_tensor_cores(const HdlaDims* dims);
 
-/* Debugging aid for tests: converts one named bf16 tile buffer of the tensor-core workspace
- * ("Qh","Kh","Ah","Bh","Vc","Aqk","Aqb","Aak","Aab","M","W","P","U","Hs","V2") to fp32 row-major
- * [B*H*NT][rows][cols] in `out` (device memory), or copies "E" / the 4-byte "status" word.  It has no
- * counterpart in the reference, whose intermediates are ordinary torch tensors. */
-HDLA_API int hdla_debug_tc_buffer(const HdlaDims* dims, const void* workspace, const char* name, float* out,
-                                  void* cuda_stream);
-
-/* The first 8 bytes of a workspace used by the bf16 tensor-core pipeline are two int32 status words
- * written by the kernels: word 0 is non-zero if a bounded device-side wait ran out (results invalid),
- * word 1 is non-zero if some chunk's total log decay |sum_chunk gk| exceeded 150 in some channel, which
- * the bf16 pipeline cannot represent (results invalid; rerun with HDLA_FLAG_FORCE_SIMT, whose fp32
- * pipeline has no such limit).  Callers read them after the stream has finished the call. */
+/* The first 12 bytes of a workspace used by the bf16 tensor-core pipeline are three int32 status words
+ * written by the kernels:
+ *   word 0  non-zero if a bounded device-side wait ran out (results invalid); the value names the wait
+ *   word 1  non-zero if some chunk's total log decay |sum_chunk gk| exceeded 150 in some channel, which the
+ *           bf16 pipeline cannot represent (results invalid; rerun with HDLA_FLAG_FORCE_SIMT, whose fp32
+ *           pipeline has no such limit)
+ *   word 2  the largest |sum_chunk gk| over all chunks and channels of the call, as the bit pattern of a float
+ * Callers read them after the stream has finished the call (hdla_chunk_fwd_noalloc, which has no caller
+ * workspace: hdla_noalloc_read_status).  Every device-side wait is bounded in time (2 s on the GPU's
+ * nanosecond timer), so a kernel always returns. */
 
 /* Chunked forward.  Replaces chunk_hrdplr_fwd (HRDPLR/hrdplr.py:25-99), i.e. the stage
  * sequence cumsum -> intra-chunk A matrices -> (I-Aab)^-1 and w/u -> state scan -> output.
@@ -152,8 +138,12 @@ HDLA_API int hdla_chunk_fwd(const HdlaDims* dims,
  * whose wrappers allocate their intermediates with torch.empty.
  *   - Problems whose workspace (hdla_chunk_workspace_bytes(dims, 0)) exceeds the built-in scratch are
  *     rejected with HDLA_ERR_WORKSPACE and an explanatory hdla_last_error().
- *   - The first call on each device resolves the array's device address; make that first call with
- *     the device current and before starting any stream capture.
+ *   - The first call on each device resolves the array's device address, which also makes the CUDA runtime load
+ *     this library's device code on that device and reserve the array there (it may synchronise the device or
+ *     fail if the device has no room left); make that first call with the device current, before starting any
+ *     stream capture and before the no-allocation regime begins.  Later calls allocate nothing.
+ *   - The status words described above live in the array's first bytes; hdla_noalloc_read_status() copies them
+ *     out.
  *   - All calls on a device share the one array, which keeps the previous call's contents: calls whose
  *     GPU work can overlap (different streams, different threads) race with each other.  Issue them
  *     on one stream, or order them yourself. */
@@ -162,6 +152,11 @@ HDLA_API int hdla_chunk_fwd_noalloc(const HdlaDims* dims,
                    const void* q, const void* k, const void* v, const void* a, const void* b,
                    const void* gk, float scale, const float* h0,
                    void* o, float* ht, void* cuda_stream);
+
+/* Enqueues on the stream a copy of the three status words that the most recent hdla_chunk_fwd_noalloc call on
+ * the current device left in the built-in scratch to dst (3 x int32; device memory or pinned host memory).
+ * Allocates nothing.  Like hdla_chunk_fwd_noalloc it has no counterpart in the reference. */
+HDLA_API int hdla_noalloc_read_status(int32_t* dst, void* cuda_stream);
 
 /* Chunked backward.  Replaces ChunkDPLRDeltaRuleFunction.backward (HRDPLR/hrdplr.py:146-284):
  * stages dAu, dhu (reverse state scan), dv, bwd_o, wy, intra and dgk.
@@ -193,6 +188,27 @@ HDLA_API int hdla_recurrent_fwd(const HdlaDims* dims,
                        void* o, float* ht,
                        const int64_t* cu_seqlens, int32_t n_seqs, int32_t reverse,
                        void* cuda_stream);
+
+/* Enqueues a copy of the decode kernel's status word to dst (1 x int32; device or pinned host memory): non-zero
+ * once a bounded wait for a state tile ran out in some hdla_recurrent_fwd call of this process on the current
+ * device (that call's outputs are invalid and its final state was not written).  No counterpart in the
+ * reference, whose kernel has no asynchronous copies to wait for. */
+HDLA_API int hdla_recurrent_read_status(int32_t* dst, void* cuda_stream);
+
+/* Composition of affine state maps, for callers that cut a sequence over devices (context parallelism; the
+ * reference has no counterpart, its scan HRDPLR/fwd_triton.py:853-956 is serial over the whole sequence).
+ * The state leaving a slice is affine in the state entering it, S_out = T S_in + F (T from
+ * HDLA_PHASE_TRANSITION, F from HDLA_PHASE_STATE).  With the maps of `count` consecutive slices gathered in
+ * local memory this computes, per (batch, head) pair bh and in fp32,
+ *     forward (reverse = 0):  X = S0;  for s = 0 .. count-1:      X = T_s (X + pre_s) + F_s
+ *     reverse (reverse = 1):  X = S0;  for s = count-1 .. 0:      X = T_s^T (X + pre_s) + F_s
+ *     out = X + post
+ * T_s of pair bh is the K x K matrix at T + (s * t_stride + bh) * K*K, F_s and pre_s the K x V matrices at
+ * F / pre + (s * f_stride + bh) * K*V; S0, post, out are [B*H, K, V].  S0, pre, post may be NULL (zero);
+ * count may be 0 (out = S0 + post).  dims gives B, H, K, V; only K = V = 128 is supported. */
+HDLA_API int hdla_compose_states(const HdlaDims* dims, const float* T, const float* F, const float* S0,
+                                 const float* pre, const float* post, float* out, int32_t count,
+                                 int64_t t_stride, int64_t f_stride, int32_t reverse, void* cuda_stream);
 
 /* a/b parametrisation of the HDLA layer, forward and backward.  Replaces parameterize_a_b
  * (HRDPLR/hdla_custom.py:19-43; as shipped that function builds a and b but has no return statement):

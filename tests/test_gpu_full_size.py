@@ -53,6 +53,31 @@ def test_cfg1_full_size_slice_against_oracle():
         assert orc.rel_err(a_, b_[:2]) < 5e-3
 
 
+def test_cfg3_full_size_slice_against_oracle():
+    """B1 T65536 H16 K=V=128 bf16 chunk 64 on one GPU (1024 chunks per head, scanned as concurrent segments whose
+    affine maps are composed in fp32): head 9 -- o, the final state and every gradient, the final state's
+    gradient included -- against the fp64 oracle run on that head alone, within 2e-2."""
+    import hdla_impl_b200 as H
+    dev = torch.device("cuda:0")
+    B, T, Hh, K, V = 1, 65536, 16, 128, 128
+    x = make_inputs(B, T, Hh, K, V, R, seed=3, dtype=torch.bfloat16, with_dht=True)
+    lv = [x[n].to(dev).requires_grad_(True) for n in NAMES]
+    o, ht = H.chunk_hrdplr_delta_rule(*lv, R, chunk_size=64, output_final_state=True)
+    grads = torch.autograd.grad([o, ht], lv, [x["do"].to(dev), x["dht"].to(dev)])
+    H.check_status(dev, wait=True)
+    h = 9
+    sl = lambda t: t[:, :, h:h + 1].double()
+    st = orc.staged_forward(*[sl(x[n]) for n in NAMES], R, K ** -0.5, None, 64)
+    g = orc.staged_backward(st, sl(x["do"]), x["dht"][:, h:h + 1].double())
+    bad = []
+    for name, got, ref in [("o", o[:, :, h:h + 1], st["o_bthv"]), ("ht", ht[:, h:h + 1], st["ht"])] + \
+            [(n, t[:, :, h:h + 1], g[n]) for n, t in zip(("dq", "dk", "dv", "da", "db", "dgk"), grads)]:
+        e = orc.rel_err(got, ref)
+        if not e < 2e-2:
+            bad.append(f"{name}: {e:.3e}")
+    assert not bad, "; ".join(bad)
+
+
 def test_cfg2_full_size_decode_against_oracle():
     """256 sequences x 32 heads, K=V=128, bf16 tokens, fp32 state N(0, 0.02): 4 decode steps on the GPU;
     sequences 0 and 200 against the fp64 recurrence."""

@@ -26,7 +26,7 @@ def _dump(ws, dims, name, shape, dev):
     return out.cpu().double()
 
 
-@pytest.mark.parametrize("T,gk_div,h0_std", [(256, 16.0, None), (200, 2.0, 0.5)])
+@pytest.mark.parametrize("T,gk_div,h0_std", [(256, 16.0, None), (200, 2.0, 0.5), (320, 1.0, 0.5)])
 def test_tc_forward_stages(T, gk_div, h0_std):
     from hdla_impl_b200 import _lib, hrdplr
     dev = torch.device("cuda:0")
@@ -37,7 +37,7 @@ def test_tc_forward_stages(T, gk_div, h0_std):
     args = [x[n].to(dev) for n in names]
     scale = K ** -0.5
     h0 = None if h0_std is None else x["h0"].to(dev)
-    o, ht, ws = hrdplr.chunk_hrdplr_fwd(*args, scale, h0, True, R, False, Cc, _keep_ws=True)
+    o, ht, ws, _ = hrdplr._chunk_fwd(*args, scale, h0, True, R, False, Cc, _keep_ws=True)
     torch.cuda.synchronize()
     dims = hrdplr._dims(args[0], args[2], args[3], args[5], R, Cc)
     st = orc.staged_forward(*[x[n].double() for n in names], R, scale, None if h0_std is None else x["h0"], Cc)
@@ -53,13 +53,14 @@ def test_tc_forward_stages(T, gk_div, h0_std):
         "Bh": (st["b"] * torch.exp(half - rep(st["gi"])), (128, 128)),
         "Vc": (st["v"], (64, 128)),
         "Aqk": (st["Aqk"], (64, 64)), "Aqb": (st["Aqb"], (64, 128)), "Aak": (st["Aak"], (128, 64)),
-        "Aab": (st["Aab"], (128, 128)), "M": (st["M"], (128, 128)),
+        "M": (st["M"], (128, 128)),                      # Aab itself never leaves the SM: M = (I - Aab)^-1 covers it
         "P": (st["Aak"] @ st["v"], (128, 128)), "U": (st["u"], (128, 128)),
         "W": (st["w"] / E, (128, 128)),
         "Hs": (st["h"] * E.transpose(-1, -2), (128, 128)),
         "V2": (st["v2"], (128, 128)),
     }
-    status = _dump(ws, dims, "status", (1,), dev).float().view(torch.int32) if False else None
+    status = ws[:8].view(torch.int32).tolist()
+    assert status == [0, 0], f"status words {status}"
     bad = []
     for n, (ref, shp) in want.items():
         got = _dump(ws, dims, n, (G,) + shp, dev).view(B, H, NT, *shp)
@@ -87,7 +88,7 @@ def test_tc_backward_stages():
     args = [x[n].to(dev) for n in names]
     scale = K ** -0.5
     h0 = x["h0"].to(dev)
-    o, ht, ws = hrdplr.chunk_hrdplr_fwd(*args, scale, h0, True, R, False, Cc, _keep_ws=True)
+    o, ht, ws, _ = hrdplr._chunk_fwd(*args, scale, h0, True, R, False, Cc, _keep_ws=True)
     lib = _lib.load()
     dims = hrdplr._dims(args[0], args[2], args[3], args[5], R, Cc, _lib.FLAG_WS_HOLDS_FWD)
     do = x["do"].to(dev)

@@ -14,8 +14,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_library_exports_every_declared_symbol():
     hdr = open(os.path.join(ROOT, "include", "hdla.h")).read()
-    declared = set(re.findall(r"HDLA_API[^;(]*?\b(hdla_\w+)\s*\(", hdr))
-    assert declared, "no declarations found in include/hdla.h"
+    declared = set()
+    for name in ("hdla.h", "hdla_debug.h"):            # the operator's C ABI and the instrumentation / test hooks
+        found = set(re.findall(r"HDLA_API[^;(]*?\b(hdla_\w+)\s*\(", open(os.path.join(ROOT, "include", name)).read()))
+        assert found, f"no declarations found in include/{name}"
+        declared |= found
     lib = _lib.load()
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in hdla.h but not exported"

@@ -125,3 +125,41 @@ def test_batch_head_shards_reassemble(world):
     out = mgr.dict()
     mp.spawn(_bh_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert out["err"] < 1e-12
+
+
+def _peer_loss_worker(rank, world, port, out):
+    """Rank 1 leaves right after the rendezvous, between steps and with nothing in flight; the others run one
+    context-parallel forward + backward and must get an error from their send/recv, not a hang."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    if rank == 1:
+        out[rank] = "left"
+        os._exit(0)                                   # no destroy_process_group: the peer is simply gone
+    from hdla_impl_b200.context_parallel import cp_chunk_hrdplr_delta_rule
+    from hdla_impl_b200.synthetic import make_inputs
+    torch.set_num_threads(1)
+    T, C = 96, 16
+    x = make_inputs(1, T, 1, 16, 16, R, seed=5, gk_div=4.0)
+    lo, hi = shard_time(T, rank, world, C)
+    sl = lambda n, r=1: x[n][:, lo * r:hi * r].double().requires_grad_(True)
+    lv = [sl("q"), sl("k"), sl("v"), sl("a", R), sl("b", R), sl("gk")]
+    try:
+        o, _ = cp_chunk_hrdplr_delta_rule(*lv, R, scale=0.3, chunk_size=C, op=_oracle_op)
+        torch.autograd.grad(o.sum(), lv)
+        out[rank] = "completed"
+    except Exception as e:                            # gloo reports a closed connection or a timed-out recv
+        out[rank] = f"error: {type(e).__name__}: {str(e)[:200]}"
+    os._exit(0)                                       # a clean shutdown handshake with a missing peer would block
+
+
+@pytest.mark.timeout(180)
+def test_context_parallel_peer_loss_is_an_error_not_a_hang():
+    world = 3
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_peer_loss_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert out[1] == "left"
+    # rank 2 waits for a state that never comes; rank 0's send or its backward recv meets the closed peer
+    assert out[2].startswith("error"), dict(out)
+    assert out[0].startswith("error"), dict(out)

@@ -105,3 +105,21 @@ def test_reverse_and_varlen_recurrence():
     of, hf = orc.recurrent_ref(x["q"].flip(1), x["k"].flip(1), x["v"].flip(1), flip2(x["a"]), flip2(x["b"]),
                                x["gk"].flip(1), R, None, None)
     assert orc.rel_err(orv, of.flip(1)) < 1e-13 and orc.rel_err(hrv, hf) < 1e-13
+
+
+def test_installed_reference_matches_oracle():
+    """Where oracle/install_ref.py has placed the reference's own naive.py, it and the restatement agree on
+    forward and autograd gradients (fp64, seeded inputs); skipped where the reference is not installed."""
+    import pytest
+    from oracle import ref_naive
+    if not ref_naive.available():
+        pytest.skip("oracle/_ref/naive.py is not installed")
+    from hdla_impl_b200.synthetic import make_inputs
+    x = make_inputs(1, 128, 2, 32, 32, 2, seed=11, gk_div=2.0)
+    o, ht, grads = ref_naive.fwd_bwd(x, 2, 32, dtype=torch.float64)
+    f = lambda n: x[n].double()
+    st = orc.staged_forward(f("q"), f("k"), f("v"), f("a"), f("b"), f("gk"), 2, 1.0, None, 32)
+    g = orc.staged_backward(st, f("do"), None)
+    assert orc.rel_err(o, st["o_bthv"]) < 1e-10 and orc.rel_err(ht, st["ht"]) < 1e-10
+    for t, n in zip(grads, ("dq", "dk", "dv", "da", "db", "dgk")):
+        assert orc.rel_err(t, g[n]) < 1e-10, n
