@@ -43,20 +43,30 @@ struct ChunkPrepP {
 
 struct In6 { uint4 q, k, a0, a1, b0, b1; };
 
+// 16-byte read-only load that stays where it is written: the loads of the streaming part are issued long before
+// their use on purpose (a whole tile phase ahead), and an ordinary load may be moved down to its use.
+__device__ __forceinline__ uint4 ld_pinned(const void* ptr) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(ptr) : "memory");
+    return r;
+}
+
+// The six operand pieces of (row, column group cg).  Unconditional: a row beyond the sequence's end is read from
+// the last row that exists and zeroed when it is used (a conditional load would tie the data to a register move at
+// the point of the condition and so bring the wait for the data forward to there).
 __device__ __forceinline__ In6 load6(const ChunkPrepP& p, int b, int h, int t0, int valid, int row, int cg) {
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    In6 x{zero, zero, zero, zero, zero, zero};
-    if (row < valid) {
-        const size_t src = (((size_t)b * p.T + t0 + row) * p.H + h) * K + cg * 8;
-        const size_t sa0 = (((size_t)b * p.T * R + (size_t)(t0 + row) * R) * p.H + h) * K + cg * 8;
-        const size_t sa1 = sa0 + (size_t)p.H * K;
-        x.q = __ldg(reinterpret_cast<const uint4*>(p.q + src));
-        x.k = __ldg(reinterpret_cast<const uint4*>(p.k + src));
-        x.a0 = __ldg(reinterpret_cast<const uint4*>(p.a + sa0));
-        x.a1 = __ldg(reinterpret_cast<const uint4*>(p.a + sa1));
-        x.b0 = __ldg(reinterpret_cast<const uint4*>(p.b + sa0));
-        x.b1 = __ldg(reinterpret_cast<const uint4*>(p.b + sa1));
-    }
+    const int rr = min(row, valid - 1);
+    const size_t src = (((size_t)b * p.T + t0 + rr) * p.H + h) * K + cg * 8;
+    const size_t sa0 = (((size_t)b * p.T * R + (size_t)(t0 + rr) * R) * p.H + h) * K + cg * 8;
+    const size_t sa1 = sa0 + (size_t)p.H * K;
+    In6 x;
+    x.q = ld_pinned(p.q + src);
+    x.k = ld_pinned(p.k + src);
+    x.a0 = ld_pinned(p.a + sa0);
+    x.a1 = ld_pinned(p.a + sa1);
+    x.b0 = ld_pinned(p.b + sa0);
+    x.b1 = ld_pinned(p.b + sa1);
     return x;
 }
 
@@ -73,9 +83,95 @@ __device__ __forceinline__ float c8_elem(const uint4* tile, int rows, int r, int
     return __bfloat162float(p[c & 7]);
 }
 
+// 32 accumulator columns [col0, col0 + 32) of this thread's row -> four bf16 chunks, keep(column) says which
+// entries survive the mask; emit(chunk number within the 32 columns, chunk).  32 columns at a time keep the
+// epilogues' register footprint small next to the requests held for the next tile.
+template <typename Keep, typename Emit>
+__device__ __forceinline__ void epilogue32(uint32_t taddr, int col0, Keep keep, Emit emit) {
+    uint32_t a[32];
+    tmem_ld_x32(taddr, a);
+    tmem_wait_ld();
+#pragma unroll
+    for (int c8 = 0; c8 < 4; ++c8) {
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = keep(col0 + c8 * 8 + j) ? __uint_as_float(a[c8 * 8 + j]) : 0.f;
+        emit(c8, t8::pack8(f));
+    }
+}
+
 constexpr int kPrepSmem = 16384 + 16384 + 32768 + 32768 + 16384;      // 112 KB
 
-__global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p) {
+// 16-byte asynchronous copy global -> shared without a register stage; with ok == false nothing is read and the
+// destination is filled with zeros.
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src, bool ok) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                 ::"r"(smem_u32(dst_smem)), "l"(src), "r"(ok ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Raw gk pieces of one thread: rows r8 + 8 j, j = 0..7, of its column group (8 channels each).
+template <bool GK32> struct GkRaw { uint4 r[GK32 ? 16 : 8]; };
+
+// What a thread requests ahead of a tile: its gk pieces and the operand pieces of the first four row blocks.
+template <bool GK32> struct TileHead { GkRaw<GK32> gk; In6 in[4]; };
+
+struct TileCoord { int b, h, t0, valid; };
+
+__device__ __forceinline__ TileCoord tile_coord(const ChunkPrepP& p, long long g) {
+    const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
+    TileCoord c;
+    c.b = bh / p.H; c.h = bh % p.H; c.t0 = n * C; c.valid = min(C, p.T - c.t0);
+    return c;
+}
+
+// The requests are issued in small batches at several points of the preceding tile's tensor-core phases: the SM
+// tracks a limited number of outstanding loads, and a burst of all of them at once holds up every later memory
+// instruction of the warp (the epilogues' stores among them) until the burst has drained.
+template <bool GK32>
+__device__ __forceinline__ void load_head_gk(TileHead<GK32>& hd, const ChunkPrepP& p, const TileCoord& tc, int r8, int cg) {
+    const size_t rstride = (size_t)p.H * K;
+    const size_t e0 = (((size_t)tc.b * p.T + tc.t0 + r8) * p.H + tc.h) * K + cg * 8;
+    if (GK32) {
+        const float* src = static_cast<const float*>(p.gk) + e0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const long long off = (long long)(min(8 * j + r8, tc.valid - 1) - r8) * (long long)rstride;
+            hd.gk.r[GK32 ? 2 * j : 0] = ld_pinned(src + off);
+            hd.gk.r[GK32 ? 2 * j + 1 : 0] = ld_pinned(src + off + 4);
+        }
+    } else {
+        const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.gk) + e0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            hd.gk.r[GK32 ? 0 : j] = ld_pinned(src + (long long)(min(8 * j + r8, tc.valid - 1) - r8) * (long long)rstride);
+    }
+}
+
+template <bool GK32>
+__device__ __forceinline__ void load_head_in(TileHead<GK32>& hd, const ChunkPrepP& p, const TileCoord& tc, int r8, int cg,
+                                             int j) {
+    hd.in[j] = load6(p, tc.b, tc.h, tc.t0, tc.valid, 8 * j + r8, cg);
+}
+
+// v rows of a tile -> the v slot in shared memory, by asynchronous copies (no registers held meanwhile)
+__device__ __forceinline__ void request_v(const ChunkPrepP& p, const TileCoord& tc, uint4* sV, int r8, int cg) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int row = 8 * j + r8;
+        const bool ok = row < tc.valid;
+        const size_t src = (((size_t)tc.b * p.T + tc.t0 + (ok ? row : 0)) * p.H + tc.h) * V + cg * 8;
+        cp_async16(sV + cg * 64 + row, p.v + src, ok);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// Persistent: the grid is two CTAs per SM and every CTA walks over the tiles g = blockIdx.x, blockIdx.x +
+// gridDim.x, ...  While a tile's products, inverse and epilogues run, the thread already holds the requests for the
+// NEXT tile's gk and first operand pieces in registers and the next tile's v is on its way to shared memory, so
+// the load latency of a tile lies under the tensor-core phases of the tile before it.
+template <bool GK32>
+__global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p, long long G) {
     // (un-swizzled operand tiles and bulk copies need 16-byte alignment only; a small alignment keeps the static
     //  part of the allocation small enough for two CTAs per SM)
     extern __shared__ __align__(128) unsigned char smem[];
@@ -87,52 +183,50 @@ __global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p) {
     uint4* sP = sQ;
     __shared__ __align__(8) uint64_t mma_bar;
     __shared__ uint32_t tmem_s;
-    const long long g = blockIdx.x;
-    const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
-    const int b = bh / p.H, h = bh % p.H;
-    const int t0 = n * C;
-    const int valid = min(C, p.T - t0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r8 = lane & 7, cg = warp * 4 + (lane >> 3);
     const unsigned full = 0xffffffffu;
     if (warp == 0) { tmem_alloc(&tmem_s, 256); tmem_relinquish(); }
     if (tid == 0) { mbar_init(&mma_bar, 1); fence_mbar_init(); }
-
-    // ---- the operand pieces of the first four row blocks are requested before anything else: they do not
-    //      depend on the decay sums, and four blocks in flight per thread keep the SM's share of HBM busy
-    In6 in[4];
+    long long g = blockIdx.x;
+    TileCoord tc = tile_coord(p, g);
+    TileHead<GK32> head;
+    load_head_gk<GK32>(head, p, tc, r8, cg);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) in[j] = load6(p, b, h, t0, valid, 8 * j + r8, cg);
+    for (int j = 0; j < 4; ++j) load_head_in<GK32>(head, p, tc, r8, cg, j);
+    request_v(p, tc, sV, r8, cg);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_s;
+    uint32_t phase = 0;
+#pragma unroll 1
+    for (; g < G; g += gridDim.x) {
+    const long long gn = g + gridDim.x;
+    const bool more = gn < G;
+    const int b = tc.b, h = tc.h, t0 = tc.t0, valid = tc.valid;
+    if (tid == 0) TL(0);
 
     // ---- chunk-local cumulative sum of gk (inclusive), in registers
     float gi[8][8];
-    {
-        const size_t rstride = (size_t)p.H * K;
-        const size_t e0 = (((size_t)b * p.T + t0 + r8) * p.H + h) * K + cg * 8;
-        if (p.gdt == HDLA_F32) {
-            const float* src = static_cast<const float*>(p.gk) + e0;
-            float4 lo[8], hi[8];
+    if (GK32) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const bool ok = 8 * j + r8 < valid;
-                lo[j] = ok ? __ldg(reinterpret_cast<const float4*>(src + (size_t)(8 * j) * rstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
-                hi[j] = ok ? __ldg(reinterpret_cast<const float4*>(src + (size_t)(8 * j) * rstride + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                gi[j][0] = lo[j].x; gi[j][1] = lo[j].y; gi[j][2] = lo[j].z; gi[j][3] = lo[j].w;
-                gi[j][4] = hi[j].x; gi[j][5] = hi[j].y; gi[j][6] = hi[j].z; gi[j][7] = hi[j].w;
-            }
-        } else {
-            const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.gk) + e0;
-            uint4 raw[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                raw[j] = 8 * j + r8 < valid ? __ldg(reinterpret_cast<const uint4*>(src + (size_t)(8 * j) * rstride))
-                                            : make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) t8::unpack8(raw[j], gi[j]);
+        for (int j = 0; j < 8; ++j) {
+            const uint4 lo = head.gk.r[GK32 ? 2 * j : 0], hi = head.gk.r[GK32 ? 2 * j + 1 : 0];
+            gi[j][0] = __uint_as_float(lo.x); gi[j][1] = __uint_as_float(lo.y); gi[j][2] = __uint_as_float(lo.z); gi[j][3] = __uint_as_float(lo.w);
+            gi[j][4] = __uint_as_float(hi.x); gi[j][5] = __uint_as_float(hi.y); gi[j][6] = __uint_as_float(hi.z); gi[j][7] = __uint_as_float(hi.w);
         }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t8::unpack8(head.gk.r[GK32 ? 0 : j], gi[j]);
+    }
+    if (valid < C) {                                           // ragged last chunk: rows beyond the end decay by nothing
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (8 * j + r8 >= valid) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) gi[j][c] = 0.f;
+            }
     }
     float half[8];
     {
@@ -171,6 +265,7 @@ __global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p) {
         }
     }
 
+    if (tid == 0) TL(1);
     // ---- hat operands, straight into the C8 operand tiles
     {
         float ep_prev[8];                                         // e^{gi - half} of this lane's row in the previous block
@@ -178,9 +273,13 @@ __global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p) {
         for (int c = 0; c < 8; ++c) ep_prev[c] = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const In6 cur = in[j & 3];
-            if (j + 4 < 8) in[j & 3] = load6(p, b, h, t0, valid, 8 * (j + 4) + r8, cg);
+            In6 cur = head.in[j & 3];
+            if (j + 4 < 8) head.in[j & 3] = load6(p, b, h, t0, valid, 8 * (j + 4) + r8, cg);
             const int row = 8 * j + r8;
+            if (row >= valid) {                                // rows beyond the sequence's end are zero
+                const uint4 zero = make_uint4(0, 0, 0, 0);
+                cur.q = zero; cur.k = zero; cur.a0 = zero; cur.a1 = zero; cur.b0 = zero; cur.b1 = zero;
+            }
             float ep[8], em[8], ea[8], qs[8];
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -205,21 +304,14 @@ __global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p) {
                 *reinterpret_cast<uint4*>(p.ghat + (size_t)g * C * K + (size_t)row * K + cg * 8) = t8::pack8(ep);
         }
     }
-    // v rows of the tile: requested now, stored to shared memory after the first products are issued
-    uint4 vv[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int row = 8 * j + r8;
-        vv[j] = row < valid ? __ldg(reinterpret_cast<const uint4*>(p.v + (((size_t)b * p.T + t0 + row) * p.H + h) * V + cg * 8))
-                            : make_uint4(0, 0, 0, 0);
-    }
+    if (tid == 0) TL(2);
+    cp_async_wait_all();                                       // this tile's v has landed in its slot
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = tmem_s;
+    if (tid == 0) TL(3);
     const Tile tQ = t8::tile(sQ, 64), tK = t8::tile(sK, 64), tA = t8::tile(sA, 128), tB = t8::tile(sD, 128);
-    uint32_t phase = 0;
     if (tid == 0) {
         // hat operands for the scan, the output and the backward kernels
         bulk_s2g(p.Qh + g * CH64, sQ, 16384);
@@ -233,33 +325,26 @@ __global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p) {
         t8::mma_chain<false, false>(tmem + 64, tQ, 0, 0, tB, 0, 0, 128, K, false);
         umma_commit(&mma_bar);
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) sV[cg * 64 + 8 * j + r8] = vv[j];
+    // the registers of the streaming part are free: request the next tile's gk and first operand pieces now
+    // (unconditionally -- the last tile of a CTA requests its own pieces once more -- so that no condition ties the
+    //  data to this point)
+    tc = tile_coord(p, more ? gn : g);
+    load_head_gk<GK32>(head, p, tc, r8, cg);
     if (warp < 2) {
         wait_or_flag(&mma_bar, phase, p.status, 20);
         tc_fence_after();
         const int i = tid;
-        float f[64];
-        tmem_row64(t8::taddr(tmem, warp, 0), f);              // Aqk: j <= i
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) if (!((c8 * 8 + j) <= i)) f[c8 * 8 + j] = 0.f;
-            p.Aqk[g * 512 + c8 * 64 + i] = t8::pack8(f + c8 * 8);
-        }
 #pragma unroll 1
-        for (int hh = 0; hh < 2; ++hh) {                      // Aqb: column token <= i
-            tmem_row64(t8::taddr(tmem, warp, 64 + hh * 64), f);
-#pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) if (!(((hh * 64 + c8 * 8 + j) >> 1) <= i)) f[c8 * 8 + j] = 0.f;
-                p.Aqb[g * CH64 + (hh * 8 + c8) * 64 + i] = t8::pack8(f + c8 * 8);
-            }
-        }
+        for (int q4 = 0; q4 < 2; ++q4)                         // Aqk: j <= i
+            epilogue32(t8::taddr(tmem, warp, q4 * 32), q4 * 32, [&](int c) { return c <= i; },
+                       [&](int c8, uint4 ch) { p.Aqk[g * 512 + (q4 * 4 + c8) * 64 + i] = ch; });
+#pragma unroll 1
+        for (int q4 = 0; q4 < 4; ++q4)                         // Aqb: column token <= i
+            epilogue32(t8::taddr(tmem, warp, 64 + q4 * 32), q4 * 32, [&](int c) { return (c >> 1) <= i; },
+                       [&](int c8, uint4 ch) { p.Aqb[g * CH64 + (q4 * 4 + c8) * 64 + i] = ch; });
     }
     phase ^= 1;
-    fence_proxy_async();                                       // v tile -> visible to the copy engine and the MMAs
+    if (tid == 0) TL(4);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -276,27 +361,19 @@ __global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p) {
     wait_or_flag(&mma_bar, phase, p.status, 21);
     phase ^= 1;
     tc_fence_after();
+    if (tid == 0) TL(5);
     {   // Aak (strict mask) replaces Qh, Aab (strict mask in tokens) replaces Bh
         const int r = tid, i = r >> 1;
-        float f[64];
-        tmem_row64(t8::taddr(tmem, warp, 0), f);
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) if (!((c8 * 8 + j) < i)) f[c8 * 8 + j] = 0.f;
-            sQ[c8 * 128 + r] = t8::pack8(f + c8 * 8);          // [128 x 64] tile: 8 column groups of 128 rows
-        }
 #pragma unroll 1
-        for (int hh = 0; hh < 2; ++hh) {
-            tmem_row64(t8::taddr(tmem, warp, 64 + hh * 64), f);
-#pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) if (!(((hh * 64 + c8 * 8 + j) >> 1) < i)) f[c8 * 8 + j] = 0.f;
-                sD[(hh * 8 + c8) * 128 + r] = t8::pack8(f + c8 * 8);
-            }
-        }
+        for (int q4 = 0; q4 < 2; ++q4)                         // [128 x 64] tile: 8 column groups of 128 rows
+            epilogue32(t8::taddr(tmem, warp, q4 * 32), q4 * 32, [&](int c) { return c < i; },
+                       [&](int c8, uint4 ch) { sQ[(q4 * 4 + c8) * 128 + r] = ch; });
+#pragma unroll 1
+        for (int q4 = 0; q4 < 4; ++q4)
+            epilogue32(t8::taddr(tmem, warp, 64 + q4 * 32), q4 * 32, [&](int c) { return (c >> 1) < i; },
+                       [&](int c8, uint4 ch) { sD[(q4 * 4 + c8) * 128 + r] = ch; });
     }
+    load_head_in<GK32>(head, p, tc, r8, cg, 0);                // next tile: first row block
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
@@ -305,6 +382,7 @@ __global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p) {
         bulk_s2g(p.Aak + g * CH64, sQ, 16384);
         bulk_commit();
     }
+    if (tid == 0) TL(6);
 
     // ---- M = (I - Aab)^-1 in place: 16 x 16 diagonal blocks by forward substitution in registers, then three
     //      doubling levels.  A block of L = Aab is read for the last time at the level that produces the block of
@@ -332,6 +410,8 @@ __global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p) {
     }
     fence_proxy_async();
     __syncthreads();
+    if (tid == 0) TL(7);
+    load_head_in<GK32>(head, p, tc, r8, cg, 1);
     // Doubling: with the diagonal blocks of size bs inverted, the block below the diagonal of every pair
     // (even block J, odd block I = J+1) is  M[I,J] = D[I,I] L[I,J] D[J,J].  Each product is restricted to the
     // pair's own column range (N = bs) and contraction range (K = bs); the accumulator rows outside block I
@@ -394,6 +474,8 @@ __global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p) {
         tc_fence_before();
         __syncthreads();
     }
+    if (tid == 0) TL(8);
+    load_head_in<GK32>(head, p, tc, r8, cg, 2);
     for (int e = tid; e < 512; e += 128) sD[(8 + (e >> 6)) * 128 + (e & 63)] = make_uint4(0, 0, 0, 0);    // the quadrant
     fence_proxy_async();
     tc_fence_before();
@@ -416,13 +498,13 @@ __global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p) {
     wait_or_flag(&mma_bar, phase, p.status, 24);
     phase ^= 1;
     tc_fence_after();
+    if (tid == 0) TL(9);
+    load_head_in<GK32>(head, p, tc, r8, cg, 3);
+    if (more) request_v(p, tc, sV, r8, cg);                    // P = Aak v is complete: the v slot takes the next tile's
 #pragma unroll 1
-    for (int hh = 0; hh < 2; ++hh) {
-        float f[64];
-        tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) sP[(hh * 8 + c8) * 128 + tid] = t8::pack8(f + c8 * 8);
-    }
+    for (int q4 = 0; q4 < 4; ++q4)
+        epilogue32(t8::taddr(tmem, warp, q4 * 32), 0, [](int) { return true; },
+                   [&](int c8, uint4 ch) { sP[(q4 * 4 + c8) * 128 + tid] = ch; });
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
@@ -435,25 +517,34 @@ __global__ void __launch_bounds__(128, 2) chunk_prep_tc_kernel(ChunkPrepP p) {
             bulk_commit();
         }
     }
+    // Wh while u runs: into the Ah slot (Wh = M Ah is complete, Ah's copy to global memory was waited for before
+    // the Aak epilogue), from where one bulk copy takes it to global memory
 #pragma unroll 1
-    for (int hh = 0; hh < 2; ++hh) {                                                      // Wh while u runs
-        float f[64];
-        tmem_row64(t8::taddr(tmem, warp, 128 + hh * 64), f);
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) p.W[g * CH128 + (hh * 8 + c8) * 128 + tid] = t8::pack8(f + c8 * 8);
-    }
+    for (int q4 = 0; q4 < 4; ++q4)
+        epilogue32(t8::taddr(tmem, warp, 128 + q4 * 32), 0, [](int) { return true; },
+                   [&](int c8, uint4 ch) { sA[(q4 * 4 + c8) * 128 + tid] = ch; });
+    if (tid == 0) TL(10);
     wait_or_flag(&mma_bar, phase, p.status, 25);
+    phase ^= 1;
     tc_fence_after();
+    if (tid == 0) TL(11);
 #pragma unroll 1
-    for (int hh = 0; hh < 2; ++hh) {
-        float f[64];
-        tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) p.U[g * CH128 + (hh * 8 + c8) * 128 + tid] = t8::pack8(f + c8 * 8);
-    }
-    if (tid == 0) bulk_wait_read<0>();                         // shared memory stays valid until the copies have read it
+    for (int q4 = 0; q4 < 4; ++q4)
+        epilogue32(t8::taddr(tmem, warp, q4 * 32), 0, [](int) { return true; },
+                   [&](int c8, uint4 ch) { p.U[g * CH128 + (q4 * 4 + c8) * 128 + tid] = ch; });
+    if (tid == 0) TL(12);
+    fence_proxy_async();
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) {
+        bulk_s2g(p.W + g * CH128, sA, 32768);
+        bulk_commit();
+        bulk_wait_read<0>();                                   // the tiles are rewritten / released only after the copies read them
+    }
+    __syncthreads();
+    tc_fence_after();
+    if (tid == 0) TL(13);
+    }
     if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
@@ -466,7 +557,9 @@ int tc_launch_chunk_prep(const TcPlan& pl, const HdlaDims& d, const void* q, con
     int dev = 0;
     cudaGetDevice(&dev);
     if (attr_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(chunk_prep_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem);
+        cudaError_t e = cudaFuncSetAttribute(chunk_prep_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(chunk_prep_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrepSmem);
         if (e != cudaSuccess) return fail(HDLA_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
         attr_dev = dev;
     }
@@ -477,9 +570,20 @@ int tc_launch_chunk_prep(const TcPlan& pl, const HdlaDims& d, const void* q, con
                   U4(pl.W), U4(pl.P), U4(pl.U), reinterpret_cast<float*>(ws + pl.E),
                   reinterpret_cast<__nv_bfloat16*>(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, save_bwd ? 1 : 0,
                   reinterpret_cast<int*>(ws + pl.status)};
-    chunk_prep_tc_kernel<<<(unsigned)pl.G, 128, kPrepSmem, st>>>(pp);
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const long long slots = 2LL * sms;                     // two CTAs per SM, persistent
+    const unsigned grid = (unsigned)(pl.G < slots ? pl.G : slots);
+    if (d.gk_dtype == HDLA_F32) chunk_prep_tc_kernel<true><<<grid, 128, kPrepSmem, st>>>(pp, pl.G);
+    else                        chunk_prep_tc_kernel<false><<<grid, 128, kPrepSmem, st>>>(pp, pl.G);
     HDLA_CHECK_LAUNCH("chunk_prep_tc_kernel");
     return HDLA_OK;
 }
 
 }  // namespace hdla
+
+#ifdef HDLA_TIMELINE
+extern "C" __attribute__((visibility("default"))) int hdla_debug_timeline_prep(unsigned long long* host_dst, size_t count) {
+    return (int)cudaMemcpyFromSymbol(host_dst, hdla::tc::g_timeline, count * sizeof(unsigned long long));
+}
+#endif

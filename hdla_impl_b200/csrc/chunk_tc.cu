@@ -13,7 +13,6 @@
 //
 // All matrices between kernels are bf16 in the C8 blocked layout (tc_tiles.cuh) and move with
 // bulk asynchronous copies; all products run on tcgen05.mma with fp32 accumulation in TMEM.
-#include <cstdlib>
 #include <cstring>
 
 #include "tc_plan.cuh"
@@ -1544,7 +1543,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     const TcPlan pl = make_tc_plan(d);
     // a workspace sized for the backward pass also receives what only the backward kernels read
     const bool save_bwd = ws_bytes >= pl.total;
-    static const bool unfused = getenv("HDLA_UNFUSED_PREP") != nullptr;
+    const bool unfused = !(d.flags & HDLA_FLAG_FUSED_PREP);
     static thread_local int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1572,7 +1571,6 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         if (!unfused) {
             TRY(tc_launch_chunk_prep(pl, d, q, k, v, a, b, gk, scale, ws, save_bwd, st));
         } else {
-            if (!save_bwd) return fail(HDLA_ERR_WORKSPACE, "the unfused preparation needs the backward-sized workspace");
             PrepP pp{(bp)q, (bp)k, (bp)v, (bp)a, (bp)b, gk, U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc),
                      F(pl.E), (__nv_bfloat16*)(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status};
             prep_hat_kernel<<<G, 128, 0, st>>>(pp);
@@ -1793,7 +1791,7 @@ int tc_debug_buffer(const HdlaDims& d, const unsigned char* ws, const char* name
     struct Ent { const char* n; size_t off; int rows, cols; };
     const Ent tab[] = {{"Qh", pl.Qh, 64, 128}, {"Kh", pl.Kh, 64, 128}, {"Ah", pl.Ah, 128, 128}, {"Bh", pl.Bh, 128, 128},
                        {"Vc", pl.Vc, 64, 128}, {"Aqk", pl.Aqk, 64, 64}, {"Aqb", pl.Aqb, 64, 128},
-                       {"Aak", pl.Aak, 128, 64}, {"Aab", pl.Aab, 128, 128}, {"M", pl.M, 128, 128},
+                       {"Aak", pl.Aak, 128, 64}, {"M", pl.M, 128, 128},
                        {"W", pl.W, 128, 128}, {"P", pl.P, 128, 128}, {"U", pl.U, 128, 128}, {"Hs", pl.Hs, 128, 128},
                        {"V2", pl.V2, 128, 128},
                        {"dOc", pl.dOc, 64, 128}, {"dAqk", pl.dAqk, 64, 64}, {"dAqb", pl.dAqb, 64, 128},

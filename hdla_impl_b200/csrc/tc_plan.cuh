@@ -40,11 +40,18 @@ inline TcPlan make_tc_plan(const HdlaDims& d) {
         return o;
     };
     p.status = off; off += 256;
-    // forward region: what the scan and the output kernel read
+    // forward region: what the scan and the output kernel read.  The fused preparation kernel (HDLA_FLAG_FUSED_PREP)
+    // keeps Aab on chip and writes Ah, Aak, M, P and the un-gating factors only for a backward pass, so with it
+    // those live in the backward region; the four-kernel preparation passes them from kernel to kernel.
+    const bool fused = (d.flags & HDLA_FLAG_FUSED_PREP) != 0;
     p.Qh = take(16384); p.Kh = take(16384); p.Bh = take(32768); p.Vc = take(16384);
     p.E = take(K * 4);
     p.Aqk = take(8192); p.Aqb = take(16384);
     p.W = take(32768); p.U = take(32768); p.Hs = take(32768); p.V2 = take(32768);
+    if (!fused) {
+        p.Ah = take(32768); p.ghat = take(C * K * 2); p.Aak = take(16384); p.M = take(32768); p.P = take(32768);
+        p.Aab = take(32768);
+    }
     p.HT = off; off += (((size_t)p.BH * K * V * 4 + 255) / 256) * 256;
     p.zero = off; off += 32768;
     // Few (batch, head) pairs leave most SMs idle during the serial scan: cut each sequence into segments that
@@ -75,8 +82,10 @@ inline TcPlan make_tc_plan(const HdlaDims& d) {
     p.Sin = off; off += nseg_max > 1 ? slots * K * V * 4 : 0;
     p.total_fwd = off;
     // backward region: forward intermediates that only the backward kernels read, then the backward's own
-    p.Ah = take(32768); p.ghat = take(C * K * 2); p.Aak = take(16384); p.M = take(32768); p.P = take(32768);
-    p.Aab = take(32768);
+    if (fused) {
+        p.Ah = take(32768); p.ghat = take(C * K * 2); p.Aak = take(16384); p.M = take(32768); p.P = take(32768);
+        p.Aab = 0;                                         // never leaves the SM
+    }
     p.dOc = take(16384); p.dAqk = take(8192); p.dAqb = take(16384); p.DV2 = take(32768); p.DE = take(32768);
     p.dgl = take(K * 4); p.dW = take(32768); p.dP = take(32768); p.dAak = take(16384); p.dAab = take(32768);
     p.total = off;

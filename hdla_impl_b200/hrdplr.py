@@ -47,6 +47,8 @@ def _dims(q, v, a, gk, RANK_AB: int, chunk_size: int, flags: int = 0) -> _lib.Hd
     B, T, H, K = q.shape
     if os.environ.get("HDLA_FORCE_SIMT", "0") == "1":      # debugging aid: fp32 CUDA-core pipeline for any dtype
         flags |= _lib.FLAG_FORCE_SIMT
+    if os.environ.get("HDLA_FUSED_PREP", "0") == "1":      # one-kernel chunk preparation (see include/hdla.h)
+        flags |= _lib.FLAG_FUSED_PREP
     return _lib.HdlaDims(B, T, H, K, v.shape[-1], RANK_AB, chunk_size, _lib.dtype_code(q.dtype),
                          _lib.dtype_code(gk.dtype), flags)
 

@@ -50,6 +50,12 @@ extern "C" {
 #define HDLA_FLAG_WS_HOLDS_FWD  1   /* hdla_chunk_bwd: the workspace still holds what hdla_chunk_fwd
                                        left there for the same inputs -> skip the recomputation  */
 #define HDLA_FLAG_FORCE_SIMT    2   /* use the fp32 CUDA-core pipeline even for bf16 inputs       */
+#define HDLA_FLAG_FUSED_PREP    4   /* bf16 tensor-core pipeline: run everything before the scan (cumulative decay,
+                                       hat operands, score matrices, WY inverse, w/u) as ONE kernel per tile instead
+                                       of four.  It moves 38 % fewer bytes and needs a smaller forward workspace,
+                                       but runs about 5 % slower on large problems (two CTAs of four warps per SM do
+                                       not hide its latencies); the workspace layout depends on it, so a forward
+                                       and its backward must agree on the flag.                                   */
 
 /* Phase selector (bits 4..7 of HdlaDims.flags), for callers that split a sequence over devices
  * (context parallelism).  Only the inter-chunk scan depends on the incoming state, so a call can be cut:

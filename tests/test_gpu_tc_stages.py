@@ -26,9 +26,11 @@ def _dump(ws, dims, name, shape, dev):
     return out.cpu().double()
 
 
+@pytest.mark.parametrize("fused", [False, True])          # four-kernel and one-kernel chunk preparation
 @pytest.mark.parametrize("T,gk_div,h0_std", [(256, 16.0, None), (200, 2.0, 0.5), (320, 1.0, 0.5)])
-def test_tc_forward_stages(T, gk_div, h0_std):
+def test_tc_forward_stages(T, gk_div, h0_std, fused, monkeypatch):
     from hdla_impl_b200 import _lib, hrdplr
+    monkeypatch.setenv("HDLA_FUSED_PREP", "1" if fused else "0")
     dev = torch.device("cuda:0")
     B, H, K, V, Cc = 2, 2, 128, 128, 64
     x = make_inputs(B, T, H, K, V, R, seed=21, dtype=torch.bfloat16, gk_div=gk_div, h0_std=h0_std)
@@ -76,10 +78,12 @@ def test_tc_forward_stages(T, gk_div, h0_std):
     assert not bad, "; ".join(bad)
 
 
-def test_tc_backward_stages():
+@pytest.mark.parametrize("fused", [False, True])
+def test_tc_backward_stages(fused, monkeypatch):
     """Backward intermediates of the tensor-core pipeline (hat-operand form) against the oracle's stage formulas."""
     import hdla_impl_b200 as HD
     from hdla_impl_b200 import _lib, hrdplr
+    monkeypatch.setenv("HDLA_FUSED_PREP", "1" if fused else "0")
     dev = torch.device("cuda:0")
     B, T, H, K, V, Cc = 1, 192, 2, 128, 128, 64
     x = make_inputs(B, T, H, K, V, R, seed=22, dtype=torch.bfloat16, gk_div=8.0, h0_std=0.3, with_dht=True)
