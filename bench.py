@@ -52,6 +52,9 @@ WORKLOADS = {
     "cfg0": (2, 256, 4, 64, 64, 64, "f32"),
     # profiling case: cfg 1 with a quarter of the batch (inputs still larger than L2, ~2 GB on the device)
     "cfg1_small": (2, 4096, 16, 128, 128, 64, "bf16"),
+    # what one GPU holds of cfg 1 when the batch is sharded over 2 / 8 GPUs (for profiling the sharded case on one GPU)
+    "cfg1_shard2": (4, 4096, 16, 128, 128, 64, "bf16"),
+    "cfg1_shard8": (1, 4096, 16, 128, 128, 64, "bf16"),
     "cfg3": (1, 65536, 16, 128, 128, 64, "bf16"),
     # one layer of the 24-layer stack of cfg 4 (B32 sharded over the GPUs by batch): operator only
     "cfg4": (32, 4096, 16, 128, 128, 64, "bf16"),

@@ -1424,52 +1424,93 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
 // `pre` (optional, indexed like F) is added to the running state before a segment's map is applied, `post` (optional,
 // one K x V matrix per pair) to the final value: with them the same chain serves the gradient of a sequence that is
 // cut over ranks, where every rank contributes the gradient of its own final state.
+// Layout of the work: one CTA per (pair, 16 state columns) -- 8 CTAs per pair, so even 16 pairs fill most SMs --
+// and one thread per state row, its 16 columns in registers.  The K x K transition of a segment is staged in shared
+// memory in the orientation the product reads it (element (j, k) at [j][k], pitch 129 words: conflict-free both for
+// the transposing store of the forward case and for the reads), the running state columns in a second small tile;
+// the inner loop is 128 x 16 fused multiply-adds per thread and segment.
+constexpr int kComposeCols = 16;
+constexpr int kComposeSmem = (K * 129 + K * (kComposeCols + 4)) * 4;
+
 __global__ void __launch_bounds__(128) compose_segments_kernel(const float* T, const float* F, const float* S0,
                                                                float* Sin, float* fin, int nseg, int reverse,
                                                                int s0_identity, int lead_final, long long bh_stride,
                                                                long long seg_stride, long long t_bh_stride,
                                                                long long t_seg_stride, const float* pre,
                                                                const float* post) {
-    __shared__ float cur[K][33];
-    const int bh = blockIdx.x, c0 = blockIdx.y * 32, k = threadIdx.x;
-    float x[32];
+    constexpr int CB = kComposeCols;
+    extern __shared__ __align__(16) float csm[];
+    float (*sT)[129] = reinterpret_cast<float (*)[129]>(csm);                    // sT[j][k] = factor of cur[j] in row k
+    float (*cur)[CB + 4] = reinterpret_cast<float (*)[CB + 4]>(csm + K * 129);   // 16-byte aligned rows: read as float4
+    const int bh = blockIdx.x, c0 = blockIdx.y * CB, k = threadIdx.x;
+    const int lane = k & 31, warp = k >> 5;
+    float x[CB];
 #pragma unroll
-    for (int c = 0; c < 32; ++c)
+    for (int c = 0; c < CB; ++c)
         x[c] = s0_identity ? (c0 + c == k ? 1.f : 0.f) : (S0 ? S0[((size_t)bh * K + k) * V + c0 + c] : 0.f);
     const int first = reverse ? nseg - 1 : 0, step = reverse ? -1 : 1;
     if (lead_final) {          // F of the first segment in scan order IS the state leaving it (it was scanned for real)
         const size_t slot = (size_t)(bh * bh_stride + first * seg_stride);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) x[c] = F[(slot * K + k) * V + c0 + c];
+        for (int c = 0; c < CB; ++c) x[c] = F[(slot * K + k) * V + c0 + c];
     }
     for (int i = lead_final ? 1 : 0; i < nseg; ++i) {
         const int sgm = first + i * step;
         const size_t slot = (size_t)(bh * bh_stride + sgm * seg_stride);
+        const bool apply = i + 1 < nseg || fin;
+        if (apply) {
+            // stage the transition: forward needs T[k][j] at sT[j][k] (transposed), reverse T[j][k] at sT[j][k]
+            const float* Tm = T + (size_t)(bh * t_bh_stride + sgm * t_seg_stride) * K * K;
+            // a warp reads one 512-byte row of T per load (lane = four consecutive j); sixteen rows are requested
+            // before the first is stored, so the staging costs two round trips to L2, not thirty-two
+#pragma unroll 1
+            for (int base = 0; base < 32; base += 16) {
+                float4 buf[16];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
+                for (int u = 0; u < 16; ++u)
+                    buf[u] = __ldg(reinterpret_cast<const float4*>(Tm + (size_t)(warp + 4 * (base + u)) * K + 4 * lane));
+#pragma unroll
+                for (int u = 0; u < 16; ++u) {
+                    const int r = warp + 4 * (base + u);
+                    if (reverse) {
+                        sT[r][4 * lane] = buf[u].x; sT[r][4 * lane + 1] = buf[u].y;
+                        sT[r][4 * lane + 2] = buf[u].z; sT[r][4 * lane + 3] = buf[u].w;
+                    } else {
+                        sT[4 * lane][r] = buf[u].x; sT[4 * lane + 1][r] = buf[u].y;
+                        sT[4 * lane + 2][r] = buf[u].z; sT[4 * lane + 3][r] = buf[u].w;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < CB; ++c) {
             if (pre) x[c] += pre[(slot * K + k) * V + c0 + c];
             if (Sin) Sin[(slot * K + k) * V + c0 + c] = x[c];
             cur[k][c] = x[c];
         }
         __syncthreads();
-        if (i + 1 < nseg || fin) {
-            const float* Tm = T + (size_t)(bh * t_bh_stride + sgm * t_seg_stride) * K * K;
-            float acc[32];
+        if (apply) {
+            float acc[CB];
 #pragma unroll
-            for (int c = 0; c < 32; ++c) acc[c] = s0_identity ? 0.f : F[(slot * K + k) * V + c0 + c];
+            for (int c = 0; c < CB; ++c) acc[c] = s0_identity ? 0.f : F[(slot * K + k) * V + c0 + c];
+#pragma unroll 4
             for (int j = 0; j < K; ++j) {
-                const float t = reverse ? Tm[(size_t)j * K + k] : Tm[(size_t)k * K + j];
+                const float t = sT[j][k];
 #pragma unroll
-                for (int c = 0; c < 32; ++c) acc[c] = fmaf(t, cur[j][c], acc[c]);
+                for (int c4 = 0; c4 < CB / 4; ++c4) {             // the same address for all lanes: a broadcast
+                    const float4 v = *reinterpret_cast<const float4*>(&cur[j][c4 * 4]);
+                    acc[c4 * 4] = fmaf(t, v.x, acc[c4 * 4]); acc[c4 * 4 + 1] = fmaf(t, v.y, acc[c4 * 4 + 1]);
+                    acc[c4 * 4 + 2] = fmaf(t, v.z, acc[c4 * 4 + 2]); acc[c4 * 4 + 3] = fmaf(t, v.w, acc[c4 * 4 + 3]);
+                }
             }
 #pragma unroll
-            for (int c = 0; c < 32; ++c) x[c] = acc[c];
+            for (int c = 0; c < CB; ++c) x[c] = acc[c];
         }
         __syncthreads();
     }
     if (fin) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c)
+        for (int c = 0; c < CB; ++c)
             fin[((size_t)bh * K + k) * V + c0 + c] = x[c] + (post ? post[((size_t)bh * K + k) * V + c0 + c] : 0.f);
     }
 }
@@ -1513,8 +1554,16 @@ int sm_count() {
 int tc_compose_states(const float* T, const float* F, const float* S0, const float* pre, const float* post,
                       float* out, int BH, int count, long long f_stride, long long t_stride, int reverse,
                       cudaStream_t st) {
-    compose_segments_kernel<<<dim3(BH, V / 32), 128, 0, st>>>(T, F, S0, nullptr, out, count, reverse, 0, 0, 1, f_stride,
-                                                              1, t_stride, pre, post);
+    static thread_local int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+        int rc = set_smem(compose_segments_kernel, kComposeSmem);
+        if (rc != HDLA_OK) return rc;
+        attr_dev = dev;
+    }
+    compose_segments_kernel<<<dim3(BH, V / kComposeCols), 128, kComposeSmem, st>>>(T, F, S0, nullptr, out, count, reverse,
+                                                                                 0, 0, 1, f_stride, 1, t_stride, pre, post);
     HDLA_CHECK_LAUNCH("compose_segments_kernel");
     return HDLA_OK;
 }
@@ -1556,6 +1605,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         TRY(set_smem(wy_bwd_tc_kernel, kWySmem));
         TRY(set_smem(grad_tc_kernel, kGradSmem));
         TRY(set_smem(dau_tc_kernel, 81920));
+        TRY(set_smem(compose_segments_kernel, kComposeSmem));
         attr_dev = dev;
     }
     auto U4 = [&](size_t off) { return reinterpret_cast<uint4*>(ws + off); };
@@ -1606,7 +1656,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1; s1.fin_transition = F(pl.Tseg);
             scan_tc_kernel<<<dim3(pl.BH * pl.nseg, 2), 256, 196608, st>>>(s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
-            compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, nullptr, ht,
+            compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, nullptr, ht,
                                                                          pl.nseg, 0, 1, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
@@ -1621,7 +1671,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     if (phase == HDLA_PHASE_STATE) {
         if (!ht) return fail(HDLA_ERR_INVALID, "state pass needs the output pointer (ht)");
         if (pl.nseg > 1) {                    // affine maps of the segments are in the workspace (TRANSITION phase)
-            compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), h0, nullptr, ht,
+            compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), h0, nullptr, ht,
                                                                          pl.nseg, 0, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
@@ -1640,7 +1690,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         scan_tc_kernel<<<dim3(pl.BH * (pl.nseg - 1), 2), 256, 196608, st>>>(s1);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         // ... the state entering every later segment follows from the first segment's final state ...
-        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
+        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
                                                                      pl.nseg, 0, 0, 1, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         // ... and the remaining segments are scanned for real at once
@@ -1658,7 +1708,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
         }
         // ... composed into the state entering every segment ...
-        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), nullptr, pl.nseg, 0, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
+        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), nullptr, pl.nseg, 0, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         // ... and the real scan of all segments at once
         ScanTcP s2 = scan_params(F(pl.Sin), U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
@@ -1722,7 +1772,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1;
             scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
-            compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), dht, nullptr, dh0,
+            compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), dht, nullptr, dh0,
                                                                          pl.nseg, 1, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
@@ -1741,7 +1791,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         s1.seg_off = 1; s1.seg_cnt = pl.nseg - 1; s1.lead_real = 1; s1.lead_init = dht;
         scan_tc_kernel<<<pl.BH * (pl.nseg - 1), 256, 196608, st>>>(s1);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
-        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
+        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
                                                                      pl.nseg, 1, 0, 1, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         ScanTcP s2 = rscan_params(F(pl.Sin), U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
@@ -1757,7 +1807,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
         }
-        compose_segments_kernel<<<dim3(pl.BH, V / 32), 128, 0, st>>>(F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), nullptr, pl.nseg, 1, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
+        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), nullptr, pl.nseg, 1, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         ScanTcP s2 = rscan_params(F(pl.Sin), U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
         s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;
