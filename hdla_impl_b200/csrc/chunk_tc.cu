@@ -38,6 +38,7 @@ struct PrepP {
     float scale;
     int T, H, NT, gdt;
     int* status;
+    int Kd, Vd;                           // head dims of the public tensors (multiples of 8, <= 128); the tiles are padded with zeros
 };
 
 // the seven 16-byte input pieces one thread handles per step: (row r, column group kc) of q, k, v, a0, a1, b0, b1
@@ -48,18 +49,19 @@ __device__ __forceinline__ PrepIn prep_load(const PrepP& p, int b, int h, int t0
     const int kc = (blk & 3) * 4 + (lane >> 3);
     const uint4 zero = make_uint4(0, 0, 0, 0);
     PrepIn x{zero, zero, zero, zero, zero, zero, zero};
-    if (r < valid) {
-        const size_t src = (((size_t)b * p.T + t0 + r) * p.H + h) * K + kc * 8;
-        const size_t sa0 = (((size_t)b * p.T * R + (size_t)(t0 + r) * R) * p.H + h) * K + kc * 8;
-        const size_t sa1 = sa0 + (size_t)p.H * K;
+    if (r < valid && kc * 8 < p.Kd) {
+        const size_t src = (((size_t)b * p.T + t0 + r) * p.H + h) * p.Kd + kc * 8;
+        const size_t sa0 = (((size_t)b * p.T * R + (size_t)(t0 + r) * R) * p.H + h) * p.Kd + kc * 8;
+        const size_t sa1 = sa0 + (size_t)p.H * p.Kd;
         x.q = __ldg(reinterpret_cast<const uint4*>(p.q + src));
         x.k = __ldg(reinterpret_cast<const uint4*>(p.k + src));
-        x.v = __ldg(reinterpret_cast<const uint4*>(p.v + (((size_t)b * p.T + t0 + r) * p.H + h) * V + kc * 8));
         x.a0 = __ldg(reinterpret_cast<const uint4*>(p.a + sa0));
         x.a1 = __ldg(reinterpret_cast<const uint4*>(p.a + sa1));
         x.b0 = __ldg(reinterpret_cast<const uint4*>(p.b + sa0));
         x.b1 = __ldg(reinterpret_cast<const uint4*>(p.b + sa1));
     }
+    if (r < valid && kc * 8 < p.Vd)
+        x.v = __ldg(reinterpret_cast<const uint4*>(p.v + (((size_t)b * p.T + t0 + r) * p.H + h) * p.Vd + kc * 8));
     return x;
 }
 
@@ -80,9 +82,9 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
     {   // two-level cumulative sum: warp w owns rows [16w, 16w+16), lane owns 4 columns
         // (all sixteen loads are issued before the first value is used: the dtype branch stays outside the loops)
         float4 x[16];
-        const size_t row0 = (((size_t)b * p.T + t0 + warp * 16) * p.H + h) * K + lane * 4;
-        const size_t rstride = (size_t)p.H * K;
-        const int nrow = valid - warp * 16;                    // rows of this warp that exist
+        const size_t row0 = (((size_t)b * p.T + t0 + warp * 16) * p.H + h) * p.Kd + lane * 4;
+        const size_t rstride = (size_t)p.H * p.Kd;
+        const int nrow = lane * 4 < p.Kd ? valid - warp * 16 : 0;     // rows of this warp that exist (none in the padding)
         if (p.gdt == HDLA_F32) {
             const float* src = static_cast<const float*>(p.gk) + row0;
 #pragma unroll
@@ -125,6 +127,13 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
         const float gl = gis[C - 1][tid];
         p.E[(size_t)g * K + tid] = __expf(0.5f * gl);
         if (!(fabsf(gl) <= kMaxChunkDecay)) atomicExch(p.status + kStatusDecay, 1);      // also catches NaN
+        // largest chunk decay of the call (status word 2): warp maximum, then one filtered atomic per warp
+        float worst = fabsf(gl);
+        worst = worst == worst ? worst : 0.f;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) worst = fmaxf(worst, __shfl_xor_sync(0xffffffffu, worst, d));
+        if (lane == 0 && __float_as_int(worst) > *reinterpret_cast<volatile int*>(p.status + kStatusMaxDecay))
+            atomicMax(p.status + kStatusMaxDecay, __float_as_int(worst));
     }
     // hat operands: per instruction a warp covers 8 rows x 4 column groups, so every global access
     // is a run of full 32-byte sectors (64 B per row in, 128 B per column group out)
@@ -562,6 +571,9 @@ struct ScanTcP {
     // lead_init (indexed by batch*head, may be null) with stores; its transition twin exits at once
     int lead_real;
     const float* lead_init;
+    // head dims of the PUBLIC state tensors (h0 / ht / dht / dh0, [.., Kd, Vd]); states kept in the workspace
+    // (the by-slot ones, the transition result and fin2) are always K x V = 128 x 128
+    int Kd, Vd;
 };
 
 __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
@@ -612,10 +624,11 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         for (int j = 0; j < 64; ++j) S[j] = (half * 64 + j == row) ? 1.f : 0.f;
     } else if (p.init) {
         const size_t is = p.init_by_slot ? (size_t)slot : (size_t)bh;
-        const float4* src = reinterpret_cast<const float4*>(p.init + (is * K + row) * V + half * 64);
+        const int kd = p.init_by_slot ? K : p.Kd, vd = p.init_by_slot ? V : p.Vd;
+        const float4* src = reinterpret_cast<const float4*>(p.init + (is * kd + row) * vd + half * 64);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const float4 x = src[j];
+            const float4 x = (row < kd && half * 64 + 4 * j < vd) ? src[j] : make_float4(0.f, 0.f, 0.f, 0.f);
             S[4 * j] = x.x; S[4 * j + 1] = x.y; S[4 * j + 2] = x.z; S[4 * j + 3] = x.w;
         }
     } else {
@@ -731,12 +744,13 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     const bool ends_scan = p.reverse ? (seg == 0) : (seg == p.nseg - 1);
     if (!p.fin_last_only || ends_scan) {
         const size_t fs = p.fin_by_slot ? (size_t)slot : (size_t)bh;
-        const size_t off = (fs * K + row) * V + half * 64;
+        const int kd = p.fin_by_slot ? K : p.Kd, vd = p.fin_by_slot ? V : p.Vd;
+        const size_t off = (fs * kd + row) * vd + half * 64;
         const size_t off2 = ((size_t)bh * K + row) * V + half * 64;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float4 x = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
-            if (p.fin) reinterpret_cast<float4*>(p.fin + off)[j] = x;
+            if (p.fin && row < kd && half * 64 + 4 * j < vd) reinterpret_cast<float4*>(p.fin + off)[j] = x;
             if (p.fin2) reinterpret_cast<float4*>(p.fin2 + off2)[j] = x;
         }
     }
@@ -932,6 +946,7 @@ struct DauP {
     uint4 *dOc, *dAqk, *dAqb, *DV2;
     int T, H, NT;
     int* status;
+    int Vd;
 };
 
 __global__ void __launch_bounds__(128) dau_tc_kernel(DauP p) {
@@ -963,7 +978,8 @@ __global__ void __launch_bounds__(128) dau_tc_kernel(DauP p) {
             const int kc = (blk & 3) * 4 + (lane >> 3);
             const int t = n * C + r;
             c[it] = make_uint4(0, 0, 0, 0);
-            if (t < p.T) c[it] = __ldg(reinterpret_cast<const uint4*>(p.d_o + (((size_t)b * p.T + t) * p.H + h) * V + kc * 8));
+            if (t < p.T && kc * 8 < p.Vd)
+                c[it] = __ldg(reinterpret_cast<const uint4*>(p.d_o + (((size_t)b * p.T + t) * p.H + h) * p.Vd + kc * 8));
         }
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
@@ -1035,6 +1051,7 @@ struct OutP {
     __nv_bfloat16* o;
     int T, H, NT;
     int* status;
+    int Vd;
 };
 
 __global__ void __launch_bounds__(128) out_tc_kernel(OutP p) {
@@ -1083,15 +1100,18 @@ __global__ void __launch_bounds__(128) out_tc_kernel(OutP p) {
         const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
         const int b = bh / p.H, h = bh % p.H;
         const int t = n * C + tid;
-        uint4* dst = reinterpret_cast<uint4*>(p.o + (((size_t)b * p.T + t) * p.H + h) * V);
+        uint4* dst = reinterpret_cast<uint4*>(p.o + (((size_t)b * p.T + t) * p.H + h) * p.Vd);
 #pragma unroll 1
         for (int hh = 0; hh < 2; ++hh) {
             float f[64];
             tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
             if (t < p.T) {
 #pragma unroll
-                for (int cg = 0; cg < 8; cg += 2)          // whole 32-byte sectors per lane (lanes are 4 KB apart)
-                    sm100::st_global_32B(dst + hh * 8 + cg, t8::pack8(f + cg * 8), t8::pack8(f + cg * 8 + 8));
+                for (int cg = 0; cg < 8; cg += 2) {        // whole 32-byte sectors per lane (lanes are 4 KB apart)
+                    const int col = (hh * 8 + cg) * 8;
+                    if (col + 16 <= p.Vd) sm100::st_global_32B(dst + hh * 8 + cg, t8::pack8(f + cg * 8), t8::pack8(f + cg * 8 + 8));
+                    else if (col < p.Vd) dst[hh * 8 + cg] = t8::pack8(f + cg * 8);
+                }
             }
         }
     }
@@ -1144,6 +1164,7 @@ struct GradP {
     int T, H, NT, gdt;
     int* status;
     long long G;           // number of tiles; the grid is persistent
+    int Kd, Vd;            // head dims of the public tensors (channels beyond them are padding and are not written)
 };
 
 template <bool A_MN, bool B_MN>
@@ -1284,9 +1305,10 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         const int k = tid & 127, wg = tid >> 7;
         const int i_lo = 48 - 16 * wg;
         const int t_left = p.T - n * C;                               // tokens of this chunk that exist
-        const size_t tok_stride = (size_t)p.H * K;                    // elements between tokens in [B,T,H,K]
-        const size_t base_qk = (((size_t)b * p.T + (size_t)n * C + i_lo) * p.H + h) * K + k;
-        const size_t base_ab = (((size_t)b * p.T + (size_t)n * C + i_lo) * R * p.H + h) * K + k;
+        const size_t tok_stride = (size_t)p.H * p.Kd;                 // elements between tokens in [B,T,H,K]
+        const size_t base_qk = (((size_t)b * p.T + (size_t)n * C + i_lo) * p.H + h) * p.Kd + k;
+        const size_t base_ab = (((size_t)b * p.T + (size_t)n * C + i_lo) * R * p.H + h) * p.Kd + k;
+        const bool k_ok = k < p.Kd;                                   // this thread's channel exists in the public tensors
         // eg[j] = e^{gi - half} of token i_lo + j - 1 (the token before the chunk has e^{ge - half} = e^{-half})
         float eg[17];
         uint32_t bhp[16];                                             // Bh rows 2i, 2i+1 of this thread's tokens
@@ -1308,7 +1330,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-                if (i_lo + j < t_left) p.dq[base_qk + (size_t)j * tok_stride] = __float2bfloat16_rn(p.scale * eg[j + 1] * __uint_as_float(u[j]));
+                if (i_lo + j < t_left && k_ok) p.dq[base_qk + (size_t)j * tok_stride] = __float2bfloat16_rn(p.scale * eg[j + 1] * __uint_as_float(u[j]));
         }
         // ---- after P2: dv (lane = value channel; group w writes tokens 16w..16w+15)
         wait_idle_or_flag(&m2, ph, p.status, 90);
@@ -1320,7 +1342,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 const int t = n * C + wg * 16 + j;
-                if (t < p.T) p.dv[(((size_t)b * p.T + t) * p.H + h) * V + k] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                if (t < p.T && k < p.Vd) p.dv[(((size_t)b * p.T + t) * p.H + h) * p.Vd + k] = __float2bfloat16_rn(__uint_as_float(v[j]));
             }
         }
         // ---- after P3: da = e^{ge-half} dAh
@@ -1334,7 +1356,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const int jt = hb * 8 + j;
-                if (i_lo + jt < t_left) {
+                if (i_lo + jt < t_left && k_ok) {
                     p.da[base_ab + (size_t)(2 * jt) * tok_stride] = __float2bfloat16_rn(eg[jt] * __uint_as_float(v[2 * j]));
                     p.da[base_ab + (size_t)(2 * jt + 1) * tok_stride] = __float2bfloat16_rn(eg[jt] * __uint_as_float(v[2 * j + 1]));
                 }
@@ -1369,7 +1391,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
 #pragma unroll
             for (int j = 3; j >= 0; --j) {
                 const int jt = hb * 4 + j;
-                const bool ok = i_lo + jt < t_left;
+                const bool ok = i_lo + jt < t_left && k_ok;
                 const float em = __frcp_rn(eg[jt + 1]);
                 const float dqh = __uint_as_float(vq[j]), dkh = __uint_as_float(vk[j]);
                 const float db0 = __uint_as_float(vb[2 * j]), db1 = __uint_as_float(vb[2 * j + 1]);
@@ -1396,7 +1418,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
 #pragma unroll 4
         for (int jj = 0; jj < 16; ++jj) {
             const int t = n * C + i_lo + jj;
-            if (t < p.T) st_elem(p.dgk, (((size_t)b * p.T + t) * p.H + h) * K + k, p.gdt, dgk_loc[jj * K] + add);
+            if (t < p.T && k_ok) st_elem(p.dgk, (((size_t)b * p.T + t) * p.H + h) * p.Kd + k, p.gdt, dgk_loc[jj * K] + add);
         }
     }
     // every thread is done with this tile's slots and accumulators before the next tile's first loads and products
@@ -1424,94 +1446,105 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
 // `pre` (optional, indexed like F) is added to the running state before a segment's map is applied, `post` (optional,
 // one K x V matrix per pair) to the final value: with them the same chain serves the gradient of a sequence that is
 // cut over ranks, where every rank contributes the gradient of its own final state.
-// Layout of the work: one CTA per (pair, 16 state columns) -- 8 CTAs per pair, so even 16 pairs fill most SMs --
-// and one thread per state row, its 16 columns in registers.  The K x K transition of a segment is staged in shared
-// memory in the orientation the product reads it (element (j, k) at [j][k], pitch 129 words: conflict-free both for
-// the transposing store of the forward case and for the reads), the running state columns in a second small tile;
-// the inner loop is 128 x 16 fused multiply-adds per thread and segment.
+// Layout of the work: one CTA of 256 threads per (pair, 16 state columns) -- 8 CTAs per pair, so even 16 pairs fill
+// most SMs -- thread = (state row k, 8 of the 16 columns), its columns in registers.  The K x K transition of a
+// segment is staged in shared memory in the orientation the product reads it (element (j, k) at [j][k], pitch 129
+// words: conflict-free both for the transposing store of the forward case and for the reads) by coalesced scalar
+// loads, all 64 of a thread in flight at once together with its loads of F, so a segment costs one round trip to L2
+// plus 128 x 8 fused multiply-adds per thread.
 constexpr int kComposeCols = 16;
 constexpr int kComposeSmem = (K * 129 + K * (kComposeCols + 4)) * 4;
 
-__global__ void __launch_bounds__(128) compose_segments_kernel(const float* T, const float* F, const float* S0,
+__global__ void __launch_bounds__(256) compose_segments_kernel(const float* T, const float* F, const float* S0,
                                                                float* Sin, float* fin, int nseg, int reverse,
                                                                int s0_identity, int lead_final, long long bh_stride,
                                                                long long seg_stride, long long t_bh_stride,
                                                                long long t_seg_stride, const float* pre,
                                                                const float* post) {
-    constexpr int CB = kComposeCols;
+    constexpr int CB = kComposeCols, CT = 8;                                     // columns per CTA / per thread
     extern __shared__ __align__(16) float csm[];
     float (*sT)[129] = reinterpret_cast<float (*)[129]>(csm);                    // sT[j][k] = factor of cur[j] in row k
     float (*cur)[CB + 4] = reinterpret_cast<float (*)[CB + 4]>(csm + K * 129);   // 16-byte aligned rows: read as float4
-    const int bh = blockIdx.x, c0 = blockIdx.y * CB, k = threadIdx.x;
-    const int lane = k & 31, warp = k >> 5;
-    float x[CB];
+    const int bh = blockIdx.x, tid = threadIdx.x;
+    const int k = tid & (K - 1), ch = tid >> 7;                                  // row, column half
+    const int c0 = blockIdx.y * CB + ch * CT;                                    // first state column of this thread
+    const int lane = tid & 31, warp = tid >> 5;
+    auto ld8 = [&](const float* base, float* dst) {                              // 8 consecutive floats (32-byte aligned)
+        const float4 a = *reinterpret_cast<const float4*>(base), b = *reinterpret_cast<const float4*>(base + 4);
+        dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w; dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
+    };
+    auto st8 = [&](float* base, const float* src) {
+        *reinterpret_cast<float4*>(base) = make_float4(src[0], src[1], src[2], src[3]);
+        *reinterpret_cast<float4*>(base + 4) = make_float4(src[4], src[5], src[6], src[7]);
+    };
+    float x[CT];
 #pragma unroll
-    for (int c = 0; c < CB; ++c)
-        x[c] = s0_identity ? (c0 + c == k ? 1.f : 0.f) : (S0 ? S0[((size_t)bh * K + k) * V + c0 + c] : 0.f);
+    for (int c = 0; c < CT; ++c) x[c] = s0_identity ? (c0 + c == k ? 1.f : 0.f) : 0.f;
+    if (!s0_identity && S0) ld8(S0 + ((size_t)bh * K + k) * V + c0, x);
     const int first = reverse ? nseg - 1 : 0, step = reverse ? -1 : 1;
     if (lead_final) {          // F of the first segment in scan order IS the state leaving it (it was scanned for real)
         const size_t slot = (size_t)(bh * bh_stride + first * seg_stride);
-#pragma unroll
-        for (int c = 0; c < CB; ++c) x[c] = F[(slot * K + k) * V + c0 + c];
+        ld8(F + (slot * K + k) * V + c0, x);
     }
     for (int i = lead_final ? 1 : 0; i < nseg; ++i) {
         const int sgm = first + i * step;
         const size_t slot = (size_t)(bh * bh_stride + sgm * seg_stride);
         const bool apply = i + 1 < nseg || fin;
+        float acc[CT];
+#pragma unroll
+        for (int c = 0; c < CT; ++c) acc[c] = 0.f;
         if (apply) {
-            // stage the transition: forward needs T[k][j] at sT[j][k] (transposed), reverse T[j][k] at sT[j][k]
+            // stage the transition: forward needs T[k][j] at sT[j][k] (transposed), reverse T[j][k] at sT[j][k].
+            // Warp w reads rows w, w + 8, ...; a lane reads elements lane, lane + 32, ... of the row.
             const float* Tm = T + (size_t)(bh * t_bh_stride + sgm * t_seg_stride) * K * K;
-            // a warp reads one 512-byte row of T per load (lane = four consecutive j); sixteen rows are requested
-            // before the first is stored, so the staging costs two round trips to L2, not thirty-two
-#pragma unroll 1
-            for (int base = 0; base < 32; base += 16) {
-                float4 buf[16];
+            float buf[64];
 #pragma unroll
-                for (int u = 0; u < 16; ++u)
-                    buf[u] = __ldg(reinterpret_cast<const float4*>(Tm + (size_t)(warp + 4 * (base + u)) * K + 4 * lane));
+            for (int u = 0; u < 16; ++u)
 #pragma unroll
-                for (int u = 0; u < 16; ++u) {
-                    const int r = warp + 4 * (base + u);
-                    if (reverse) {
-                        sT[r][4 * lane] = buf[u].x; sT[r][4 * lane + 1] = buf[u].y;
-                        sT[r][4 * lane + 2] = buf[u].z; sT[r][4 * lane + 3] = buf[u].w;
-                    } else {
-                        sT[4 * lane][r] = buf[u].x; sT[4 * lane + 1][r] = buf[u].y;
-                        sT[4 * lane + 2][r] = buf[u].z; sT[4 * lane + 3][r] = buf[u].w;
-                    }
+                for (int q = 0; q < 4; ++q) buf[u * 4 + q] = __ldg(Tm + (size_t)(warp + 8 * u) * K + q * 32 + lane);
+            if (!s0_identity) ld8(F + (slot * K + k) * V + c0, acc);
+#pragma unroll
+            for (int u = 0; u < 16; ++u)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int r = warp + 8 * u, c = q * 32 + lane;
+                    if (reverse) sT[r][c] = buf[u * 4 + q];
+                    else sT[c][r] = buf[u * 4 + q];
                 }
-            }
         }
+        if (pre) {
+            float pv[CT];
+            ld8(pre + (slot * K + k) * V + c0, pv);
 #pragma unroll
-        for (int c = 0; c < CB; ++c) {
-            if (pre) x[c] += pre[(slot * K + k) * V + c0 + c];
-            if (Sin) Sin[(slot * K + k) * V + c0 + c] = x[c];
-            cur[k][c] = x[c];
+            for (int c = 0; c < CT; ++c) x[c] += pv[c];
         }
+        if (Sin) st8(Sin + (slot * K + k) * V + c0, x);
+        st8(&cur[k][ch * CT], x);
         __syncthreads();
         if (apply) {
-            float acc[CB];
-#pragma unroll
-            for (int c = 0; c < CB; ++c) acc[c] = s0_identity ? 0.f : F[(slot * K + k) * V + c0 + c];
 #pragma unroll 4
             for (int j = 0; j < K; ++j) {
                 const float t = sT[j][k];
-#pragma unroll
-                for (int c4 = 0; c4 < CB / 4; ++c4) {             // the same address for all lanes: a broadcast
-                    const float4 v = *reinterpret_cast<const float4*>(&cur[j][c4 * 4]);
-                    acc[c4 * 4] = fmaf(t, v.x, acc[c4 * 4]); acc[c4 * 4 + 1] = fmaf(t, v.y, acc[c4 * 4 + 1]);
-                    acc[c4 * 4 + 2] = fmaf(t, v.z, acc[c4 * 4 + 2]); acc[c4 * 4 + 3] = fmaf(t, v.w, acc[c4 * 4 + 3]);
-                }
+                const float4 v0 = *reinterpret_cast<const float4*>(&cur[j][ch * CT]);        // the same address for a
+                const float4 v1 = *reinterpret_cast<const float4*>(&cur[j][ch * CT + 4]);    // whole warp: a broadcast
+                acc[0] = fmaf(t, v0.x, acc[0]); acc[1] = fmaf(t, v0.y, acc[1]);
+                acc[2] = fmaf(t, v0.z, acc[2]); acc[3] = fmaf(t, v0.w, acc[3]);
+                acc[4] = fmaf(t, v1.x, acc[4]); acc[5] = fmaf(t, v1.y, acc[5]);
+                acc[6] = fmaf(t, v1.z, acc[6]); acc[7] = fmaf(t, v1.w, acc[7]);
             }
 #pragma unroll
-            for (int c = 0; c < CB; ++c) x[c] = acc[c];
+            for (int c = 0; c < CT; ++c) x[c] = acc[c];
         }
         __syncthreads();
     }
     if (fin) {
+        if (post) {
+            float pv[CT];
+            ld8(post + ((size_t)bh * K + k) * V + c0, pv);
 #pragma unroll
-        for (int c = 0; c < CB; ++c)
-            fin[((size_t)bh * K + k) * V + c0 + c] = x[c] + (post ? post[((size_t)bh * K + k) * V + c0 + c] : 0.f);
+            for (int c = 0; c < CT; ++c) x[c] += pv[c];
+        }
+        st8(fin + ((size_t)bh * K + k) * V + c0, x);
     }
 }
 
@@ -1562,7 +1595,7 @@ int tc_compose_states(const float* T, const float* F, const float* S0, const flo
         if (rc != HDLA_OK) return rc;
         attr_dev = dev;
     }
-    compose_segments_kernel<<<dim3(BH, V / kComposeCols), 128, kComposeSmem, st>>>(T, F, S0, nullptr, out, count, reverse,
+    compose_segments_kernel<<<dim3(BH, V / kComposeCols), 256, kComposeSmem, st>>>(T, F, S0, nullptr, out, count, reverse,
                                                                                  0, 0, 1, f_stride, 1, t_stride, pre, post);
     HDLA_CHECK_LAUNCH("compose_segments_kernel");
     return HDLA_OK;
@@ -1575,8 +1608,13 @@ int tc_wait_timeout_probe(int* status, unsigned long long budget_ns, cudaStream_
 }
 
 bool tc_supported(const HdlaDims& d) {
+    // head dims below 128 run on the same 128-wide tiles, padded with zeros (multiples of 8: whole 16-byte chunks);
+    // phased calls (context parallelism) exchange K x V states between devices and need the full 128 x 128
+    const bool dims_ok = d.K % 8 == 0 && d.V % 8 == 0 && d.K >= 8 && d.V >= 8 && d.K <= K && d.V <= V;
+    const bool full = d.K == K && d.V == V;
+    if ((d.flags & HDLA_PHASE_MASK) != HDLA_PHASE_ALL && !full) return false;
     return d.dtype == HDLA_BF16 && !(d.flags & HDLA_FLAG_FORCE_SIMT) && effective_chunk(d.T, d.C) == C && d.R == R &&
-           d.K == K && d.V == V && (long long)d.B * d.H * ((d.T + C - 1) / C) < 0x7fffffffLL;
+           dims_ok && (long long)d.B * d.H * ((d.T + C - 1) / C) < 0x7fffffffLL;
 }
 
 size_t tc_workspace_bytes(const HdlaDims& d, int with_backward) {
@@ -1592,7 +1630,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     const TcPlan pl = make_tc_plan(d);
     // a workspace sized for the backward pass also receives what only the backward kernels read
     const bool save_bwd = ws_bytes >= pl.total;
-    const bool unfused = !(d.flags & HDLA_FLAG_FUSED_PREP);
+    const bool unfused = !(d.flags & HDLA_FLAG_FUSED_PREP) || d.K != K || d.V != V;    // the one-kernel form needs full head dims
     static thread_local int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1622,7 +1660,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             TRY(tc_launch_chunk_prep(pl, d, q, k, v, a, b, gk, scale, ws, save_bwd, st));
         } else {
             PrepP pp{(bp)q, (bp)k, (bp)v, (bp)a, (bp)b, gk, U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc),
-                     F(pl.E), (__nv_bfloat16*)(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status};
+                     F(pl.E), (__nv_bfloat16*)(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status, d.K, d.V};
             prep_hat_kernel<<<G, 128, 0, st>>>(pp);
             HDLA_CHECK_LAUNCH("prep_hat_kernel");
             GramP gp{U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Aak), U4(pl.Aab), status};
@@ -1643,6 +1681,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         sp.init = init; sp.CK = ck; sp.Y = y; sp.fin = fin; sp.fin2 = fin2;
         sp.NT = pl.NT; sp.reverse = 0; sp.status = status; sp.add_stride = 1; sp.r1_stride = 1; sp.no_store = no_store;
         sp.nseg = 1; sp.seg_len = pl.NT; sp.zero_tile = U4(pl.zero);
+        sp.Kd = d.K; sp.Vd = d.V;
         return sp;
     };
     if (phase == HDLA_PHASE_TRANSITION) {
@@ -1656,7 +1695,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1; s1.fin_transition = F(pl.Tseg);
             scan_tc_kernel<<<dim3(pl.BH * pl.nseg, 2), 256, 196608, st>>>(s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
-            compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, nullptr, ht,
+            compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, nullptr, ht,
                                                                          pl.nseg, 0, 1, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
@@ -1671,7 +1710,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     if (phase == HDLA_PHASE_STATE) {
         if (!ht) return fail(HDLA_ERR_INVALID, "state pass needs the output pointer (ht)");
         if (pl.nseg > 1) {                    // affine maps of the segments are in the workspace (TRANSITION phase)
-            compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), h0, nullptr, ht,
+            compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), h0, nullptr, ht,
                                                                          pl.nseg, 0, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
@@ -1690,7 +1729,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         scan_tc_kernel<<<dim3(pl.BH * (pl.nseg - 1), 2), 256, 196608, st>>>(s1);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         // ... the state entering every later segment follows from the first segment's final state ...
-        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
+        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
                                                                      pl.nseg, 0, 0, 1, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         // ... and the remaining segments are scanned for real at once
@@ -1708,7 +1747,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
         }
         // ... composed into the state entering every segment ...
-        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), nullptr, pl.nseg, 0, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
+        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), nullptr, pl.nseg, 0, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         // ... and the real scan of all segments at once
         ScanTcP s2 = scan_params(F(pl.Sin), U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
@@ -1722,7 +1761,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     }
     if (need_o) {
         OutP op{U4(pl.Qh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Vc), U4(pl.Hs), U4(pl.V2), (__nv_bfloat16*)o, d.T, d.H,
-                pl.NT, status};
+                pl.NT, status, d.V};
         out_tc_kernel<<<G, 128, 73728, st>>>(op);
         HDLA_CHECK_LAUNCH("out_tc_kernel");
     }
@@ -1749,7 +1788,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
 
     if (phase == HDLA_PHASE_ALL || phase == HDLA_PHASE_PRE) {
         DauP dp{(const __nv_bfloat16*)d_o, U4(pl.Vc), U4(pl.V2), U4(pl.Aqb), U4(pl.dOc), U4(pl.dAqk), U4(pl.dAqb),
-                U4(pl.DV2), d.T, d.H, pl.NT, status};
+                U4(pl.DV2), d.T, d.H, pl.NT, status, d.V};
         dau_tc_kernel<<<G, 128, 81920, st>>>(dp);
         HDLA_CHECK_LAUNCH("dau_tc_kernel");
         if (phase == HDLA_PHASE_PRE) return HDLA_OK;
@@ -1762,6 +1801,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         sp.Hs = U4(pl.Hs); sp.HT = F(pl.HT); sp.dgl = dgl;
         sp.NT = pl.NT; sp.reverse = 1; sp.status = status; sp.add_stride = 1; sp.r1_stride = 1; sp.no_store = no_store;
         sp.nseg = 1; sp.seg_len = pl.NT; sp.zero_tile = U4(pl.zero);
+        sp.Kd = d.K; sp.Vd = d.V;
         return sp;
     };
     if (phase == HDLA_PHASE_STATE) {
@@ -1772,7 +1812,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1;
             scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
-            compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), dht, nullptr, dh0,
+            compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), dht, nullptr, dh0,
                                                                          pl.nseg, 1, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
@@ -1791,7 +1831,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         s1.seg_off = 1; s1.seg_cnt = pl.nseg - 1; s1.lead_real = 1; s1.lead_init = dht;
         scan_tc_kernel<<<pl.BH * (pl.nseg - 1), 256, 196608, st>>>(s1);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
-        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
+        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
                                                                      pl.nseg, 1, 0, 1, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         ScanTcP s2 = rscan_params(F(pl.Sin), U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
@@ -1807,7 +1847,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
         }
-        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 128, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), nullptr, pl.nseg, 1, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
+        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), nullptr, pl.nseg, 1, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         ScanTcP s2 = rscan_params(F(pl.Sin), U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
         s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;
@@ -1828,7 +1868,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     GradP gp{U4(pl.Hs), U4(pl.Bh), U4(pl.dOc), U4(pl.Kh), U4(pl.dAqb), U4(pl.dAqk), U4(pl.DE), U4(pl.dP), U4(pl.Aak),
              U4(pl.Aqk), U4(pl.dW), U4(pl.M), U4(pl.dAab), U4(pl.dAak), U4(pl.V2), U4(pl.Ah), U4(pl.Qh), U4(pl.Vc),
              (bp)(ws + pl.ghat), F(pl.E), F(pl.dgl), (bp)dq, (bp)dk, (bp)dv, (bp)da, (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype,
-             status, (long long)G};
+             status, (long long)G, d.K, d.V};
     const unsigned grad_grid = G < (unsigned)sm_count() ? G : (unsigned)sm_count();    // one persistent CTA per SM
     grad_tc_kernel<<<grad_grid, 544, kGradSmem, st>>>(gp);
     HDLA_CHECK_LAUNCH("grad_tc_kernel");

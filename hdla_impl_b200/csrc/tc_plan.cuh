@@ -43,7 +43,7 @@ inline TcPlan make_tc_plan(const HdlaDims& d) {
     // forward region: what the scan and the output kernel read.  The fused preparation kernel (HDLA_FLAG_FUSED_PREP)
     // keeps Aab on chip and writes Ah, Aak, M, P and the un-gating factors only for a backward pass, so with it
     // those live in the backward region; the four-kernel preparation passes them from kernel to kernel.
-    const bool fused = (d.flags & HDLA_FLAG_FUSED_PREP) != 0;
+    const bool fused = (d.flags & HDLA_FLAG_FUSED_PREP) != 0 && d.K == K && d.V == V;    // (it needs full head dims)
     p.Qh = take(16384); p.Kh = take(16384); p.Bh = take(32768); p.Vc = take(16384);
     p.E = take(K * 4);
     p.Aqk = take(8192); p.Aqb = take(16384);

@@ -30,14 +30,21 @@ def contiguous(fn):
     return wrapper
 
 
+def _tc_shape(q, v, RANK_AB: int) -> bool:
+    """Whether the bf16 tensor-core pipeline takes this problem (at its own chunk of 64): bf16, rank 2, head dims
+    that are multiples of 8 up to 128 (smaller ones run zero-padded on the same 128-wide tiles)."""
+    T, K, V = q.shape[1], q.shape[-1], v.shape[-1]
+    return (q.dtype == torch.bfloat16 and RANK_AB == 2 and K % 8 == 0 and V % 8 == 0 and 8 <= K <= 128
+            and 8 <= V <= 128 and T > 32)
+
+
 def _internal_chunk(q, v, RANK_AB: int, chunk_size: int) -> int:
     """Chunk size actually used.  The operator's result does not depend on the chunk size (it only sets how
     the recurrence is blocked), and the reference layer asks for 16 (HRDPLR/hdla_custom.py:308) only because its
     own backward is limited to that.  Problems the tensor-core pipeline supports are therefore run at its chunk
     of 64 whatever was requested; ``HDLA_HONOR_CHUNK=1`` keeps the requested value."""
-    T, K, V = q.shape[1], q.shape[-1], v.shape[-1]
-    if (os.environ.get("HDLA_HONOR_CHUNK", "0") != "1" and q.dtype == torch.bfloat16 and RANK_AB == 2
-            and K == 128 and V == 128 and T > 32 and os.environ.get("HDLA_FORCE_SIMT", "0") != "1"):
+    if (os.environ.get("HDLA_HONOR_CHUNK", "0") != "1" and _tc_shape(q, v, RANK_AB)
+            and os.environ.get("HDLA_FORCE_SIMT", "0") != "1"):
         return 64
     return chunk_size
 

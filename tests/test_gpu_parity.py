@@ -281,6 +281,34 @@ def test_bf16_tensor_core_path_at_reference_decay_strength(dev):
     assert hrdplr._status_state(dev)["decay"] > 40.0         # the decay really was of the reference's strength
 
 
+@pytest.mark.parametrize("B,T,H,K,V", [(2, 512, 2, 64, 64), (1, 300, 3, 128, 64), (1, 256, 2, 64, 128),
+                                       (1, 200, 2, 96, 48), (1, 2100, 2, 64, 64)])
+def test_bf16_head_dims_below_128_run_on_tensor_cores(dev, B, T, H, K, V):
+    """The reference handles any K <= 256 and any V (HRDPLR/fwd_func.py:229-241).  Head dims below 128 (multiples
+    of 8) run on the tcgen05 pipeline too, zero-padded to its 128-wide tiles: forward + backward with an initial
+    state and a final-state gradient against the oracle, ragged last chunk and two-level scan included."""
+    import ctypes as C
+    from hdla_impl_b200 import _lib, hrdplr
+    import hdla_impl_b200 as HD
+    x = make_inputs(B, T, H, K, V, R, seed=51, dtype=torch.bfloat16, gk_div=4.0, h0_std=0.3, with_dht=True)
+    x["gk"] = x["gk"].float()
+    d = hrdplr._dims(x["q"], x["v"], x["a"], x["gk"], R, 64)
+    assert _lib.load().hdla_chunk_uses_tensor_cores(C.byref(d)) == 1
+    n0 = _lib.kernel_launches()
+    got = run_chunk(x, dev, K ** -0.5, 64, True, True, torch.bfloat16)
+    assert _lib.kernel_launches() - n0 <= 14                   # the tensor-core pipeline, not the 43-launch fp32 one
+    HD.check_status(dev, wait=True)
+    ref = oracle_chunk(x, K ** -0.5, True, True, torch.bfloat16)
+    assert_close(got, ref, 2e-2, f"K={K} V={V}")
+    # outputs must be dense [.., K] / [.., V] tensors with nothing written past their ends (NaN canaries would show
+    # in the comparison above); and a forward-only call agrees bit for bit
+    with torch.no_grad():
+        o2, ht2 = HD.chunk_hrdplr_delta_rule(*[x[n].to(dev) for n in ("q", "k", "v", "a", "b", "gk")], R,
+                                             scale=K ** -0.5, initial_state=x["h0"].to(dev), output_final_state=True,
+                                             chunk_size=64)
+    assert torch.equal(o2, got["o"]) and torch.equal(ht2, got["ht"])
+
+
 def test_non_contiguous_inputs_and_autocast(dev):
     """The entry point makes its tensor arguments contiguous and is autocast-aware like the reference's
     decorators (HRDPLR/utils.py:7-25, HRDPLR/hrdplr.py:104-105,148-149)."""
