@@ -30,7 +30,18 @@ EXPORTS = (
 
 
 class HdlaDims(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("B", "T", "H", "K", "V", "R", "C", "dtype", "gk_dtype", "flags")]
+    """Mirror of the C struct (include/hdla.h).  ``cu_seqlens`` points to HOST memory; ``with_seqlens`` keeps the
+    array it points to alive for as long as the structure lives."""
+    _fields_ = ([(n, C.c_int32) for n in ("B", "T", "H", "K", "V", "R", "C", "dtype", "gk_dtype", "flags",
+                                          "n_seqs", "reserved_")]
+                + [("cu_seqlens", C.POINTER(C.c_int64))])
+
+    def with_seqlens(self, offsets) -> "HdlaDims":
+        arr = (C.c_int64 * len(offsets))(*[int(x) for x in offsets])
+        self._keep = arr
+        self.n_seqs = len(offsets) - 1
+        self.cu_seqlens = C.cast(arr, C.POINTER(C.c_int64))
+        return self
 
 
 _lock = threading.Lock()

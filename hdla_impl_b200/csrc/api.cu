@@ -28,6 +28,16 @@ int check_common(const HdlaDims* d, bool chunked) {
     if (chunked && (d->C & (d->C - 1))) return fail(HDLA_ERR_UNSUPPORTED, "chunk size C=%d must be a power of two", d->C);
     if (d->dtype != HDLA_F32 && d->dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", d->dtype);
     if (d->gk_dtype != HDLA_F32 && d->gk_dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "gk_dtype %d", d->gk_dtype);
+    if (chunked && d->cu_seqlens) {
+        if (d->B != 1) return fail(HDLA_ERR_INVALID, "cu_seqlens needs B == 1, got B=%d", d->B);
+        if (d->n_seqs < 1) return fail(HDLA_ERR_INVALID, "cu_seqlens given with n_seqs=%d", d->n_seqs);
+        if (d->cu_seqlens[0] != 0 || d->cu_seqlens[d->n_seqs] != d->T)
+            return fail(HDLA_ERR_INVALID, "cu_seqlens must start at 0 and end at T=%d", d->T);
+        for (int s = 0; s < d->n_seqs; ++s)
+            if (d->cu_seqlens[s + 1] < d->cu_seqlens[s]) return fail(HDLA_ERR_INVALID, "cu_seqlens must not decrease");
+    } else if (chunked && d->n_seqs != 0) {
+        return fail(HDLA_ERR_INVALID, "n_seqs=%d without cu_seqlens", d->n_seqs);
+    }
     return HDLA_OK;
 }
 
@@ -57,6 +67,11 @@ static size_t tc_region_bytes(const HdlaDims& d, int with_backward) {
 
 size_t hdla_chunk_workspace_bytes(const HdlaDims* dims, int with_backward) {
     if (check_common(dims, true) != HDLA_OK) return 0;
+    if (dims->cu_seqlens && !tc_supported(*dims)) {
+        fail(HDLA_ERR_UNSUPPORTED, "variable-length batches (cu_seqlens) need the bf16 tensor-core pipeline "
+                                   "(bf16, chunk 64, R=2, K and V multiples of 8 up to 128)");
+        return 0;
+    }
     const size_t simt = simt_workspace_floats(*dims, with_backward) * sizeof(float);
     if (simt == 0) return 0;
     if (tc_supported(*dims)) return tc_region_bytes(*dims, with_backward);

@@ -39,6 +39,7 @@ struct ChunkPrepP {
     int T, H, NT, gdt;
     int save_bwd;                         // also store Ah, Aak, M, P, ghat (read only by the backward kernels)
     int* status;
+    const int2* chunk_tab;                // variable-length batches: (first token, tokens) per chunk, else null
 };
 
 struct In6 { uint4 q, k, a0, a1, b0, b1; };
@@ -121,7 +122,8 @@ struct TileCoord { int b, h, t0, valid; };
 __device__ __forceinline__ TileCoord tile_coord(const ChunkPrepP& p, long long g) {
     const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
     TileCoord c;
-    c.b = bh / p.H; c.h = bh % p.H; c.t0 = n * C; c.valid = min(C, p.T - c.t0);
+    c.b = bh / p.H; c.h = bh % p.H;
+    chunk_tokens(p.chunk_tab, n, p.T, c.t0, c.valid);
     return c;
 }
 
@@ -569,7 +571,8 @@ int tc_launch_chunk_prep(const TcPlan& pl, const HdlaDims& d, const void* q, con
                   U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Aak), U4(pl.M),
                   U4(pl.W), U4(pl.P), U4(pl.U), reinterpret_cast<float*>(ws + pl.E),
                   reinterpret_cast<__nv_bfloat16*>(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, save_bwd ? 1 : 0,
-                  reinterpret_cast<int*>(ws + pl.status)};
+                  reinterpret_cast<int*>(ws + pl.status),
+                  pl.nseq ? reinterpret_cast<const int2*>(ws + pl.chunk_tab) : nullptr};
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     const long long slots = 2LL * sms;                     // two CTAs per SM, persistent

@@ -15,6 +15,8 @@
 // bulk asynchronous copies; all products run on tcgen05.mma with fp32 accumulation in TMEM.
 #include <cstring>
 
+#include <vector>
+
 #include "tc_plan.cuh"
 
 namespace hdla {
@@ -39,6 +41,7 @@ struct PrepP {
     int T, H, NT, gdt;
     int* status;
     int Kd, Vd;                           // head dims of the public tensors (multiples of 8, <= 128); the tiles are padded with zeros
+    const int2* chunk_tab;                // variable-length batches: (first token, tokens) per chunk, else null
 };
 
 // the seven 16-byte input pieces one thread handles per step: (row r, column group kc) of q, k, v, a0, a1, b0, b1
@@ -71,8 +74,8 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
     const long long g = blockIdx.x;
     const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
     const int b = bh / p.H, h = bh % p.H;
-    const int t0 = n * C;
-    const int valid = min(C, p.T - t0);
+    int t0, valid;
+    chunk_tokens(p.chunk_tab, n, p.T, t0, valid);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // The kernel is a stream: keep loads in flight at all times. The first step's operand pieces are requested
     // before the decay sums (they do not depend on them), and inside the loop the next step's pieces are
@@ -574,6 +577,10 @@ struct ScanTcP {
     // head dims of the PUBLIC state tensors (h0 / ht / dht / dh0, [.., Kd, Vd]); states kept in the workspace
     // (the by-slot ones, the transition result and fin2) are always K x V = 128 x 128
     int Kd, Vd;
+    // variable-length batches: pair bh = (sequence, head) scans chunks seq_tab[sequence] = (first chunk, chunks) of
+    // head h's row of tiles (tile = h * NT + chunk); null for uniform batches (pair bh scans tiles bh * NT ..)
+    const int2* seq_tab;
+    int H;
 };
 
 __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
@@ -602,9 +609,16 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row = (warp & 3) * 32 + lane;
     const int half = warp >> 2;
+    TLS(0);
     if (warp == 0) { tmem_alloc(&tmem_s, 256); tmem_relinquish(); }
-    const long long g0 = (long long)bh * p.NT;
-    const int n_lo = seg * p.seg_len, n_hi = min(p.NT, n_lo + p.seg_len);
+    long long g0 = (long long)bh * p.NT;
+    int NTp = p.NT;                               // chunks of this pair
+    if (p.seq_tab) {
+        const int2 e = p.seq_tab[bh / p.H];
+        g0 = (long long)(bh % p.H) * p.NT + e.x;
+        NTp = e.y;
+    }
+    const int n_lo = seg * p.seg_len, n_hi = min(NTp, n_lo + p.seg_len);
     const int steps = n_hi - n_lo;
     const int n_first = p.reverse ? n_hi - 1 : n_lo, dn = p.reverse ? -1 : 1;
     if (tid == 0) {
@@ -642,7 +656,9 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     const Tile tA1 = t8::tile(sA1, 128), tL1 = t8::tile(sL1, 64), tR1 = t8::tile(sR1, 64), tL2 = t8::tile(sL2, 128),
                tT = t8::tile(sT, 128), tY = t8::tile(sY, 128);
     float e_next = steps > 0 ? p.E[(size_t)(g0 + n_first) * K + row] : 0.f;
+    TLS(1);
     for (int it = 0; it < steps; ++it) {
+        if (it >= 1 && it <= 10) TLS(1 + it);
         const int n = n_first + it * dn;
         const long long g = g0 + n;
         const uint32_t ph = it & 1;
@@ -671,7 +687,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         }
         float part = 0.f;
         if (p.reverse && !p.no_store) {       // dgl = rowsum(dS (.) S_{n+1}), computed while the product runs
-            if (n + 1 < p.NT) {
+            if (n + 1 < NTp) {
                 const float inv = 1.f / p.E[(size_t)(g + 1) * K + row];
 #pragma unroll
                 for (int c8 = 0; c8 < 8; ++c8) {
@@ -741,6 +757,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         }
         tc_fence_before();
     }
+    TLS(12);
     const bool ends_scan = p.reverse ? (seg == 0) : (seg == p.nseg - 1);
     if (!p.fin_last_only || ends_scan) {
         const size_t fs = p.fin_by_slot ? (size_t)slot : (size_t)bh;
@@ -755,6 +772,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         }
     }
     __syncthreads();
+    TLS(13);
     if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
@@ -947,6 +965,7 @@ struct DauP {
     int T, H, NT;
     int* status;
     int Vd;
+    const int2* chunk_tab;
 };
 
 __global__ void __launch_bounds__(128) dau_tc_kernel(DauP p) {
@@ -970,15 +989,17 @@ __global__ void __launch_bounds__(128) dau_tc_kernel(DauP p) {
     {
         const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
         const int b = bh / p.H, h = bh % p.H;
+        int t0, valid;
+        chunk_tokens(p.chunk_tab, n, p.T, t0, valid);
         uint4 c[8];                                    // all eight loads in flight before the first store
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             const int blk = warp * 8 + it;
             const int r = (blk >> 2) * 8 + (lane & 7);
             const int kc = (blk & 3) * 4 + (lane >> 3);
-            const int t = n * C + r;
+            const int t = t0 + r;
             c[it] = make_uint4(0, 0, 0, 0);
-            if (t < p.T && kc * 8 < p.Vd)
+            if (r < valid && kc * 8 < p.Vd)
                 c[it] = __ldg(reinterpret_cast<const uint4*>(p.d_o + (((size_t)b * p.T + t) * p.H + h) * p.Vd + kc * 8));
         }
 #pragma unroll
@@ -1052,6 +1073,7 @@ struct OutP {
     int T, H, NT;
     int* status;
     int Vd;
+    const int2* chunk_tab;
 };
 
 __global__ void __launch_bounds__(128) out_tc_kernel(OutP p) {
@@ -1099,13 +1121,15 @@ __global__ void __launch_bounds__(128) out_tc_kernel(OutP p) {
     if (warp < 2) {
         const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
         const int b = bh / p.H, h = bh % p.H;
-        const int t = n * C + tid;
+        int t0, valid;
+        chunk_tokens(p.chunk_tab, n, p.T, t0, valid);
+        const int t = t0 + tid;
         uint4* dst = reinterpret_cast<uint4*>(p.o + (((size_t)b * p.T + t) * p.H + h) * p.Vd);
 #pragma unroll 1
         for (int hh = 0; hh < 2; ++hh) {
             float f[64];
             tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
-            if (t < p.T) {
+            if (tid < valid) {
 #pragma unroll
                 for (int cg = 0; cg < 8; cg += 2) {        // whole 32-byte sectors per lane (lanes are 4 KB apart)
                     const int col = (hh * 8 + cg) * 8;
@@ -1165,6 +1189,7 @@ struct GradP {
     int* status;
     long long G;           // number of tiles; the grid is persistent
     int Kd, Vd;            // head dims of the public tensors (channels beyond them are padding and are not written)
+    const int2* chunk_tab;
 };
 
 template <bool A_MN, bool B_MN>
@@ -1304,10 +1329,11 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         const int b = bh / p.H, h = bh % p.H;
         const int k = tid & 127, wg = tid >> 7;
         const int i_lo = 48 - 16 * wg;
-        const int t_left = p.T - n * C;                               // tokens of this chunk that exist
+        int t0, t_left;                                               // first token / tokens of this chunk that exist
+        chunk_tokens(p.chunk_tab, n, p.T, t0, t_left);
         const size_t tok_stride = (size_t)p.H * p.Kd;                 // elements between tokens in [B,T,H,K]
-        const size_t base_qk = (((size_t)b * p.T + (size_t)n * C + i_lo) * p.H + h) * p.Kd + k;
-        const size_t base_ab = (((size_t)b * p.T + (size_t)n * C + i_lo) * R * p.H + h) * p.Kd + k;
+        const size_t base_qk = (((size_t)b * p.T + (size_t)t0 + i_lo) * p.H + h) * p.Kd + k;
+        const size_t base_ab = (((size_t)b * p.T + (size_t)t0 + i_lo) * R * p.H + h) * p.Kd + k;
         const bool k_ok = k < p.Kd;                                   // this thread's channel exists in the public tensors
         // eg[j] = e^{gi - half} of token i_lo + j - 1 (the token before the chunk has e^{ge - half} = e^{-half})
         float eg[17];
@@ -1341,8 +1367,8 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                const int t = n * C + wg * 16 + j;
-                if (t < p.T && k < p.Vd) p.dv[(((size_t)b * p.T + t) * p.H + h) * p.Vd + k] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                const int t = t0 + wg * 16 + j;
+                if (wg * 16 + j < t_left && k < p.Vd) p.dv[(((size_t)b * p.T + t) * p.H + h) * p.Vd + k] = __float2bfloat16_rn(__uint_as_float(v[j]));
             }
         }
         // ---- after P3: da = e^{ge-half} dAh
@@ -1417,8 +1443,8 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         for (int w = 0; w < wg; ++w) add += group_total[w][k];
 #pragma unroll 4
         for (int jj = 0; jj < 16; ++jj) {
-            const int t = n * C + i_lo + jj;
-            if (t < p.T && k_ok) st_elem(p.dgk, (((size_t)b * p.T + t) * p.H + h) * p.Kd + k, p.gdt, dgk_loc[jj * K] + add);
+            const int t = t0 + i_lo + jj;
+            if (i_lo + jj < t_left && k_ok) st_elem(p.dgk, (((size_t)b * p.T + t) * p.H + h) * p.Kd + k, p.gdt, dgk_loc[jj * K] + add);
         }
     }
     // every thread is done with this tile's slots and accumulators before the next tile's first loads and products
@@ -1612,7 +1638,7 @@ bool tc_supported(const HdlaDims& d) {
     // phased calls (context parallelism) exchange K x V states between devices and need the full 128 x 128
     const bool dims_ok = d.K % 8 == 0 && d.V % 8 == 0 && d.K >= 8 && d.V >= 8 && d.K <= K && d.V <= V;
     const bool full = d.K == K && d.V == V;
-    if ((d.flags & HDLA_PHASE_MASK) != HDLA_PHASE_ALL && !full) return false;
+    if ((d.flags & HDLA_PHASE_MASK) != HDLA_PHASE_ALL && (!full || d.cu_seqlens)) return false;
     return d.dtype == HDLA_BF16 && !(d.flags & HDLA_FLAG_FORCE_SIMT) && effective_chunk(d.T, d.C) == C && d.R == R &&
            dims_ok && (long long)d.B * d.H * ((d.T + C - 1) / C) < 0x7fffffffLL;
 }
@@ -1652,15 +1678,32 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     const unsigned G = (unsigned)pl.G;
     typedef const __nv_bfloat16* bp;
     const int phase = d.flags & HDLA_PHASE_MASK;
+    const int2* chunk_tab = pl.nseq ? reinterpret_cast<const int2*>(ws + pl.chunk_tab) : nullptr;
+    const int2* seq_tab = pl.nseq ? reinterpret_cast<const int2*>(ws + pl.seq_tab) : nullptr;
     if (phase == HDLA_PHASE_ALL || phase == HDLA_PHASE_PRE) {
         cudaError_t e = cudaMemsetAsync(ws + pl.status, 0, 256, st);
         if (e == cudaSuccess) e = cudaMemsetAsync(ws + pl.zero, 0, 32768, st);
         if (e != cudaSuccess) return fail(HDLA_ERR_CUDA, "workspace clear: %s", cudaGetErrorString(e));
+        if (pl.nseq) {
+            // packed variable-length batch: which tokens every chunk covers and which chunks every sequence owns.
+            // (The source is pageable host memory, which cudaMemcpyAsync stages before it returns.)
+            std::vector<int2> chunks, seqs;
+            chunks.reserve(pl.NT); seqs.reserve(pl.nseq);
+            for (int s_ = 0; s_ < pl.nseq; ++s_) {
+                const long long lo = d.cu_seqlens[s_], hi = d.cu_seqlens[s_ + 1];
+                seqs.push_back(make_int2((int)chunks.size(), (int)((hi - lo + C - 1) / C)));
+                for (long long t = lo; t < hi; t += C) chunks.push_back(make_int2((int)t, (int)(hi - t < C ? hi - t : C)));
+            }
+            if (!chunks.empty()) e = cudaMemcpyAsync(ws + pl.chunk_tab, chunks.data(), chunks.size() * sizeof(int2), cudaMemcpyHostToDevice, st);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(ws + pl.seq_tab, seqs.data(), seqs.size() * sizeof(int2), cudaMemcpyHostToDevice, st);
+            if (e != cudaSuccess) return fail(HDLA_ERR_CUDA, "chunk tables: %s", cudaGetErrorString(e));
+            if (pl.G == 0) return HDLA_OK;
+        }
         if (!unfused) {
             TRY(tc_launch_chunk_prep(pl, d, q, k, v, a, b, gk, scale, ws, save_bwd, st));
         } else {
             PrepP pp{(bp)q, (bp)k, (bp)v, (bp)a, (bp)b, gk, U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc),
-                     F(pl.E), (__nv_bfloat16*)(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status, d.K, d.V};
+                     F(pl.E), (__nv_bfloat16*)(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status, d.K, d.V, chunk_tab};
             prep_hat_kernel<<<G, 128, 0, st>>>(pp);
             HDLA_CHECK_LAUNCH("prep_hat_kernel");
             GramP gp{U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Aak), U4(pl.Aab), status};
@@ -1681,7 +1724,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         sp.init = init; sp.CK = ck; sp.Y = y; sp.fin = fin; sp.fin2 = fin2;
         sp.NT = pl.NT; sp.reverse = 0; sp.status = status; sp.add_stride = 1; sp.r1_stride = 1; sp.no_store = no_store;
         sp.nseg = 1; sp.seg_len = pl.NT; sp.zero_tile = U4(pl.zero);
-        sp.Kd = d.K; sp.Vd = d.V;
+        sp.Kd = d.K; sp.Vd = d.V; sp.seq_tab = seq_tab; sp.H = d.H;
         return sp;
     };
     if (phase == HDLA_PHASE_TRANSITION) {
@@ -1761,7 +1804,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     }
     if (need_o) {
         OutP op{U4(pl.Qh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Vc), U4(pl.Hs), U4(pl.V2), (__nv_bfloat16*)o, d.T, d.H,
-                pl.NT, status, d.V};
+                pl.NT, status, d.V, chunk_tab};
         out_tc_kernel<<<G, 128, 73728, st>>>(op);
         HDLA_CHECK_LAUNCH("out_tc_kernel");
     }
@@ -1785,10 +1828,13 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     int* status = reinterpret_cast<int*>(ws + pl.status);
     const unsigned G = (unsigned)pl.G;
     typedef __nv_bfloat16* bp;
+    const int2* chunk_tab = pl.nseq ? reinterpret_cast<const int2*>(ws + pl.chunk_tab) : nullptr;
+    const int2* seq_tab = pl.nseq ? reinterpret_cast<const int2*>(ws + pl.seq_tab) : nullptr;
+    if (pl.nseq && pl.G == 0) return HDLA_OK;
 
     if (phase == HDLA_PHASE_ALL || phase == HDLA_PHASE_PRE) {
         DauP dp{(const __nv_bfloat16*)d_o, U4(pl.Vc), U4(pl.V2), U4(pl.Aqb), U4(pl.dOc), U4(pl.dAqk), U4(pl.dAqb),
-                U4(pl.DV2), d.T, d.H, pl.NT, status, d.V};
+                U4(pl.DV2), d.T, d.H, pl.NT, status, d.V, chunk_tab};
         dau_tc_kernel<<<G, 128, 81920, st>>>(dp);
         HDLA_CHECK_LAUNCH("dau_tc_kernel");
         if (phase == HDLA_PHASE_PRE) return HDLA_OK;
@@ -1801,7 +1847,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         sp.Hs = U4(pl.Hs); sp.HT = F(pl.HT); sp.dgl = dgl;
         sp.NT = pl.NT; sp.reverse = 1; sp.status = status; sp.add_stride = 1; sp.r1_stride = 1; sp.no_store = no_store;
         sp.nseg = 1; sp.seg_len = pl.NT; sp.zero_tile = U4(pl.zero);
-        sp.Kd = d.K; sp.Vd = d.V;
+        sp.Kd = d.K; sp.Vd = d.V; sp.seq_tab = seq_tab; sp.H = d.H;
         return sp;
     };
     if (phase == HDLA_PHASE_STATE) {
@@ -1868,7 +1914,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     GradP gp{U4(pl.Hs), U4(pl.Bh), U4(pl.dOc), U4(pl.Kh), U4(pl.dAqb), U4(pl.dAqk), U4(pl.DE), U4(pl.dP), U4(pl.Aak),
              U4(pl.Aqk), U4(pl.dW), U4(pl.M), U4(pl.dAab), U4(pl.dAak), U4(pl.V2), U4(pl.Ah), U4(pl.Qh), U4(pl.Vc),
              (bp)(ws + pl.ghat), F(pl.E), F(pl.dgl), (bp)dq, (bp)dk, (bp)dv, (bp)da, (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype,
-             status, (long long)G, d.K, d.V};
+             status, (long long)G, d.K, d.V, chunk_tab};
     const unsigned grad_grid = G < (unsigned)sm_count() ? G : (unsigned)sm_count();    // one persistent CTA per SM
     grad_tc_kernel<<<grad_grid, 544, kGradSmem, st>>>(gp);
     HDLA_CHECK_LAUNCH("grad_tc_kernel");
@@ -1912,6 +1958,9 @@ int tc_debug_buffer(const HdlaDims& d, const unsigned char* ws, const char* name
 }  // namespace hdla
 
 #ifdef HDLA_TIMELINE
+extern "C" __attribute__((visibility("default"))) int hdla_debug_timeline_scan(unsigned long long* host_dst, size_t count) {
+    return (int)cudaMemcpyFromSymbol(host_dst, hdla::tc::g_timeline_scan, count * sizeof(unsigned long long));
+}
 extern "C" __attribute__((visibility("default"))) int hdla_debug_timeline(unsigned long long* host_dst, size_t count) {
     return (int)cudaMemcpyFromSymbol(host_dst, hdla::g_timeline, count * sizeof(unsigned long long));
 }

@@ -17,22 +17,42 @@ constexpr int CH128 = 16 * 128;    // chunks of a [128 x 128] tile
 // workspace plan (byte offsets)
 // ------------------------------------------------------------------------------------------
 struct TcPlan {
-    int B, T, H, NT, BH;
-    long long G;
+    int B, T, H, NT, BH;               // NT: chunks per sequence (all chunks of the packed batch with cu_seqlens);
+    long long G;                       // BH: (sequence, head) pairs = scans and states;  G = tiles = H * chunks
     size_t status, Qh, Kh, Ah, Bh, Vc, E, ghat, Aqk, Aqb, Aak, Aab, M, W, P, U, Hs, V2, HT, zero;
     int nseg, seg_len;                 // two-level scan: segments per sequence, chunks per segment
     int lead_real;                     // the first segment in scan order is scanned for real in the first pass
     size_t Tseg, Fseg, Sin;            // per (b, h, segment): transition [K,K], state from zero [K,V], entering state [K,V]
     size_t dOc, dAqk, dAqb, DV2, DE, dgl, dW, dP, dAak, dAab;
     size_t total_fwd, total;
+    int nseq;                          // sequences of a packed variable-length batch, 0 otherwise
+    size_t chunk_tab, seq_tab;         // int2 per chunk: (first token, tokens);  int2 per sequence: (first chunk, chunks)
 };
+
+// Tokens of chunk n of the (packed) batch: from the chunk table of a variable-length batch, else uniform chunks.
+__device__ __forceinline__ void chunk_tokens(const int2* chunk_tab, int n, int T, int& t0, int& valid) {
+    if (chunk_tab) {
+        const int2 e = chunk_tab[n];
+        t0 = e.x; valid = e.y;
+    } else {
+        t0 = n * C; valid = min(C, T - t0);
+    }
+}
 
 inline TcPlan make_tc_plan(const HdlaDims& d) {
     TcPlan p{};
     p.B = d.B; p.T = d.T; p.H = d.H;
     p.NT = (d.T + C - 1) / C;
     p.BH = d.B * d.H;
-    p.G = (long long)p.BH * p.NT;
+    p.nseq = 0;
+    if (d.cu_seqlens && d.n_seqs > 0) {                    // packed sequences: chunks never straddle two of them
+        p.nseq = d.n_seqs;
+        long long nt = 0;
+        for (int s_ = 0; s_ < d.n_seqs; ++s_) nt += (d.cu_seqlens[s_ + 1] - d.cu_seqlens[s_] + C - 1) / C;
+        p.NT = (int)nt;
+        p.BH = d.n_seqs * d.H;
+    }
+    p.G = (long long)d.B * d.H * p.NT;
     size_t off = 0;
     auto take = [&](size_t bytes_per_chunk) {
         size_t o = off;
@@ -40,6 +60,8 @@ inline TcPlan make_tc_plan(const HdlaDims& d) {
         return o;
     };
     p.status = off; off += 256;
+    p.chunk_tab = off; off += p.nseq ? (((size_t)p.NT * 8 + 255) / 256) * 256 : 0;
+    p.seq_tab = off; off += p.nseq ? (((size_t)p.nseq * 8 + 255) / 256) * 256 : 0;
     // forward region: what the scan and the output kernel read.  The fused preparation kernel (HDLA_FLAG_FUSED_PREP)
     // keeps Aab on chip and writes Ah, Aak, M, P and the un-gating factors only for a backward pass, so with it
     // those live in the backward region; the four-kernel preparation passes them from kernel to kernel.
@@ -72,6 +94,7 @@ inline TcPlan make_tc_plan(const HdlaDims& d) {
         if (p.BH * (2 * n - 3) <= 148 && p.NT / n >= 4) nseg_all = n;
     nseg_all = fit(nseg_all);
     if (nseg_all < 3) nseg_all = 1;
+    if (p.nseq) { nseg_all = 1; nseg_phased = 1; }           // sequences of different lengths: one scan per pair
     p.lead_real = (d.flags & HDLA_PHASE_MASK) == HDLA_PHASE_ALL && nseg_all > 1;
     p.nseg = (d.flags & HDLA_PHASE_MASK) == HDLA_PHASE_ALL ? nseg_all : nseg_phased;
     p.seg_len = (p.NT + p.nseg - 1) / p.nseg;
@@ -131,8 +154,17 @@ __device__ __forceinline__ void tl_mark(long long g, int i) {
     }
 }
 #define TL(i) tl_mark(g, i)
+// second trace, for the scan kernel (slot = linear CTA number)
+static __device__ unsigned long long g_timeline_scan[4096 * 16];
+__device__ __forceinline__ void tls_mark(int slot, int i) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    if (slot < 4096) g_timeline_scan[slot * 16 + i] = t;
+}
+#define TLS(i) do { if (threadIdx.x == 0) tls_mark((int)(blockIdx.x + gridDim.x * blockIdx.y), i); } while (0)
 #else
 #define TL(i)
+#define TLS(i)
 #endif
 
 

@@ -49,18 +49,32 @@ def _internal_chunk(q, v, RANK_AB: int, chunk_size: int) -> int:
     return chunk_size
 
 
-def _dims(q, v, a, gk, RANK_AB: int, chunk_size: int, flags: int = 0) -> _lib.HdlaDims:
+def _dims(q, v, a, gk, RANK_AB: int, chunk_size: int, flags: int = 0, cu_seqlens=None) -> _lib.HdlaDims:
     chunk_size = _internal_chunk(q, v, RANK_AB, chunk_size)
     B, T, H, K = q.shape
     if os.environ.get("HDLA_FORCE_SIMT", "0") == "1":      # debugging aid: fp32 CUDA-core pipeline for any dtype
         flags |= _lib.FLAG_FORCE_SIMT
     if os.environ.get("HDLA_FUSED_PREP", "0") == "1":      # one-kernel chunk preparation (see include/hdla.h)
         flags |= _lib.FLAG_FUSED_PREP
-    return _lib.HdlaDims(B, T, H, K, v.shape[-1], RANK_AB, chunk_size, _lib.dtype_code(q.dtype),
-                         _lib.dtype_code(gk.dtype), flags)
+    d = _lib.HdlaDims(B, T, H, K, v.shape[-1], RANK_AB, chunk_size, _lib.dtype_code(q.dtype),
+                      _lib.dtype_code(gk.dtype), flags)
+    if cu_seqlens is not None:
+        d.with_seqlens(cu_seqlens)
+    return d
 
 
-def _check_shapes(q, k, v, a, b, gk, RANK_AB, initial_state):
+def _seq_offsets(cu_seqlens):
+    """cu_seqlens (tensor or sequence of ints) -> tuple of python ints, or None.  The library sizes its grids from
+    the offsets, so they are needed on the host (a device tensor is copied, which synchronises -- as the
+    reference's chunk-index preparation does)."""
+    if cu_seqlens is None:
+        return None
+    if isinstance(cu_seqlens, torch.Tensor):
+        cu_seqlens = cu_seqlens.detach().cpu().tolist()
+    return tuple(int(x) for x in cu_seqlens)
+
+
+def _check_shapes(q, k, v, a, b, gk, RANK_AB, initial_state, n_states=None):
     B, T, H, K = q.shape
     if k.shape != q.shape or gk.shape != q.shape:
         raise ValueError(f"k {tuple(k.shape)} and gk {tuple(gk.shape)} must match q {tuple(q.shape)}")
@@ -71,8 +85,10 @@ def _check_shapes(q, k, v, a, b, gk, RANK_AB, initial_state):
                          f"{(B, T * RANK_AB, H, K)}")
     if not (a.dtype == b.dtype == q.dtype):
         raise TypeError("a and b must have the dtype of q, k, v")
-    if initial_state is not None and initial_state.shape != (B, H, K, v.shape[-1]):
-        raise ValueError(f"initial_state {tuple(initial_state.shape)} must be [B, H, K, V]")
+    N = B if n_states is None else n_states
+    if initial_state is not None and initial_state.shape != (N, H, K, v.shape[-1]):
+        raise ValueError(f"initial_state {tuple(initial_state.shape)} must be [{N}, H, K, V] = "
+                         f"{(N, H, K, v.shape[-1])}")
 
 
 def workspace_bytes(dims: _lib.HdlaDims, with_backward: bool) -> int:
@@ -202,23 +218,24 @@ def chunk_hrdplr_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state
 
 
 def _chunk_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB, head_first, chunk_size,
-               _keep_ws: bool = False, _force_simt: bool = False):
+               _keep_ws: bool = False, _force_simt: bool = False, cu_seqlens=None):
     """``chunk_hrdplr_fwd`` returning ``(o, final_state, workspace, used_fp32_pipeline)``; with ``_keep_ws`` the
     workspace is sized for, and keeps what, ``hdla_chunk_bwd(HDLA_FLAG_WS_HOLDS_FWD)`` needs."""
     global _warned_fallback
     assert head_first is False, "head_first=True is not supported (as in the reference)"
     dev = _lib.require_cuda(q, k, v, a, b, gk, initial_state)
-    _check_shapes(q, k, v, a, b, gk, RANK_AB, initial_state)
+    N = None if cu_seqlens is None else len(cu_seqlens) - 1
+    _check_shapes(q, k, v, a, b, gk, RANK_AB, initial_state, N)
     check_status(dev)
     lib = _lib.load()
-    dims = _dims(q, v, a, gk, RANK_AB, chunk_size, _lib.FLAG_FORCE_SIMT if _force_simt else 0)
+    dims = _dims(q, v, a, gk, RANK_AB, chunk_size, _lib.FLAG_FORCE_SIMT if _force_simt else 0, cu_seqlens)
     B, T, H, K = q.shape
     V = v.shape[-1]
     h0 = None if initial_state is None else initial_state.to(torch.float32).contiguous()
     with torch.cuda.device(dev):
         ws = _alloc_ws(workspace_bytes(dims, _keep_ws), dev)
         o = torch.empty_like(v)
-        ht = torch.empty(B, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
+        ht = torch.empty(B if N is None else N, H, K, V, dtype=torch.float32, device=dev) if output_final_state else None
         rc = lib.hdla_chunk_fwd(C.byref(dims), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(a), _lib.ptr(b),
                                 _lib.ptr(gk), float(scale), _lib.ptr(h0), _lib.ptr(o), _lib.ptr(ht),
                                 _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
@@ -234,6 +251,9 @@ def _chunk_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK
                                       "pipeline represents; such calls are rerun on the fp32 CUDA-core pipeline "
                                       "(correct, much slower)", RuntimeWarning, stacklevel=3)
                     del ws, o, ht
+                    if cu_seqlens is not None:
+                        _raise_status(words)           # the fp32 pipeline takes no packed batches: the caller's
+                                                       # per-sequence path has to be used for such decays
                     return _chunk_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB,
                                       head_first, chunk_size, _keep_ws=_keep_ws, _force_simt=True)
                 if words[0] or words[1]:
@@ -248,11 +268,14 @@ class ChunkDPLRDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
     @contiguous
     @autocast_custom_fwd
-    def forward(ctx, q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB, head_first, chunk_size):
+    def forward(ctx, q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB, head_first, chunk_size,
+                cu_seqlens=None):
         keep = save_workspace_default() and any(
             isinstance(t, torch.Tensor) and t.requires_grad for t in (q, k, v, a, b, gk, initial_state))
         o, final_state, ctx.ws, ctx.force_simt = _chunk_fwd(q, k, v, a, b, gk, scale, initial_state, output_final_state,
-                                                            RANK_AB, head_first, chunk_size, _keep_ws=keep)
+                                                            RANK_AB, head_first, chunk_size, _keep_ws=keep,
+                                                            cu_seqlens=cu_seqlens)
+        ctx.cu_seqlens = cu_seqlens
         ctx.save_for_backward(q, k, v, a, b, gk, initial_state)
         ctx.head_first = head_first
         ctx.scale = scale
@@ -274,7 +297,7 @@ class ChunkDPLRDeltaRuleFunction(torch.autograd.Function):
         flags = _lib.FLAG_WS_HOLDS_FWD if ws is not None else 0
         if ctx.force_simt:                          # forward had to fall back to the fp32 pipeline: so does backward
             flags |= _lib.FLAG_FORCE_SIMT
-        dims = _dims(q, v, a, gk, ctx.RANK_AB, ctx.chunk_size, flags)
+        dims = _dims(q, v, a, gk, ctx.RANK_AB, ctx.chunk_size, flags, ctx.cu_seqlens)
         h0 = None if initial_state is None else initial_state.to(torch.float32).contiguous()
         if do.dtype != q.dtype:
             do = do.to(q.dtype)
@@ -295,7 +318,12 @@ class ChunkDPLRDeltaRuleFunction(torch.autograd.Function):
                 _post_status(ws, dev)                # waits that ran out in the backward kernels surface too
         if dh0 is not None and initial_state.dtype != torch.float32:
             dh0 = dh0.to(initial_state.dtype)
-        return dq, dk, dv, da, db, dgk, None, dh0, None, None, None, None
+        return dq, dk, dv, da, db, dgk, None, dh0, None, None, None, None, None
+
+
+def _packed_supported(q, v, RANK_AB: int) -> bool:
+    return _tc_shape(q, v, RANK_AB) and os.environ.get("HDLA_FORCE_SIMT", "0") != "1" \
+        and os.environ.get("HDLA_HONOR_CHUNK", "0") != "1"
 
 
 @torch.compiler.disable
@@ -312,10 +340,42 @@ def chunk_hrdplr_delta_rule(
     output_final_state: bool = False,
     head_first: bool = False,
     chunk_size: int = 32,
+    cu_seqlens=None,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-    """Drop-in for the reference's ``chunk_hrdplr_delta_rule`` (HRDPLR/hrdplr.py:286-318)."""
+    """Drop-in for the reference's ``chunk_hrdplr_delta_rule`` (HRDPLR/hrdplr.py:286-318).
+
+    ``cu_seqlens`` (an extension; the reference plumbs it only into its chunk kernels, HRDPLR/fwd_triton.py:618-623,
+    HRDPLR/bwd_triton.py:919-924): offsets of sequences packed along T in a batch of one, as in
+    ``fused_recurrent_dplr_delta_rule``; ``initial_state`` / the final state are then ``[n_seqs, H, K, V]``.  bf16
+    problems of the tensor-core pipeline run packed (chunks never straddle two sequences; one scan per sequence
+    and head); anything else is computed sequence by sequence."""
     assert q.dtype == k.dtype == v.dtype
     scale = k.shape[-1] ** -0.5 if scale is None else scale
+    offsets = _seq_offsets(cu_seqlens)
+    if offsets is not None:
+        if q.shape[0] != 1:
+            raise ValueError(f"The batch size is expected to be 1 rather than {q.shape[0]} when using `cu_seqlens`."
+                             f"Please flatten variable-length inputs before processing.")
+        if initial_state is not None and initial_state.shape[0] != len(offsets) - 1:
+            raise ValueError(f"The number of initial states is expected to be equal to the number of input sequences, "
+                             f"i.e., {len(offsets) - 1} rather than {initial_state.shape[0]}.")
+        if offsets[0] != 0 or offsets[-1] != q.shape[1] or any(y < x for x, y in zip(offsets, offsets[1:])):
+            raise ValueError(f"cu_seqlens {offsets} must rise from 0 to T={q.shape[1]}")
+        if not _packed_supported(q, v, RANK_AB):
+            outs, states = [], []
+            for s_, (lo, hi) in enumerate(zip(offsets, offsets[1:])):
+                if hi == lo:
+                    states.append(initial_state[s_:s_ + 1].float() if initial_state is not None else
+                                  q.new_zeros(1, q.shape[2], q.shape[3], v.shape[-1], dtype=torch.float32))
+                    continue
+                h0 = None if initial_state is None else initial_state[s_:s_ + 1]
+                o_s, ht_s = ChunkDPLRDeltaRuleFunction.apply(
+                    q[:, lo:hi], k[:, lo:hi], v[:, lo:hi], a[:, lo * RANK_AB:hi * RANK_AB],
+                    b[:, lo * RANK_AB:hi * RANK_AB], gk[:, lo:hi], scale, h0, output_final_state, RANK_AB,
+                    head_first, chunk_size)
+                outs.append(o_s)
+                states.append(ht_s)
+            return torch.cat(outs, 1), (torch.cat(states, 0) if output_final_state else None)
     o, final_state = ChunkDPLRDeltaRuleFunction.apply(
-        q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB, head_first, chunk_size)
+        q, k, v, a, b, gk, scale, initial_state, output_final_state, RANK_AB, head_first, chunk_size, offsets)
     return o, final_state

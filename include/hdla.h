@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define HDLA_VERSION 100
+#define HDLA_VERSION 101
 
 #if defined(__GNUC__)
 #define HDLA_API __attribute__((visibility("default")))
@@ -91,6 +91,16 @@ typedef struct HdlaDims {
     int32_t dtype;     /* HDLA_F32 | HDLA_BF16 for q,k,v,a,b,o,do and dq..db   */
     int32_t gk_dtype;  /* HDLA_F32 | HDLA_BF16 for gk and dgk                  */
     int32_t flags;     /* HDLA_FLAG_*                                          */
+    /* Variable-length batches for the chunked entry points (packed sequences, as in the reference's chunk kernels,
+     * HRDPLR/fwd_triton.py:618-623 and HRDPLR/bwd_triton.py:919-924): with cu_seqlens != NULL, B must be 1, T is the
+     * total number of tokens, sequence s holds tokens [cu_seqlens[s], cu_seqlens[s+1]) and has its own state, so h0 /
+     * ht / dht / dh0 are [n_seqs, H, K, V].  cu_seqlens is a HOST array of n_seqs + 1 offsets (the library sizes its
+     * grids from it); it only needs to live for the duration of the call.  The bf16 tensor-core pipeline implements
+     * this; other problems report HDLA_ERR_UNSUPPORTED.  hdla_recurrent_fwd takes its own (device) cu_seqlens
+     * argument and ignores these two fields. */
+    int32_t n_seqs;    /* number of sequences, 0 without cu_seqlens            */
+    int32_t reserved_; /* keep 0                                               */
+    const int64_t* cu_seqlens;
 } HdlaDims;
 
 /* Library version (HDLA_VERSION of the build). */

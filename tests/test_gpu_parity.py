@@ -309,6 +309,79 @@ def test_bf16_head_dims_below_128_run_on_tensor_cores(dev, B, T, H, K, V):
     assert torch.equal(o2, got["o"]) and torch.equal(ht2, got["ht"])
 
 
+def _varlen_case(dev, lens, H, K, V, dtype, tol, seed):
+    """Packed sequences through chunk_hrdplr_delta_rule(cu_seqlens=...) against the oracle run per sequence."""
+    import hdla_impl_b200 as HD
+    T = sum(lens)
+    N = len(lens)
+    x = make_inputs(1, T, H, K, V, R, seed=seed, dtype=dtype, gk_div=4.0)
+    x["gk"] = x["gk"].float()
+    g = torch.Generator().manual_seed(seed + 1)
+    h0 = torch.randn(N, H, K, V, generator=g) * 0.3
+    dht = torch.randn(N, H, K, V, generator=g)
+    cu = [0]
+    for n_ in lens:
+        cu.append(cu[-1] + n_)
+    names = ("q", "k", "v", "a", "b", "gk")
+    lv = [x[n].to(dev).requires_grad_(True) for n in names]
+    h0d = h0.to(dev).requires_grad_(True)
+    o, ht = HD.chunk_hrdplr_delta_rule(*lv, R, scale=K ** -0.5, initial_state=h0d, output_final_state=True,
+                                       chunk_size=64, cu_seqlens=torch.tensor(cu, device=dev))
+    assert ht.shape == (N, H, K, V)
+    loss = (o.float() * x["do"].to(dev).float()).sum() + (ht * dht.to(dev)).sum()
+    grads = torch.autograd.grad(loss, lv + [h0d])
+    HD.check_status(dev, wait=True)
+    rr = lambda n: R if n in ("a", "b") else 1
+    bad = []
+    for s_, (lo, hi) in enumerate(zip(cu, cu[1:])):
+        if hi == lo:
+            assert orc.rel_err(ht[s_], h0[s_]) < 1e-6 and orc.rel_err(grads[6][s_], dht[s_]) < 1e-6
+            continue
+        f = lambda n: (x[n].to(dtype) if n != "gk" else x[n])[:, lo * rr(n):hi * rr(n)].double()
+        st = orc.staged_forward(*[f(n) for n in names], R, K ** -0.5, h0[s_:s_ + 1], 64)
+        gr = orc.staged_backward(st, x["do"].to(dtype)[:, lo:hi].double(), dht[s_:s_ + 1])
+        pairs = [("o", o[:, lo:hi], st["o_bthv"]), ("ht", ht[s_:s_ + 1], st["ht"]), ("dh0", grads[6][s_:s_ + 1], gr["dh0"])]
+        pairs += [(gn, t[:, lo * rr(n):hi * rr(n)], gr[gn]) for gn, t, n in zip(GRADS, grads[:6], names)]
+        for name, got, ref in pairs:
+            e = orc.rel_err(got, ref)
+            if not e < tol:
+                bad.append(f"seq {s_} {name}: {e:.3e}")
+    assert not bad, "; ".join(bad)
+    return o, ht
+
+
+def test_chunked_varlen_packed_sequences_on_tensor_cores(dev):
+    """cu_seqlens in the chunked path (the reference plumbs it into its chunk kernels, HRDPLR/fwd_triton.py:618-623,
+    HRDPLR/bwd_triton.py:919-924): four packed sequences -- ragged, exactly one chunk, several chunks, a single
+    token -- each with its own initial state and final-state gradient; forward and every gradient against the oracle
+    run per sequence, on the tcgen05 pipeline (one launch sequence for the whole packed batch)."""
+    import hdla_impl_b200 as HD
+    from hdla_impl_b200 import _lib
+    n0 = _lib.kernel_launches()
+    o, ht = _varlen_case(dev, [200, 64, 333, 1], 2, 128, 128, torch.bfloat16, 2e-2, seed=61)
+    assert _lib.kernel_launches() - n0 == 10
+    # the packed result equals the sequences run one by one through the same operator
+    x = make_inputs(1, 598, 2, 128, 128, R, seed=61, dtype=torch.bfloat16, gk_div=4.0)
+    x["gk"] = x["gk"].float()
+    h0 = torch.randn(4, 2, 128, 128, generator=torch.Generator().manual_seed(62)) * 0.3
+    with torch.no_grad():
+        o1, ht1 = HD.chunk_hrdplr_delta_rule(*[x[n][:, 264 * (R if n in "ab" else 1):597 * (R if n in "ab" else 1)].to(dev)
+                                               for n in ("q", "k", "v", "a", "b", "gk")], R, scale=128 ** -0.5,
+                                             initial_state=h0[2:3].to(dev), output_final_state=True, chunk_size=64)
+    assert torch.equal(o1, o[:, 264:597]) and torch.equal(ht1, ht[2:3])
+    # head dims below 128 and an empty sequence in the middle
+    _varlen_case(dev, [70, 0, 130], 3, 64, 64, torch.bfloat16, 2e-2, seed=63)
+
+
+def test_chunked_varlen_falls_back_to_per_sequence_calls(dev):
+    """Problems outside the tensor-core pipeline (here fp32) take cu_seqlens too: sequence by sequence."""
+    _varlen_case(dev, [50, 64, 17], 2, 32, 48, torch.float32, 1e-4, seed=65)
+    with pytest.raises(ValueError, match="batch size"):
+        import hdla_impl_b200 as HD
+        x = make_inputs(2, 64, 1, 32, 32, R, seed=1)
+        HD.chunk_hrdplr_delta_rule(*[x[n].to(dev) for n in ("q", "k", "v", "a", "b", "gk")], R, cu_seqlens=[0, 64])
+
+
 def test_non_contiguous_inputs_and_autocast(dev):
     """The entry point makes its tensor arguments contiguous and is autocast-aware like the reference's
     decorators (HRDPLR/utils.py:7-25, HRDPLR/hrdplr.py:104-105,148-149)."""
