@@ -577,8 +577,8 @@ int tc_launch_chunk_prep(const TcPlan& pl, const HdlaDims& d, const void* q, con
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     const long long slots = 2LL * sms;                     // two CTAs per SM, persistent
     const unsigned grid = (unsigned)(pl.G < slots ? pl.G : slots);
-    if (d.gk_dtype == HDLA_F32) chunk_prep_tc_kernel<true><<<grid, 128, kPrepSmem, st>>>(pp, pl.G);
-    else                        chunk_prep_tc_kernel<false><<<grid, 128, kPrepSmem, st>>>(pp, pl.G);
+    if (d.gk_dtype == HDLA_F32) launch(chunk_prep_tc_kernel<true>, dim3(grid), dim3(128), kPrepSmem, st, pp, pl.G);
+    else                        launch(chunk_prep_tc_kernel<false>, dim3(grid), dim3(128), kPrepSmem, st, pp, pl.G);
     HDLA_CHECK_LAUNCH("chunk_prep_tc_kernel");
     return HDLA_OK;
 }

@@ -656,6 +656,14 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     const Tile tA1 = t8::tile(sA1, 128), tL1 = t8::tile(sL1, 64), tR1 = t8::tile(sR1, 64), tL2 = t8::tile(sL2, 128),
                tT = t8::tile(sT, 128), tY = t8::tile(sY, 128);
     float e_next = steps > 0 ? p.E[(size_t)(g0 + n_first) * K + row] : 0.f;
+    const bool want_dgl = p.reverse && !p.no_store;
+    uint4 hs[8];                                                 // reverse scan: St of the following chunk, for dgl
+    float e_hs = 1.f;                                            // ... and that chunk's E
+    if (want_dgl && steps > 0 && n_first + 1 < NTp) {            // a segment that does not end the sequence
+        e_hs = p.E[(size_t)(g0 + n_first + 1) * K + row];
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) hs[c8] = __ldg(p.Hs + (g0 + n_first + 1) * CH128 + (half * 8 + c8) * 128 + row);
+    }
     TLS(1);
     for (int it = 0; it < steps; ++it) {
         if (it >= 1 && it <= 10) TLS(1 + it);
@@ -665,6 +673,13 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         const bool more = it + 1 < steps;
         const float e = e_next;                                  // loaded one chunk ahead: off the critical path
         if (more) e_next = p.E[(size_t)(g + dn) * K + row];
+        if (want_dgl && it > 0) {
+            // this thread's piece of the forward checkpoint of the chunk AFTER this one (its factor E is the previous
+            // step's): requested here, used after the first product is issued -- the pack, the barrier and the issue
+            // in between cover most of the round trip
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) hs[c8] = __ldg(p.Hs + (g + 1) * CH128 + (half * 8 + c8) * 128 + row);
+        }
         // T = E (.) X  -> operand tile and checkpoint
 #pragma unroll
         for (int c8 = 0; c8 < 8; ++c8) {
@@ -684,15 +699,18 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
             tc_fence_after();
             t8::mma_chain<false, true>(tmem, tA1, 0, 0, tT, 0, 0, 128, 128, false);      // A1 T
             umma_commit(&barA);
+            // L1^T R1 does not depend on Y: it runs on the tensor pipe while the threads turn A1 T into Y
+            wait_or_flag(&ldB, ph, p.status, 14);
+            t8::mma_chain<true, true>(tmem + 128, tL1, 0, 0, tR1, 0, 0, 128, 64, false);   // L1^T R1
         }
         float part = 0.f;
         if (p.reverse && !p.no_store) {       // dgl = rowsum(dS (.) S_{n+1}), computed while the product runs
             if (n + 1 < NTp) {
-                const float inv = 1.f / p.E[(size_t)(g + 1) * K + row];
+                const float inv = 1.f / e_hs;
 #pragma unroll
                 for (int c8 = 0; c8 < 8; ++c8) {
                     float f[8];
-                    t8::unpack8(p.Hs[(g + 1) * CH128 + (half * 8 + c8) * 128 + row], f);
+                    t8::unpack8(hs[c8], f);
 #pragma unroll
                     for (int j = 0; j < 8; ++j) part = fmaf(S[c8 * 8 + j], f[j] * inv, part);
                 }
@@ -706,6 +724,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
                 }
             }
             if (half == 1) red[row] = part;
+            e_hs = e;                                            // the next step's following chunk is this one
         }
         wait_or_flag(&barA, ph, p.status, 12);
         wait_or_flag(&ldA, ph, p.status, 13);         // ADD is read from shared memory below
@@ -735,9 +754,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
                 bulk_g2s(sA1, p.A1 + (g + dn) * CH128, 32768, &ldA);
                 bulk_g2s(sADD, p.ADD + (g + dn) * p.add_stride * CH128, 32768, &ldA);
             }
-            wait_or_flag(&ldB, ph, p.status, 14);
             tc_fence_after();
-            t8::mma_chain<true, true>(tmem + 128, tL1, 0, 0, tR1, 0, 0, 128, 64, false);   // L1^T R1
             t8::mma_chain<true, true>(tmem + 128, tL2, 0, 0, tY, 0, 0, 128, 128, true);    // + L2^T Y
             umma_commit(&barB);
         }
@@ -1621,7 +1638,7 @@ int tc_compose_states(const float* T, const float* F, const float* S0, const flo
         if (rc != HDLA_OK) return rc;
         attr_dev = dev;
     }
-    compose_segments_kernel<<<dim3(BH, V / kComposeCols), 256, kComposeSmem, st>>>(T, F, S0, nullptr, out, count, reverse,
+    launch(compose_segments_kernel, dim3(dim3(BH, V / kComposeCols)), dim3(256), kComposeSmem, st, T, F, S0, nullptr, out, count, reverse,
                                                                                  0, 0, 1, f_stride, 1, t_stride, pre, post);
     HDLA_CHECK_LAUNCH("compose_segments_kernel");
     return HDLA_OK;
@@ -1704,16 +1721,16 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         } else {
             PrepP pp{(bp)q, (bp)k, (bp)v, (bp)a, (bp)b, gk, U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc),
                      F(pl.E), (__nv_bfloat16*)(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status, d.K, d.V, chunk_tab};
-            prep_hat_kernel<<<G, 128, 0, st>>>(pp);
+            launch(prep_hat_kernel, dim3(G), dim3(128), 0, st, pp);
             HDLA_CHECK_LAUNCH("prep_hat_kernel");
             GramP gp{U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Aak), U4(pl.Aab), status};
-            gram_tc_kernel<<<G, 128, 98304 + 1024, st>>>(gp);
+            launch(gram_tc_kernel, dim3(G), dim3(128), 98304 + 1024, st, gp);
             HDLA_CHECK_LAUNCH("gram_tc_kernel");
             InvP ivp{U4(pl.Aab), U4(pl.M), status};
-            inverse_tc_kernel<<<G, 128, 32768, st>>>(ivp);
+            launch(inverse_tc_kernel, dim3(G), dim3(128), 32768, st, ivp);
             HDLA_CHECK_LAUNCH("inverse_tc_kernel");
             WuP wp{U4(pl.M), U4(pl.Ah), U4(pl.Aak), U4(pl.Vc), U4(pl.P), U4(pl.U), U4(pl.W), status};
-            wu_tc_kernel<<<G, 128, 98304, st>>>(wp);
+            launch(wu_tc_kernel, dim3(G), dim3(128), 98304, st, wp);
             HDLA_CHECK_LAUNCH("wu_tc_kernel");
         }
         if (phase == HDLA_PHASE_PRE) return HDLA_OK;
@@ -1736,9 +1753,9 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             // both stay in the workspace for the STATE and POST phases of this sequence slice
             ScanTcP s1 = scan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
             s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1; s1.fin_transition = F(pl.Tseg);
-            scan_tc_kernel<<<dim3(pl.BH * pl.nseg, 2), 256, 196608, st>>>(s1);
+            launch(scan_tc_kernel, dim3(dim3(pl.BH * pl.nseg, 2)), dim3(256), 196608, st, s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
-            compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, nullptr, ht,
+            launch(compose_segments_kernel, dim3(dim3(pl.BH, V / kComposeCols)), dim3(256), kComposeSmem, st, F(pl.Tseg), F(pl.Fseg), nullptr, nullptr, ht,
                                                                          pl.nseg, 0, 1, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
@@ -1746,20 +1763,20 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         ScanTcP sp = scan_params(nullptr, nullptr, nullptr, ht, nullptr, 1);
         sp.ADD = U4(pl.zero); sp.R1 = U4(pl.zero); sp.L1 = U4(pl.zero); sp.add_stride = 0; sp.r1_stride = 0;
         sp.init_identity = 1;
-        scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
+        launch(scan_tc_kernel, dim3(pl.BH), dim3(256), 196608, st, sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         return HDLA_OK;
     }
     if (phase == HDLA_PHASE_STATE) {
         if (!ht) return fail(HDLA_ERR_INVALID, "state pass needs the output pointer (ht)");
         if (pl.nseg > 1) {                    // affine maps of the segments are in the workspace (TRANSITION phase)
-            compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), h0, nullptr, ht,
+            launch(compose_segments_kernel, dim3(dim3(pl.BH, V / kComposeCols)), dim3(256), kComposeSmem, st, F(pl.Tseg), F(pl.Fseg), h0, nullptr, ht,
                                                                          pl.nseg, 0, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
         }
         ScanTcP sp = scan_params(h0, nullptr, nullptr, ht, nullptr, 1);
-        scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
+        launch(scan_tc_kernel, dim3(pl.BH), dim3(256), 196608, st, sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         return HDLA_OK;
     }
@@ -1769,43 +1786,43 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         ScanTcP s1 = scan_params(nullptr, U4(pl.Hs), U4(pl.V2), F(pl.Fseg), nullptr, 1);
         s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1; s1.fin_transition = F(pl.Tseg);
         s1.seg_off = 0; s1.seg_cnt = pl.nseg - 1; s1.lead_real = 1; s1.lead_init = h0;
-        scan_tc_kernel<<<dim3(pl.BH * (pl.nseg - 1), 2), 256, 196608, st>>>(s1);
+        launch(scan_tc_kernel, dim3(dim3(pl.BH * (pl.nseg - 1), 2)), dim3(256), 196608, st, s1);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         // ... the state entering every later segment follows from the first segment's final state ...
-        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
+        launch(compose_segments_kernel, dim3(dim3(pl.BH, V / kComposeCols)), dim3(256), kComposeSmem, st, F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
                                                                      pl.nseg, 0, 0, 1, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         // ... and the remaining segments are scanned for real at once
         ScanTcP s2 = scan_params(F(pl.Sin), U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
         s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;
         s2.seg_off = 1; s2.seg_cnt = pl.nseg - 1;
-        scan_tc_kernel<<<pl.BH * (pl.nseg - 1), 256, 196608, st>>>(s2);
+        launch(scan_tc_kernel, dim3(pl.BH * (pl.nseg - 1)), dim3(256), 196608, st, s2);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
     } else     if (pl.nseg > 1) {
         // two-level scan: per segment, transition and state-from-zero side by side (grid.y = 2) ...
         if (phase == HDLA_PHASE_ALL) {        // (a phased POST call finds them in the workspace)
             ScanTcP s1 = scan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
             s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1; s1.fin_transition = F(pl.Tseg);
-            scan_tc_kernel<<<dim3(pl.BH * pl.nseg, 2), 256, 196608, st>>>(s1);
+            launch(scan_tc_kernel, dim3(dim3(pl.BH * pl.nseg, 2)), dim3(256), 196608, st, s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
         }
         // ... composed into the state entering every segment ...
-        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), nullptr, pl.nseg, 0, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
+        launch(compose_segments_kernel, dim3(dim3(pl.BH, V / kComposeCols)), dim3(256), kComposeSmem, st, F(pl.Tseg), F(pl.Fseg), h0, F(pl.Sin), nullptr, pl.nseg, 0, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         // ... and the real scan of all segments at once
         ScanTcP s2 = scan_params(F(pl.Sin), U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
         s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;
-        scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s2);
+        launch(scan_tc_kernel, dim3(pl.BH * pl.nseg), dim3(256), 196608, st, s2);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
     } else {
         ScanTcP sp = scan_params(h0, U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
-        scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
+        launch(scan_tc_kernel, dim3(pl.BH), dim3(256), 196608, st, sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
     }
     if (need_o) {
         OutP op{U4(pl.Qh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Vc), U4(pl.Hs), U4(pl.V2), (__nv_bfloat16*)o, d.T, d.H,
                 pl.NT, status, d.V, chunk_tab};
-        out_tc_kernel<<<G, 128, 73728, st>>>(op);
+        launch(out_tc_kernel, dim3(G), dim3(128), 73728, st, op);
         HDLA_CHECK_LAUNCH("out_tc_kernel");
     }
     return HDLA_OK;
@@ -1835,7 +1852,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     if (phase == HDLA_PHASE_ALL || phase == HDLA_PHASE_PRE) {
         DauP dp{(const __nv_bfloat16*)d_o, U4(pl.Vc), U4(pl.V2), U4(pl.Aqb), U4(pl.dOc), U4(pl.dAqk), U4(pl.dAqb),
                 U4(pl.DV2), d.T, d.H, pl.NT, status, d.V, chunk_tab};
-        dau_tc_kernel<<<G, 128, 81920, st>>>(dp);
+        launch(dau_tc_kernel, dim3(G), dim3(128), 81920, st, dp);
         HDLA_CHECK_LAUNCH("dau_tc_kernel");
         if (phase == HDLA_PHASE_PRE) return HDLA_OK;
     }
@@ -1856,15 +1873,15 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         if (pl.nseg > 1) {                    // per-segment gradients from zero, then composed with T^T
             ScanTcP s1 = rscan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
             s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1;
-            scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
+            launch(scan_tc_kernel, dim3(pl.BH * pl.nseg), dim3(256), 196608, st, s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
-            compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), dht, nullptr, dh0,
+            launch(compose_segments_kernel, dim3(dim3(pl.BH, V / kComposeCols)), dim3(256), kComposeSmem, st, F(pl.Tseg), F(pl.Fseg), dht, nullptr, dh0,
                                                                          pl.nseg, 1, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
             HDLA_CHECK_LAUNCH("compose_segments_kernel");
             return HDLA_OK;
         }
         ScanTcP sp = rscan_params(dht, nullptr, nullptr, dh0, nullptr, 1);
-        scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
+        launch(scan_tc_kernel, dim3(pl.BH), dim3(256), 196608, st, sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
         return HDLA_OK;
     }
@@ -1875,40 +1892,40 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         ScanTcP s1 = rscan_params(nullptr, U4(pl.DE), U4(pl.DV2), F(pl.Fseg), F(pl.dgl), 1);
         s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1;
         s1.seg_off = 1; s1.seg_cnt = pl.nseg - 1; s1.lead_real = 1; s1.lead_init = dht;
-        scan_tc_kernel<<<pl.BH * (pl.nseg - 1), 256, 196608, st>>>(s1);
+        launch(scan_tc_kernel, dim3(pl.BH * (pl.nseg - 1)), dim3(256), 196608, st, s1);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
-        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
+        launch(compose_segments_kernel, dim3(dim3(pl.BH, V / kComposeCols)), dim3(256), kComposeSmem, st, F(pl.Tseg), F(pl.Fseg), nullptr, F(pl.Sin), nullptr,
                                                                      pl.nseg, 1, 0, 1, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         ScanTcP s2 = rscan_params(F(pl.Sin), U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
         s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;
         s2.seg_off = 0; s2.seg_cnt = pl.nseg - 1;
-        scan_tc_kernel<<<pl.BH * (pl.nseg - 1), 256, 196608, st>>>(s2);
+        launch(scan_tc_kernel, dim3(pl.BH * (pl.nseg - 1)), dim3(256), 196608, st, s2);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
     } else     if (pl.nseg > 1) {
         // two-level reverse scan; the segment transitions were left in the workspace by the forward pass
         if (phase == HDLA_PHASE_ALL) {        // (a phased POST call finds the per-segment gradients in the workspace)
             ScanTcP s1 = rscan_params(nullptr, nullptr, nullptr, F(pl.Fseg), nullptr, 1);
             s1.nseg = pl.nseg; s1.seg_len = pl.seg_len; s1.fin_by_slot = 1;
-            scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s1);
+            launch(scan_tc_kernel, dim3(pl.BH * pl.nseg), dim3(256), 196608, st, s1);
             HDLA_CHECK_LAUNCH("scan_tc_kernel");
         }
-        compose_segments_kernel<<<dim3(pl.BH, V / kComposeCols), 256, kComposeSmem, st>>>(F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), nullptr, pl.nseg, 1, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
+        launch(compose_segments_kernel, dim3(dim3(pl.BH, V / kComposeCols)), dim3(256), kComposeSmem, st, F(pl.Tseg), F(pl.Fseg), dht, F(pl.Sin), nullptr, pl.nseg, 1, 0, 0, pl.nseg, 1, pl.nseg, 1, nullptr, nullptr);
         HDLA_CHECK_LAUNCH("compose_segments_kernel");
         ScanTcP s2 = rscan_params(F(pl.Sin), U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
         s2.nseg = pl.nseg; s2.seg_len = pl.seg_len; s2.init_by_slot = 1; s2.fin_last_only = 1;
-        scan_tc_kernel<<<pl.BH * pl.nseg, 256, 196608, st>>>(s2);
+        launch(scan_tc_kernel, dim3(pl.BH * pl.nseg), dim3(256), 196608, st, s2);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
     } else {
         ScanTcP sp = rscan_params(dht, U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
-        scan_tc_kernel<<<pl.BH, 256, 196608, st>>>(sp);
+        launch(scan_tc_kernel, dim3(pl.BH), dim3(256), 196608, st, sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
     }
     // --- wy: dWh, dP, dAak, dAab in one kernel
     WyBwdP wyp{U4(pl.M), U4(pl.DV2), U4(pl.Hs), U4(pl.Vc), U4(pl.P), U4(pl.Ah), U4(pl.dW), U4(pl.dP), U4(pl.dAak),
                U4(pl.dAab), status, (long long)G};
     const unsigned wy_grid = G < (unsigned)sm_count() ? G : (unsigned)sm_count();      // one persistent CTA per SM
-    wy_bwd_tc_kernel<<<wy_grid, 128, kWySmem, st>>>(wyp);
+    launch(wy_bwd_tc_kernel, dim3(wy_grid), dim3(128), kWySmem, st, wyp);
     HDLA_CHECK_LAUNCH("wy_bwd_tc_kernel");
     // --- everything else: hat-operand gradients, dv, un-gating, dgk
     GradP gp{U4(pl.Hs), U4(pl.Bh), U4(pl.dOc), U4(pl.Kh), U4(pl.dAqb), U4(pl.dAqk), U4(pl.DE), U4(pl.dP), U4(pl.Aak),
@@ -1916,7 +1933,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
              (bp)(ws + pl.ghat), F(pl.E), F(pl.dgl), (bp)dq, (bp)dk, (bp)dv, (bp)da, (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype,
              status, (long long)G, d.K, d.V, chunk_tab};
     const unsigned grad_grid = G < (unsigned)sm_count() ? G : (unsigned)sm_count();    // one persistent CTA per SM
-    grad_tc_kernel<<<grad_grid, 544, kGradSmem, st>>>(gp);
+    launch(grad_tc_kernel, dim3(grad_grid), dim3(544), kGradSmem, st, gp);
     HDLA_CHECK_LAUNCH("grad_tc_kernel");
     return HDLA_OK;
 }

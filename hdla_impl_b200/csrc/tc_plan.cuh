@@ -168,6 +168,16 @@ __device__ __forceinline__ void tls_mark(int slot, int i) {
 #endif
 
 
+// Kernel launch through cudaLaunchKernelEx (errors are picked up by HDLA_CHECK_LAUNCH).  Launching the pipeline's
+// kernels with programmatic stream serialisation (each kernel's prologue under the tail of the one before) was
+// measured and left out: within noise at 8192 tiles, 2 % faster at 2048, 1.7 % slower at 1024.
+template <typename... KArgs, typename... Args>
+inline void launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 }  // namespace tc
 
 // chunk_prep.cu: cumulative decay, hat operands, score matrices, inverse, Wh / u in one launch
