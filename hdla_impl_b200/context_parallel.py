@@ -115,18 +115,27 @@ class _CPChunkFunction(torch.autograd.Function):
         V = v.shape[-1]
         lib = _lib.load()
         check_status(dev)
-        mk = lambda phase, extra=0: _dims(q, v, a, gk, RANK_AB, chunk_size, phase | extra)
-        ws = _alloc_ws(workspace_bytes(mk(0), True), dev)
+        # one dims structure, its flags rewritten per phase, and the tensor / stream pointers taken once: a step makes
+        # a dozen calls into the library and their host-side cost adds up to the step's critical path
+        d = _dims(q, v, a, gk, RANK_AB, chunk_size)
+        base_flags = d.flags
+        ws = _alloc_ws(workspace_bytes(d, True), dev)
         f32 = dict(dtype=torch.float32, device=dev)
+        ins = [_lib.ptr(t) for t in (q, k, v, a, b, gk)]
+        ws_p, ws_n, sc = _lib.ptr(ws), ws.numel(), float(scale)
 
         def fwd(phase, h0, o, ht):
-            d = mk(phase)
-            rc = lib.hdla_chunk_fwd(C.byref(d), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(a), _lib.ptr(b),
-                                    _lib.ptr(gk), float(scale), _lib.ptr(h0), _lib.ptr(o), _lib.ptr(ht), _lib.ptr(ws),
-                                    ws.numel(), _lib.stream_ptr(dev))
-            _lib.check(rc, "hdla_chunk_fwd")
+            d.flags = base_flags | phase
+            rc = lib.hdla_chunk_fwd(C.byref(d), *ins, sc, _lib.ptr(h0), _lib.ptr(o), _lib.ptr(ht), ws_p, ws_n, stream)
+            if rc:
+                _lib.check(rc, "hdla_chunk_fwd")
+
+        def mk(_phase):
+            d.flags = base_flags
+            return d
 
         with torch.cuda.device(dev):
+            stream = _lib.stream_ptr(dev)
             fwd(_lib.PHASE_PRE, None, None, None)
             # one collective per direction: every rank contributes its transition map, its state-from-zero map and
             # (rank 0 only) the sequence's initial state, packed as [3, B, H, K, V] (K == V on this path)
@@ -149,6 +158,7 @@ class _CPChunkFunction(torch.autograd.Function):
         ctx.save_for_backward(q, k, v, a, b, gk, S, maps)
         ctx.ws, ctx.scale, ctx.R, ctx.chunk, ctx.group = ws, scale, RANK_AB, chunk_size, group
         ctx.has_h0 = initial_state is not None
+        ctx.rank, ctx.world = rank, world
         return o, ht
 
     @staticmethod
@@ -159,7 +169,7 @@ class _CPChunkFunction(torch.autograd.Function):
         q, k, v, a, b, gk, S_in, maps = ctx.saved_tensors
         group = ctx.group
         dev = q.device
-        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        rank, world = ctx.rank, ctx.world
         B, T, H, K = q.shape
         V = v.shape[-1]
         lib = _lib.load()
@@ -169,17 +179,25 @@ class _CPChunkFunction(torch.autograd.Function):
         do = do.contiguous().to(q.dtype)
         f32 = dict(dtype=torch.float32, device=dev)
         grads = [torch.empty_like(t) for t in (q, k, v, a, b, gk)]
-        mk = lambda phase: _dims(q, v, a, gk, ctx.R, ctx.chunk, phase | _lib.FLAG_WS_HOLDS_FWD)
+        d = _dims(q, v, a, gk, ctx.R, ctx.chunk, _lib.FLAG_WS_HOLDS_FWD)
+        base_flags = d.flags
+        ins = [_lib.ptr(t) for t in (q, k, v, a, b, gk)]
+        gp, none6 = [_lib.ptr(t) for t in grads], [None] * 6
+        ws_p, ws_n, sc, s_in, do_p = _lib.ptr(ws), ws.numel(), float(ctx.scale), _lib.ptr(S_in), _lib.ptr(do)
 
         def bwd(phase, dht_, dh0_, with_grads):
-            d = mk(phase)
-            g = [_lib.ptr(t) for t in grads] if with_grads else [None] * 6
-            rc = lib.hdla_chunk_bwd(C.byref(d), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(a), _lib.ptr(b),
-                                    _lib.ptr(gk), float(ctx.scale), _lib.ptr(S_in), _lib.ptr(do), _lib.ptr(dht_),
-                                    *g, _lib.ptr(dh0_), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
-            _lib.check(rc, "hdla_chunk_bwd")
+            d.flags = base_flags | phase
+            rc = lib.hdla_chunk_bwd(C.byref(d), *ins, sc, s_in, do_p, _lib.ptr(dht_), *(gp if with_grads else none6),
+                                    _lib.ptr(dh0_), ws_p, ws_n, stream)
+            if rc:
+                _lib.check(rc, "hdla_chunk_bwd")
+
+        def mk(_phase):
+            d.flags = base_flags & ~_lib.FLAG_WS_HOLDS_FWD
+            return d
 
         with torch.cuda.device(dev):
+            stream = _lib.stream_ptr(dev)
             bwd(_lib.PHASE_PRE, None, None, False)
             # mirror image: every rank contributes its gradient-from-zero map G and the gradient of the final
             # state IT returned (rank j's final state is the state entering rank j+1)
