@@ -174,10 +174,15 @@ def cpu_reference_pass(H: int, K: int, V: int, C: int, T_sample: int, B_sample: 
     torch.set_num_threads(os.cpu_count() or 1)
     x = make_inputs(B_sample, T_sample, H, K, V, R, seed=0)
     from oracle import ref_naive
+    sec = None
     if ref_naive.available():
-        sec = ref_naive.time_fwd_bwd(x, R, C, repeats=repeats)
-        kind = "reference"
-    else:
+        try:
+            sec = ref_naive.time_fwd_bwd(x, R, C, repeats=repeats)
+            kind = "reference"
+        except Exception as e:                           # noqa: BLE001  (e.g. one of naive.py's imports is missing)
+            print(f"bench: oracle/_ref/naive.py could not run ({type(e).__name__}: {e}); timing the oracle port",
+                  file=sys.stderr)
+    if sec is None:
         from oracle import hdla_oracle as orc
         sec = None
         for _ in range(repeats):
@@ -392,15 +397,23 @@ def run_ours(args, rank, world, local_rank):
     if not args.no_secondary and args.workload == "cfg1":
         del leaves, dev_in, host, out_host, x
         torch.cuda.empty_cache()
+
+        def record(name, fn):
+            # a secondary measurement must not take the headline line down with it (collective ones are entered by
+            # every rank in the same order, so a failure on one rank fails them all at the same call)
+            try:
+                secondary[name] = fn()
+            except Exception as e:                       # noqa: BLE001
+                secondary[name] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
         if world > 1:
-            secondary["cp_check"] = cp_parity_check(dev, rank, world)
-            secondary["cfg3"] = bench_cfg3(dev, rank, world, barrier)
+            record("cp_check", lambda: cp_parity_check(dev, rank, world))
+            record("cfg3", lambda: bench_cfg3(dev, rank, world, barrier))
             if scaling == "strong":
-                secondary["weak"] = bench_weak(dev, rank, world, barrier)
+                record("weak", lambda: bench_weak(dev, rank, world, barrier))
         else:
-            secondary["cfg3"] = bench_cfg3(dev, rank, world, barrier)
-            secondary["cfg2_decode"] = bench_decode_small(dev)
-            secondary["cfg0_fp32_gpu"] = bench_cfg0_gpu(dev)
+            record("cfg3", lambda: bench_cfg3(dev, rank, world, barrier))
+            record("cfg2_decode", lambda: bench_decode_small(dev))
+            record("cfg0_fp32_gpu", lambda: bench_cfg0_gpu(dev))
 
     if rank == 0:
         peaks, how = load_peaks()
@@ -508,8 +521,7 @@ def cp_parity_check(dev, rank, world):
     dist.all_reduce(e, op=dist.ReduceOp.MAX)
     HD.check_status(dev, wait=True)
     err = float(e.item())
-    assert err < 2e-2, f"context-parallel parity check failed: max relative error {err}"
-    return {"max_rel_err": err, "world": world, "T": T, "tolerance": 2e-2,
+    return {"max_rel_err": err, "passed": bool(err < 2e-2), "world": world, "T": T, "tolerance": 2e-2,
             "what": "cp_chunk_hrdplr_delta_rule vs the single-GPU operator: o, final states, dq dk dv da db dgk, dh0"}
 
 
