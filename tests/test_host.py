@@ -87,3 +87,38 @@ def test_numa_binding_is_best_effort_and_restores_affinity():
         inside = os.sched_getaffinity(0)
         assert nb.node is None or inside <= before
     assert os.sched_getaffinity(0) == before
+
+
+def test_packed_batch_dims_are_validated_on_the_host():
+    """cu_seqlens travels in HdlaDims as a HOST array: the workspace query sizes the plan from it and rejects
+    offsets that do not rise from 0 to T, B != 1, and problems outside the tensor-core pipeline."""
+    lib = _lib.load()
+    d = _lib.HdlaDims(1, 598, 2, 128, 128, 2, 64, 1, 0, 0).with_seqlens([0, 200, 264, 597, 598])
+    packed = lib.hdla_chunk_workspace_bytes(C.byref(d), 1)
+    assert packed > 0, _lib.last_error()
+    # 4 + 1 + 6 + 1 = 12 chunks against 10 for one sequence of 598 tokens: the packed plan is larger
+    plain = lib.hdla_chunk_workspace_bytes(C.byref(_lib.HdlaDims(1, 598, 2, 128, 128, 2, 64, 1, 0, 0)), 1)
+    assert packed > plain
+    d = _lib.HdlaDims(1, 598, 2, 128, 128, 2, 64, 1, 0, 0).with_seqlens([0, 300, 200, 598])
+    assert lib.hdla_chunk_workspace_bytes(C.byref(d), 1) == 0 and "decrease" in _lib.last_error()
+    d = _lib.HdlaDims(1, 598, 2, 128, 128, 2, 64, 1, 0, 0).with_seqlens([0, 300, 500])
+    assert lib.hdla_chunk_workspace_bytes(C.byref(d), 1) == 0 and "end at T" in _lib.last_error()
+    d = _lib.HdlaDims(2, 598, 2, 128, 128, 2, 64, 1, 0, 0).with_seqlens([0, 598])
+    assert lib.hdla_chunk_workspace_bytes(C.byref(d), 1) == 0 and "B == 1" in _lib.last_error()
+    d = _lib.HdlaDims(1, 598, 2, 128, 128, 2, 64, 0, 0, 0).with_seqlens([0, 598])          # fp32: no packed path
+    assert lib.hdla_chunk_workspace_bytes(C.byref(d), 1) == 0 and "tensor-core" in _lib.last_error()
+
+
+def test_tensor_core_pipeline_selection():
+    """bf16, rank 2, chunk 64 and head dims that are multiples of 8 up to 128 run on the tcgen05 pipeline."""
+    lib = _lib.load()
+    uses = lambda *a: lib.hdla_chunk_uses_tensor_cores(C.byref(_lib.HdlaDims(*a)))
+    assert uses(2, 256, 2, 128, 128, 2, 64, 1, 0, 0) == 1
+    assert uses(2, 256, 2, 64, 64, 2, 64, 1, 0, 0) == 1
+    assert uses(2, 256, 2, 96, 48, 2, 64, 1, 1, 0) == 1
+    assert uses(2, 256, 2, 100, 64, 2, 64, 1, 0, 0) == 0          # not a multiple of 8
+    assert uses(2, 256, 2, 256, 128, 2, 64, 1, 0, 0) == 0         # beyond 128
+    assert uses(2, 256, 2, 128, 128, 2, 16, 1, 0, 0) == 0         # chunk 16: fp32 pipeline
+    assert uses(2, 256, 2, 128, 128, 2, 64, 0, 0, 0) == 0         # fp32 inputs
+    assert uses(2, 256, 2, 128, 128, 2, 64, 1, 0, _lib.FLAG_FORCE_SIMT) == 0
+    assert uses(2, 256, 2, 64, 64, 2, 64, 1, 0, _lib.PHASE_PRE) == 0      # phased calls need the full 128 x 128
