@@ -581,10 +581,6 @@ struct ScanTcP {
     // head h's row of tiles (tile = h * NT + chunk); null for uniform batches (pair bh scans tiles bh * NT ..)
     const int2* seq_tab;
     int H;
-    // column split: two CTAs of 128 threads per scan (blockIdx.z = 0, 1), each owning 64 of the 128 state columns --
-    // the recurrence couples rows, never columns -- with N = 64 products and tiles half as wide.  Used for one-level
-    // scans of so few pairs that half the SMs would idle; each step is shorter, and twice as many SMs take part.
-    int vsplit;
 };
 
 __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
@@ -612,12 +608,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row = (warp & 3) * 32 + lane;
-    const bool vs = p.vsplit != 0;
-    const int half = vs ? (int)blockIdx.z : warp >> 2;             // which 64 state columns this thread owns
-    const int lc = vs ? 0 : half * 8;                              // their first column group inside the shared-memory tiles
-    const int NV = vs ? 64 : 128;                                  // columns of the T / Y / ADD / R1 tiles
-    const uint32_t add_bytes = vs ? 16384u : 32768u, r1_bytes = vs ? 8192u : 16384u;
-    const long long add_off = vs ? half * 8 * 128 : 0, r1_off = vs ? half * 8 * 64 : 0;    // column slice, in chunks
+    const int half = warp >> 2;
     TLS(0);
     if (warp == 0) { tmem_alloc(&tmem_s, 256); tmem_relinquish(); }
     long long g0 = (long long)bh * p.NT;
@@ -633,12 +624,12 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     if (tid == 0) {
         const long long g = g0 + n_first;
         mbar_init(&ldA, 1); mbar_init(&ldB, 1); mbar_init(&barA, 1); mbar_init(&barB, 1); fence_mbar_init();
-        mbar_expect_tx(&ldA, 32768 + add_bytes);
+        mbar_expect_tx(&ldA, 65536);
         bulk_g2s(sA1, p.A1 + g * CH128, 32768, &ldA);
-        bulk_g2s(sADD, p.ADD + g * p.add_stride * CH128 + add_off, add_bytes, &ldA);
-        mbar_expect_tx(&ldB, 16384 + r1_bytes + 32768);
+        bulk_g2s(sADD, p.ADD + g * p.add_stride * CH128, 32768, &ldA);
+        mbar_expect_tx(&ldB, 65536);
         bulk_g2s(sL1, p.L1 + g * p.r1_stride * CH64, 16384, &ldB);
-        bulk_g2s(sR1, p.R1 + g * p.r1_stride * CH64 + r1_off, r1_bytes, &ldB);
+        bulk_g2s(sR1, p.R1 + g * p.r1_stride * CH64, 16384, &ldB);
         bulk_g2s(sL2, p.L2 + g * CH128, 32768, &ldB);
     }
     float S[64];
@@ -696,8 +687,9 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) f[j] = e * S[c8 * 8 + j];
             const uint4 c = t8::pack8(f);
-            sT[(lc + c8) * 128 + row] = c;
-            if (!p.no_store) p.CK[g * CH128 + (half * 8 + c8) * 128 + row] = c;
+            const int cg = half * 8 + c8;
+            sT[cg * 128 + row] = c;
+            if (!p.no_store) p.CK[g * CH128 + cg * 128 + row] = c;
         }
         fence_proxy_async();
         tc_fence_before();
@@ -705,11 +697,11 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         if (tid == 0) {
             wait_or_flag(&ldA, ph, p.status, 11);
             tc_fence_after();
-            t8::mma_chain<false, true>(tmem, tA1, 0, 0, tT, 0, 0, NV, 128, false);       // A1 T
+            t8::mma_chain<false, true>(tmem, tA1, 0, 0, tT, 0, 0, 128, 128, false);      // A1 T
             umma_commit(&barA);
             // L1^T R1 does not depend on Y: it runs on the tensor pipe while the threads turn A1 T into Y
             wait_or_flag(&ldB, ph, p.status, 14);
-            t8::mma_chain<true, true>(tmem + 128, tL1, 0, 0, tR1, 0, 0, NV, 64, false);    // L1^T R1
+            t8::mma_chain<true, true>(tmem + 128, tL1, 0, 0, tR1, 0, 0, 128, 64, false);   // L1^T R1
         }
         float part = 0.f;
         if (p.reverse && !p.no_store) {       // dgl = rowsum(dS (.) S_{n+1}), computed while the product runs
@@ -731,7 +723,7 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
                     part = fmaf(S[4 * j + 2], x.z, part); part = fmaf(S[4 * j + 3], x.w, part);
                 }
             }
-            if (!vs && half == 1) red[row] = part;
+            if (half == 1) red[row] = part;
             e_hs = e;                                            // the next step's following chunk is this one
         }
         wait_or_flag(&barA, ph, p.status, 12);
@@ -739,46 +731,44 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
         tc_fence_after();
         {
             float acc[64];
-            tmem_row64(t8::taddr(tmem, warp, lc * 8), acc);
+            tmem_row64(t8::taddr(tmem, warp, half * 64), acc);
 #pragma unroll
             for (int c8 = 0; c8 < 8; ++c8) {
+                const int cg = half * 8 + c8;
                 float u[8];
-                t8::unpack8(sADD[(lc + c8) * 128 + row], u);
+                t8::unpack8(sADD[cg * 128 + row], u);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) u[j] += acc[c8 * 8 + j];
                 const uint4 c = t8::pack8(u);
-                sY[(lc + c8) * 128 + row] = c;
-                if (!p.no_store) p.Y[g * CH128 + (half * 8 + c8) * 128 + row] = c;
+                sY[cg * 128 + row] = c;
+                if (!p.no_store) p.Y[g * CH128 + cg * 128 + row] = c;
             }
         }
         fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        if (p.reverse && !p.no_store) {                // the two column halves' partial sums (dgl is zeroed when split)
-            if (vs) atomicAdd(p.dgl + (size_t)g * K + row, part);
-            else if (half == 0) p.dgl[(size_t)g * K + row] = part + red[row];
-        }
+        if (p.reverse && !p.no_store && half == 0) p.dgl[(size_t)g * K + row] = part + red[row];
         if (tid == 0) {
             if (more) {                                // A1 and ADD buffers are free: prefetch the next chunk's
-                mbar_expect_tx(&ldA, 32768 + add_bytes);
+                mbar_expect_tx(&ldA, 65536);
                 bulk_g2s(sA1, p.A1 + (g + dn) * CH128, 32768, &ldA);
-                bulk_g2s(sADD, p.ADD + (g + dn) * p.add_stride * CH128 + add_off, add_bytes, &ldA);
+                bulk_g2s(sADD, p.ADD + (g + dn) * p.add_stride * CH128, 32768, &ldA);
             }
             tc_fence_after();
-            t8::mma_chain<true, true>(tmem + 128, tL2, 0, 0, tY, 0, 0, NV, 128, true);     // + L2^T Y
+            t8::mma_chain<true, true>(tmem + 128, tL2, 0, 0, tY, 0, 0, 128, 128, true);    // + L2^T Y
             umma_commit(&barB);
         }
         wait_or_flag(&barB, ph, p.status, 15);
         tc_fence_after();
         if (tid == 0 && more) {
-            mbar_expect_tx(&ldB, 16384 + r1_bytes + 32768);
+            mbar_expect_tx(&ldB, 65536);
             bulk_g2s(sL1, p.L1 + (g + dn) * p.r1_stride * CH64, 16384, &ldB);
-            bulk_g2s(sR1, p.R1 + (g + dn) * p.r1_stride * CH64 + r1_off, r1_bytes, &ldB);
+            bulk_g2s(sR1, p.R1 + (g + dn) * p.r1_stride * CH64, 16384, &ldB);
             bulk_g2s(sL2, p.L2 + (g + dn) * CH128, 32768, &ldB);
         }
         {
             float acc[64];
-            tmem_row64(t8::taddr(tmem, warp, 128 + lc * 8), acc);
+            tmem_row64(t8::taddr(tmem, warp, 128 + half * 64), acc);
 #pragma unroll
             for (int j = 0; j < 64; ++j) S[j] = e * fmaf(e, S[j], acc[j]);
         }
@@ -1826,9 +1816,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
     } else {
         ScanTcP sp = scan_params(h0, U4(pl.Hs), U4(pl.V2), ht, F(pl.HT), 0);
-        sp.vsplit = pl.vsplit;
-        if (pl.vsplit) launch(scan_tc_kernel, dim3(pl.BH, 1, 2), dim3(128), 196608, st, sp);
-        else launch(scan_tc_kernel, dim3(pl.BH), dim3(256), 196608, st, sp);
+        launch(scan_tc_kernel, dim3(pl.BH), dim3(256), 196608, st, sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
     }
     if (need_o) {
@@ -1930,14 +1918,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
     } else {
         ScanTcP sp = rscan_params(dht, U4(pl.DE), U4(pl.DV2), dh0, F(pl.dgl), 0);
-        sp.vsplit = pl.vsplit;
-        if (pl.vsplit) {                      // the two column halves add their parts of dgl
-            cudaError_t e = cudaMemsetAsync(ws + pl.dgl, 0, (size_t)pl.G * K * sizeof(float), st);
-            if (e != cudaSuccess) return fail(HDLA_ERR_CUDA, "dgl clear: %s", cudaGetErrorString(e));
-            launch(scan_tc_kernel, dim3(pl.BH, 1, 2), dim3(128), 196608, st, sp);
-        } else {
-            launch(scan_tc_kernel, dim3(pl.BH), dim3(256), 196608, st, sp);
-        }
+        launch(scan_tc_kernel, dim3(pl.BH), dim3(256), 196608, st, sp);
         HDLA_CHECK_LAUNCH("scan_tc_kernel");
     }
     // --- wy: dWh, dP, dAak, dAab in one kernel

@@ -22,7 +22,6 @@ struct TcPlan {
     size_t status, Qh, Kh, Ah, Bh, Vc, E, ghat, Aqk, Aqb, Aak, Aab, M, W, P, U, Hs, V2, HT, zero;
     int nseg, seg_len;                 // two-level scan: segments per sequence, chunks per segment
     int lead_real;                     // the first segment in scan order is scanned for real in the first pass
-    int vsplit;                        // one-level scan of a complete call: two CTAs per pair, 64 state columns each
     size_t Tseg, Fseg, Sin;            // per (b, h, segment): transition [K,K], state from zero [K,V], entering state [K,V]
     size_t dOc, dAqk, dAqb, DV2, DE, dgl, dW, dP, dAak, dAab;
     size_t total_fwd, total;
@@ -99,7 +98,6 @@ inline TcPlan make_tc_plan(const HdlaDims& d) {
     p.lead_real = (d.flags & HDLA_PHASE_MASK) == HDLA_PHASE_ALL && nseg_all > 1;
     p.nseg = (d.flags & HDLA_PHASE_MASK) == HDLA_PHASE_ALL ? nseg_all : nseg_phased;
     p.seg_len = (p.NT + p.nseg - 1) / p.nseg;
-    p.vsplit = (d.flags & HDLA_PHASE_MASK) == HDLA_PHASE_ALL && p.nseg == 1 && 2 * p.BH <= 148;
     const int nseg_max = nseg_all > nseg_phased ? nseg_all : nseg_phased;     // same offsets for both kinds of call
     const size_t slots = (size_t)p.BH * nseg_max;
     p.Tseg = off; off += nseg_max > 1 ? slots * K * K * 4 : 0;
