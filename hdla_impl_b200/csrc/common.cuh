@@ -45,6 +45,52 @@ __device__ __forceinline__ void st_elem(void* p, size_t i, int dt, float x) {
     else static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(x);
 }
 
+// Eight consecutive elements of a row (the index is a multiple of 8 and the base 16-byte aligned): requested as raw
+// 16-byte pieces (one for bf16, two for fp32) so that a kernel can hold the request for its next row while it works
+// on the current one, and turned into floats where they are used.
+struct Raw8 { uint4 lo, hi; };
+__device__ __forceinline__ Raw8 ld_raw8(const void* base, size_t i, int dt) {
+    Raw8 r;
+    if (dt == HDLA_F32) {
+        r.lo = *reinterpret_cast<const uint4*>(static_cast<const float*>(base) + i);
+        r.hi = *reinterpret_cast<const uint4*>(static_cast<const float*>(base) + i + 4);
+    } else {
+        r.lo = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(base) + i);
+        r.hi = make_uint4(0, 0, 0, 0);
+    }
+    return r;
+}
+__device__ __forceinline__ void raw8_to_float(const Raw8& r, int dt, float* f) {
+    if (dt == HDLA_F32) {
+        f[0] = __uint_as_float(r.lo.x); f[1] = __uint_as_float(r.lo.y); f[2] = __uint_as_float(r.lo.z); f[3] = __uint_as_float(r.lo.w);
+        f[4] = __uint_as_float(r.hi.x); f[5] = __uint_as_float(r.hi.y); f[6] = __uint_as_float(r.hi.z); f[7] = __uint_as_float(r.hi.w);
+    } else {
+        const uint32_t w[4] = {r.lo.x, r.lo.y, r.lo.z, r.lo.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            f[2 * j] = __uint_as_float(w[j] << 16);
+            f[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        }
+    }
+}
+__device__ __forceinline__ void ld_elem8(const void* base, size_t i, int dt, float* f) {
+    raw8_to_float(ld_raw8(base, i, dt), dt, f);
+}
+__device__ __forceinline__ void st_elem8(void* base, size_t i, int dt, const float* f) {
+    if (dt == HDLA_F32) {
+        *reinterpret_cast<float4*>(static_cast<float*>(base) + i) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(static_cast<float*>(base) + i + 4) = make_float4(f[4], f[5], f[6], f[7]);
+    } else {
+        uint4 c;
+        __nv_bfloat162 h;
+        h = __floats2bfloat162_rn(f[0], f[1]); c.x = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(f[2], f[3]); c.y = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(f[4], f[5]); c.z = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(f[6], f[7]); c.w = *reinterpret_cast<uint32_t*>(&h);
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(base) + i) = c;
+    }
+}
+
 // pipelines implemented in the other translation units
 int recurrent_fwd_launch(const HdlaDims& d, const void* q, const void* k, const void* v, const void* a,
                          const void* b, const void* gk, float scale, const float* h0, void* o, float* ht,

@@ -1,7 +1,10 @@
 // a/b parametrisation of the HDLA layer (reference: parameterize_a_b, HRDPLR/hdla_custom.py:19-43):
 //   ef = exp(log_f);  a1 = -beta k;  at2 = -beta ef k;  s = sum_K(k at2);  a2 = at2 + a1 s
 //   b1 = ef k;  b2 = k;   a, b interleaved time-major / rank-minor: row 2t + r of [B, 2T, H, K]
-// One warp per (b, t, h) row; the K-reduction is a shuffle tree.  Forward and backward.
+// Forward and backward, bandwidth bound.  Head dims that are multiples of 8 up to 256 (the operator's own) take the
+// vector kernels: 16 lanes per (b, t, h) row, 16-byte loads and stores, the row held in registers between the
+// K-reduction (a shuffle tree over the 16 lanes) and the stores.  Other head dims take the scalar kernels, one warp
+// per row.
 #include "common.cuh"
 
 namespace hdla {
@@ -93,11 +96,137 @@ __global__ void __launch_bounds__(256) param_ab_bwd_kernel(AbP p) {
     if (lane == 0) st_elem(p.dbeta, (size_t)row, p.dt, dbeta);
 }
 
+// ---- vector kernels: 16 lanes per row, lane l owns the 8-column pieces l and l + 16
+constexpr int kAbLanes = 16;
+
+__device__ __forceinline__ float sub_sum(float x) {
+#pragma unroll
+    for (int o = kAbLanes / 2; o; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    return x;
+}
+
+template <int PIECES>
+__global__ void __launch_bounds__(256) param_ab_fwd_vec_kernel(AbP p) {
+    const long long row = (long long)blockIdx.x * (256 / kAbLanes) + (threadIdx.x / kAbLanes);
+    const bool live = row < p.rows;                          // whole warps stay for the shuffles
+    const int l = threadIdx.x % kAbLanes, npiece = p.K / 8;
+    size_t in = 0, o1 = 0, o2 = 0;
+    if (live) row_index(p, row, in, o1, o2);
+    const float beta = live ? ld_elem(p.beta, (size_t)row, p.dt) : 0.f;
+    float kv[PIECES][8], ef[PIECES][8];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < PIECES; ++j) {
+        const int pc = l + j * kAbLanes;
+        if (live && pc < npiece) {
+            ld_elem8(p.k, in + pc * 8, p.dt, kv[j]);
+            ld_elem8(p.log_f, in + pc * 8, p.dt, ef[j]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                ef[j][e] = __expf(ef[j][e]);
+                s += kv[j][e] * (-beta * ef[j][e] * kv[j][e]);
+            }
+        }
+    }
+    s = sub_sum(s);
+#pragma unroll
+    for (int j = 0; j < PIECES; ++j) {
+        const int pc = l + j * kAbLanes;
+        if (live && pc < npiece) {
+            float a1[8], a2[8], b1[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                a1[e] = -beta * kv[j][e];
+                a2[e] = -beta * ef[j][e] * kv[j][e] + a1[e] * s;
+                b1[e] = ef[j][e] * kv[j][e];
+            }
+            st_elem8(p.a, o1 + pc * 8, p.dt, a1);
+            st_elem8(p.a, o2 + pc * 8, p.dt, a2);
+            st_elem8(p.b, o1 + pc * 8, p.dt, b1);
+            st_elem8(p.b, o2 + pc * 8, p.dt, kv[j]);
+        }
+    }
+}
+
+template <int PIECES>
+__global__ void __launch_bounds__(256) param_ab_bwd_vec_kernel(AbP p) {
+    const long long row = (long long)blockIdx.x * (256 / kAbLanes) + (threadIdx.x / kAbLanes);
+    const bool live = row < p.rows;
+    const int l = threadIdx.x % kAbLanes, npiece = p.K / 8;
+    size_t in = 0, o1 = 0, o2 = 0;
+    if (live) row_index(p, row, in, o1, o2);
+    const float beta = live ? ld_elem(p.beta, (size_t)row, p.dt) : 0.f;
+    float kv[PIECES][8], ef[PIECES][8], da1[PIECES][8], da2[PIECES][8], db1[PIECES][8], db2[PIECES][8];
+    float s = 0.f, ds = 0.f;
+#pragma unroll
+    for (int j = 0; j < PIECES; ++j) {
+        const int pc = l + j * kAbLanes;
+        if (live && pc < npiece) {
+            ld_elem8(p.k, in + pc * 8, p.dt, kv[j]);
+            ld_elem8(p.log_f, in + pc * 8, p.dt, ef[j]);
+            ld_elem8(p.a, o1 + pc * 8, p.dt, da1[j]);
+            ld_elem8(p.a, o2 + pc * 8, p.dt, da2[j]);
+            ld_elem8(p.b, o1 + pc * 8, p.dt, db1[j]);
+            ld_elem8(p.b, o2 + pc * 8, p.dt, db2[j]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                ef[j][e] = __expf(ef[j][e]);
+                s += kv[j][e] * (-beta * ef[j][e] * kv[j][e]);
+                ds += (-beta * kv[j][e]) * da2[j][e];
+            }
+        }
+    }
+    s = sub_sum(s);
+    ds = sub_sum(ds);
+    float dbeta = 0.f;
+#pragma unroll
+    for (int j = 0; j < PIECES; ++j) {
+        const int pc = l + j * kAbLanes;
+        if (live && pc < npiece) {
+            float dk[8], dlf[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float k = kv[j][e], f = ef[j][e];
+                const float at2 = -beta * f * k;
+                const float dat2 = da2[j][e] + k * ds;       // a2 = at2 + a1 s,  s = sum k at2
+                const float da1t = da1[j][e] + s * da2[j][e];
+                float g = at2 * ds;                          // through s (the factor k)
+                g += -beta * f * dat2;                       // at2 = -beta ef k
+                g += -beta * da1t;                           // a1 = -beta k
+                g += f * db1[j][e] + db2[j][e];              // b1 = ef k, b2 = k
+                dk[e] = g;
+                dlf[e] = (-beta * k * dat2 + k * db1[j][e]) * f;
+                dbeta += -f * k * dat2 - k * da1t;
+            }
+            st_elem8(p.dk, in + pc * 8, p.dt, dk);
+            st_elem8(p.dlog_f, in + pc * 8, p.dt, dlf);
+        }
+    }
+    dbeta = sub_sum(dbeta);
+    if (live && l == 0) st_elem(p.dbeta, (size_t)row, p.dt, dbeta);
+}
+
 }  // namespace
 
 int param_ab_launch(bool backward, const void* beta, const void* k, const void* log_f, void* a, void* b, void* dbeta,
                     void* dk, void* dlog_f, int B, int T, int H, int K, int dt, cudaStream_t st) {
     AbP p{beta, k, log_f, a, b, dbeta, dk, dlog_f, (long long)B * T * H, T, H, K, dt};
+    bool aligned = true;
+    for (const void* q : {k, log_f, (const void*)a, (const void*)b, (const void*)dk, (const void*)dlog_f})
+        aligned = aligned && reinterpret_cast<uintptr_t>(q) % 16 == 0;
+    if (aligned && K % 8 == 0 && K <= kAbLanes * 16) {
+        const unsigned blocks = (unsigned)((p.rows + 15) / 16);
+        const bool wide = K > kAbLanes * 8;
+        if (backward) {
+            if (wide) param_ab_bwd_vec_kernel<2><<<blocks, 256, 0, st>>>(p);
+            else param_ab_bwd_vec_kernel<1><<<blocks, 256, 0, st>>>(p);
+        } else {
+            if (wide) param_ab_fwd_vec_kernel<2><<<blocks, 256, 0, st>>>(p);
+            else param_ab_fwd_vec_kernel<1><<<blocks, 256, 0, st>>>(p);
+        }
+        HDLA_CHECK_LAUNCH(backward ? "param_ab_bwd_vec_kernel" : "param_ab_fwd_vec_kernel");
+        return HDLA_OK;
+    }
     const unsigned blocks = (unsigned)((p.rows + 7) / 8);
     if (backward) param_ab_bwd_kernel<<<blocks, 256, 0, st>>>(p);
     else param_ab_fwd_kernel<<<blocks, 256, 0, st>>>(p);

@@ -527,11 +527,12 @@ def _param_ab_torch(beta, k, log_f):
     return a, b
 
 
+@pytest.mark.parametrize("K", [96, 128, 200, 100])   # one piece per lane, full rows, two pieces, scalar kernels
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-def test_parameterize_a_b_forward_backward(dev, dtype, tol):
+def test_parameterize_a_b_forward_backward(dev, dtype, tol, K):
     from hdla_impl_b200.layer_ops import parameterize_a_b
     g = torch.Generator().manual_seed(3)
-    B, T, H, K = 2, 33, 3, 96
+    B, T, H = 2, 33, 3
     k = torch.nn.functional.normalize(torch.randn(B, T, H, K, generator=g), dim=-1)
     beta = 2 * torch.sigmoid(torch.randn(B, T, H, 1, generator=g))
     log_f = torch.nn.functional.logsigmoid(torch.randn(B, T, H, K, generator=g))
@@ -565,12 +566,14 @@ def test_bf16_recompute_and_forward_only(dev, monkeypatch):
     assert torch.equal(o, a["o"]) and torch.equal(ht, a["ht"])
 
 
+@pytest.mark.parametrize("rows,D", [(37, 2048), (700, 64), (5, 4096), (3, 8192), (9, 1000)])
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
-def test_rms_norm_fused_gate_forward_backward(dev, dtype, tol):
-    """Against the arithmetic of the reference's normalize_torch (c = sqrt(D), no mean, sigmoid gate applied before)."""
+def test_rms_norm_fused_gate_forward_backward(dev, dtype, tol, rows, D):
+    """Against the arithmetic of the reference's normalize_torch (c = sqrt(D), no mean, sigmoid gate applied before).
+    3 x 700 rows is more than the grid holds, so every CTA walks over several rows and sums its share of dweight."""
     from hdla_impl_b200.layer_ops import rms_norm_fused_gate
     g = torch.Generator().manual_seed(5)
-    rows, D, eps = 37, 2048, 1e-5
+    eps = 1e-5
     x, gate = torch.randn(3, rows, D, generator=g), torch.randn(3, rows, D, generator=g)
     w, go = 1 + 0.1 * torch.randn(D, generator=g), torch.randn(3, rows, D, generator=g)
     rd = lambda t: t.to(dtype).double().requires_grad_(True)
