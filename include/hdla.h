@@ -240,7 +240,8 @@ HDLA_API int hdla_param_ab_bwd(const void* beta, const void* k, const void* log_
 /* Output epilogue of the layer: o = sqrt(D) * y / sqrt(sum(y^2) + eps) * weight with y = x * sigmoid(gate), per row
  * of length D.  Replaces the layer's RMSNormFusedGate call (HRDPLR/hdla_custom.py:341-345,
  * HRDPLR/normalizations/rms_norm.py:48-91).  x, gate, o, dx, dgate: [rows, D] in `dtype`; weight [D] in `dtype`;
- * dweight [D] fp32, ACCUMULATED (the caller zeroes it). */
+ * dweight [D] fp32, ACCUMULATED (the caller zeroes it).  D is a multiple of 8, at most 8192 (HDLA_ERR_UNSUPPORTED
+ * otherwise) and every tensor starts on a 16-byte boundary (HDLA_ERR_INVALID otherwise). */
 HDLA_API int hdla_norm_gate_fwd(const void* x, const void* gate, const void* weight, void* o,
                                 int64_t rows, int32_t D, float eps, int32_t dtype, void* cuda_stream);
 HDLA_API int hdla_norm_gate_bwd(const void* x, const void* gate, const void* weight, const void* d_o,
