@@ -414,6 +414,7 @@ def run_ours(args, rank, world, local_rank):
             record("cfg3", lambda: bench_cfg3(dev, rank, world, barrier))
             record("cfg2_decode", lambda: bench_decode_small(dev))
             record("cfg0_fp32_gpu", lambda: bench_cfg0_gpu(dev))
+            record("layer_call", lambda: bench_layer_call(dev))
 
     if rank == 0:
         peaks, how = load_peaks()
@@ -659,6 +660,58 @@ def bench_cfg0_gpu(dev, steps=20):
     ms = e0.elapsed_time(e1) / steps
     return {"workload": "cfg0: B2 T256 H4 K=V=64 fp32 chunk 64, fwd+bwd (fp32 CUDA-core pipeline; launch bound)",
             "ms_per_step": ms, "value": B * T / (ms / 1e3), "unit": "tokens/s", "steps": steps}
+
+
+def bench_layer_call(dev, steps=10):
+    """The operator as the reference layer calls it (HRDPLR/hdla_custom.py:290-345), at the cfg 1 shape, fwd+bwd:
+    parameterize_a_b + chunk_hrdplr_delta_rule as two calls against chunk_hdla_delta_rule (a and b formed inside the
+    chunk-preparation kernel), and the layer's norm x gate epilogue on the operator's output."""
+    import torch.nn.functional as F
+    import hdla_impl_b200 as HD
+    from hdla_impl_b200.layer_ops import chunk_hdla_delta_rule, parameterize_a_b, rms_norm_fused_gate
+    B, T, H, K, V, C, _ = WORKLOADS["cfg1"]
+    g = torch.Generator().manual_seed(7)
+    rn = lambda *s_: torch.randn(*s_, generator=g)
+    bf = torch.bfloat16
+    mk = lambda x: x.to(bf).to(dev).requires_grad_(True)
+    q, k, v = mk(F.normalize(rn(B, T, H, K), dim=-1)), mk(F.normalize(rn(B, T, H, K), dim=-1)), mk(rn(B, T, H, V))
+    beta, log_f = mk(2 * torch.sigmoid(rn(B, T, H, 1))), mk(F.logsigmoid(rn(B, T, H, K)) / 16)
+    do = rn(B, T, H, V).to(bf).to(dev)
+    lv = [q, k, v, beta, log_f]
+
+    def two_calls():
+        a, b = parameterize_a_b(beta, k, log_f)
+        o, _ = HD.chunk_hrdplr_delta_rule(q, k, v, a, b, log_f, R, scale=1.0, chunk_size=C)
+        torch.autograd.grad(o, lv, do)
+
+    def one_call():
+        o, _ = chunk_hdla_delta_rule(q, k, v, beta, log_f, scale=1.0)
+        torch.autograd.grad(o, lv, do)
+
+    x = rn(B * T, H * V).to(bf).to(dev).requires_grad_(True)
+    gate = rn(B * T, H * V).to(bf).to(dev).requires_grad_(True)
+    w = torch.ones(H * V, dtype=bf, device=dev, requires_grad=True)
+    dn = rn(B * T, H * V).to(bf).to(dev)
+
+    def norm():
+        torch.autograd.grad(rms_norm_fused_gate(x, gate, w, 1e-5), [x, gate, w], dn)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / steps
+
+    t2, t1, tn = timed(two_calls), timed(one_call), timed(norm)
+    return {"workload": "cfg1 shape as the layer calls the operator (q, k, v, beta, log_f; scale 1), bf16, fwd+bwd",
+            "two_calls_ms": t2, "one_call_ms": t1, "norm_gate_fwd_bwd_ms": tn,
+            "one_call_tokens_per_s": B * T / (t1 / 1e3), "steps": steps}
 
 
 def run_decode(args, rank, world, local_rank):

@@ -72,6 +72,11 @@ size_t hdla_chunk_workspace_bytes(const HdlaDims* dims, int with_backward) {
                                    "(bf16, chunk 64, R=2, K and V multiples of 8 up to 128)");
         return 0;
     }
+    if ((dims->flags & HDLA_FLAG_PARAM_AB) && !tc_supported(*dims)) {
+        fail(HDLA_ERR_UNSUPPORTED, "the in-operator a/b parametrisation (HDLA_FLAG_PARAM_AB) needs the bf16 tensor-core "
+                                   "pipeline (bf16, chunk 64, R=2, K and V multiples of 8 up to 128)");
+        return 0;
+    }
     const size_t simt = simt_workspace_floats(*dims, with_backward) * sizeof(float);
     if (simt == 0) return 0;
     if (tc_supported(*dims)) return tc_region_bytes(*dims, with_backward);
@@ -91,7 +96,8 @@ int hdla_chunk_fwd(const HdlaDims* dims, const void* q, const void* k, const voi
     begin_call(static_cast<cudaStream_t>(cuda_stream));
     const int phase = dims->flags & HDLA_PHASE_MASK;
     const bool needs_o = phase == HDLA_PHASE_ALL || phase == HDLA_PHASE_POST;
-    if (!q || !k || !v || !a || !b || !gk || (needs_o && !o))
+    const bool param_ab = (dims->flags & HDLA_FLAG_PARAM_AB) != 0;       // `a` is beta, `b` is not read
+    if (!q || !k || !v || !a || (!b && !param_ab) || !gk || (needs_o && !o))
         return fail(HDLA_ERR_INVALID, "chunk_fwd: null tensor pointer");
     rc = check_ws(dims, workspace, workspace_bytes, phase == HDLA_PHASE_ALL ? 0 : 1);
     if (rc != HDLA_OK) return rc;
@@ -113,8 +119,9 @@ int hdla_chunk_bwd(const HdlaDims* dims, const void* q, const void* k, const voi
     begin_call(static_cast<cudaStream_t>(cuda_stream));
     const int phase = dims->flags & HDLA_PHASE_MASK;
     const bool needs_grads = phase == HDLA_PHASE_ALL || phase == HDLA_PHASE_POST;
-    if (!q || !k || !v || !a || !b || !gk || (phase != HDLA_PHASE_STATE && !d_o) ||
-        (needs_grads && (!dq || !dk || !dv || !da || !db || !dgk)))
+    const bool param_ab = (dims->flags & HDLA_FLAG_PARAM_AB) != 0;       // `a` is beta, `da` dbeta; `b`, `db` unused
+    if (!q || !k || !v || !a || (!b && !param_ab) || !gk || (phase != HDLA_PHASE_STATE && !d_o) ||
+        (needs_grads && (!dq || !dk || !dv || !da || (!db && !param_ab) || !dgk)))
         return fail(HDLA_ERR_INVALID, "chunk_bwd: null tensor pointer");
     rc = check_ws(dims, workspace, workspace_bytes, 1);
     if (rc != HDLA_OK) return rc;
@@ -163,7 +170,7 @@ int hdla_param_ab_fwd(const void* beta, const void* k, const void* log_f, void* 
     if (B <= 0 || T <= 0 || H <= 0 || K <= 0) return fail(HDLA_ERR_INVALID, "param_ab_fwd: non-positive dimension");
     if (dtype != HDLA_F32 && dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", dtype);
     begin_call(static_cast<cudaStream_t>(cuda_stream));
-    return param_ab_launch(false, beta, k, log_f, a, b, nullptr, nullptr, nullptr, B, T, H, K, dtype,
+    return param_ab_launch(false, beta, k, log_f, a, b, nullptr, nullptr, nullptr, B, T, H, K, dtype, dtype, 0,
                            static_cast<cudaStream_t>(cuda_stream));
 }
 
@@ -176,7 +183,7 @@ int hdla_param_ab_bwd(const void* beta, const void* k, const void* log_f, const 
     if (dtype != HDLA_F32 && dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", dtype);
     begin_call(static_cast<cudaStream_t>(cuda_stream));
     return param_ab_launch(true, beta, k, log_f, const_cast<void*>(da), const_cast<void*>(db), dbeta, dk, dlog_f, B, T,
-                           H, K, dtype, static_cast<cudaStream_t>(cuda_stream));
+                           H, K, dtype, dtype, 0, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int hdla_norm_gate_fwd(const void* x, const void* gate, const void* weight, void* o, int64_t rows, int32_t D,

@@ -42,11 +42,14 @@ struct PrepP {
     int* status;
     int Kd, Vd;                           // head dims of the public tensors (multiples of 8, <= 128); the tiles are padded with zeros
     const int2* chunk_tab;                // variable-length batches: (first token, tokens) per chunk, else null
+    const __nv_bfloat16* beta;            // in-operator a/b parametrisation: [B,T,H]; a and b are not read, gk is log_f
 };
 
 // the seven 16-byte input pieces one thread handles per step: (row r, column group kc) of q, k, v, a0, a1, b0, b1
+// (with the in-operator a/b parametrisation only q, k, v are read)
 struct PrepIn { uint4 q, k, v, a0, a1, b0, b1; };
 
+template <bool AB>
 __device__ __forceinline__ PrepIn prep_load(const PrepP& p, int b, int h, int t0, int valid, int blk, int lane) {
     const int r = (blk >> 2) * 8 + (lane & 7);
     const int kc = (blk & 3) * 4 + (lane >> 3);
@@ -58,19 +61,27 @@ __device__ __forceinline__ PrepIn prep_load(const PrepP& p, int b, int h, int t0
         const size_t sa1 = sa0 + (size_t)p.H * p.Kd;
         x.q = __ldg(reinterpret_cast<const uint4*>(p.q + src));
         x.k = __ldg(reinterpret_cast<const uint4*>(p.k + src));
-        x.a0 = __ldg(reinterpret_cast<const uint4*>(p.a + sa0));
-        x.a1 = __ldg(reinterpret_cast<const uint4*>(p.a + sa1));
-        x.b0 = __ldg(reinterpret_cast<const uint4*>(p.b + sa0));
-        x.b1 = __ldg(reinterpret_cast<const uint4*>(p.b + sa1));
+        if (!AB) {
+            x.a0 = __ldg(reinterpret_cast<const uint4*>(p.a + sa0));
+            x.a1 = __ldg(reinterpret_cast<const uint4*>(p.a + sa1));
+            x.b0 = __ldg(reinterpret_cast<const uint4*>(p.b + sa0));
+            x.b1 = __ldg(reinterpret_cast<const uint4*>(p.b + sa1));
+        }
     }
     if (r < valid && kc * 8 < p.Vd)
         x.v = __ldg(reinterpret_cast<const uint4*>(p.v + (((size_t)b * p.T + t0 + r) * p.H + h) * p.Vd + kc * 8));
     return x;
 }
 
+// AB: the layer's a/b parametrisation (HRDPLR/hdla_custom.py:19-43) on the way:  with ef = e^{log_f} (log_f = gk),
+//   a0 = -beta k,  a1 = a0 (ef + s),  s = -beta sum_K ef k^2,  b0 = ef k,  b1 = k      (rows 2t, 2t+1 of a / b)
+// s needs whole rows: the cumulative-sum phase, where a warp holds 16 complete rows of log_f, also loads those rows
+// of k and reduces ef k^2 over the warp; ef of a piece in the hat loop is e^{gi - ge}.
+template <bool AB>
 __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
     __shared__ float gis[C][K + 4];
     __shared__ float tot[4][K];
+    __shared__ float2 beta_s[AB ? C : 1];           // (beta, s) per row
     const long long g = blockIdx.x;
     const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
     const int b = bh / p.H, h = bh % p.H;
@@ -81,7 +92,7 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
     // before the decay sums (they do not depend on them), and inside the loop the next step's pieces are
     // requested before the current step's arithmetic and stores.
     if (tid == 0) TL(0);
-    PrepIn cur = prep_load(p, b, h, t0, valid, warp * 8, lane);
+    PrepIn cur = prep_load<AB>(p, b, h, t0, valid, warp * 8, lane);
     {   // two-level cumulative sum: warp w owns rows [16w, 16w+16), lane owns 4 columns
         // (all sixteen loads are issued before the first value is used: the dtype branch stays outside the loops)
         float4 x[16];
@@ -103,6 +114,27 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
             for (int i = 0; i < 16; ++i)
                 x[i] = make_float4(__uint_as_float(raw[i].x << 16), __uint_as_float(raw[i].x & 0xffff0000u),
                                    __uint_as_float(raw[i].y << 16), __uint_as_float(raw[i].y & 0xffff0000u));
+        }
+        if (AB) {
+            const __nv_bfloat16* ksrc = p.k + row0;
+            uint2 kraw[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                kraw[i] = i < nrow ? __ldg(reinterpret_cast<const uint2*>(ksrc + i * rstride)) : make_uint2(0u, 0u);
+            const int myrow = warp * 16 + (lane & 15);
+            const float beta = myrow < valid ? __bfloat162float(p.beta[((size_t)b * p.T + t0 + myrow) * p.H + h]) : 0.f;
+            float mine = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float k0 = __uint_as_float(kraw[i].x << 16), k1 = __uint_as_float(kraw[i].x & 0xffff0000u);
+                const float k2 = __uint_as_float(kraw[i].y << 16), k3 = __uint_as_float(kraw[i].y & 0xffff0000u);
+                float part = __expf(x[i].x) * k0 * k0 + __expf(x[i].y) * k1 * k1 + __expf(x[i].z) * k2 * k2 +
+                             __expf(x[i].w) * k3 * k3;
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) part += __shfl_xor_sync(0xffffffffu, part, d);
+                if ((lane & 15) == i) mine = part;
+            }
+            if (lane < 16) beta_s[myrow] = make_float2(beta, -beta * mine);
         }
         float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -146,7 +178,7 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
         const int r = (blk >> 2) * 8 + (lane & 7);
         const int kc = (blk & 3) * 4 + (lane >> 3);
         PrepIn nxt = cur;
-        if (it < 7) nxt = prep_load(p, b, h, t0, valid, blk + 1, lane);
+        if (it < 7) nxt = prep_load<AB>(p, b, h, t0, valid, blk + 1, lane);
         float gi[8], ge[8], hf[8];
         {
             const float4 g0 = *reinterpret_cast<const float4*>(&gis[r][kc * 8]);
@@ -177,7 +209,24 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
         for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
         p.Kh[(size_t)g * CH64 + kc * 64 + r] = t8::pack8(y);
         p.Vc[(size_t)g * CH64 + kc * 64 + r] = cur.v;
-        {   // rows 2r, 2r+1 of Ah / Bh are adjacent chunks: one 32-byte store each
+        if (AB) {   // x still holds this piece of k
+            const float2 bs = beta_s[r];
+            float a0[8], z[8];
+            uint4 c0, c1;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { a0[j] = -bs.x * x[j]; y[j] = a0[j] * ea[j]; }
+            c0 = t8::pack8(y);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { z[j] = __expf(gi[j] - ge[j]); y[j] = a0[j] * (z[j] + bs.y) * ea[j]; }
+            c1 = t8::pack8(y);
+            sm100::st_global_32B(p.Ah + (size_t)g * CH128 + kc * 128 + r * R, c0, c1);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { y[j] = z[j] * x[j] * em[j]; z[j] = x[j] * em[j]; }
+            c0 = t8::pack8(y);
+            c1 = t8::pack8(z);
+            sm100::st_global_32B(p.Bh + (size_t)g * CH128 + kc * 128 + r * R, c0, c1);
+            *reinterpret_cast<uint4*>(p.ghat + (size_t)g * C * K + (size_t)r * K + kc * 8) = t8::pack8(ep);
+        } else {   // rows 2r, 2r+1 of Ah / Bh are adjacent chunks: one 32-byte store each
             uint4 c0, c1;
             t8::unpack8(cur.a0, x);
 #pragma unroll
@@ -1673,7 +1722,9 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     const TcPlan pl = make_tc_plan(d);
     // a workspace sized for the backward pass also receives what only the backward kernels read
     const bool save_bwd = ws_bytes >= pl.total;
-    const bool unfused = !(d.flags & HDLA_FLAG_FUSED_PREP) || d.K != K || d.V != V;    // the one-kernel form needs full head dims
+    const bool param_ab = (d.flags & HDLA_FLAG_PARAM_AB) != 0;
+    // the one-kernel form needs full head dims and reads a and b as tensors
+    const bool unfused = !(d.flags & HDLA_FLAG_FUSED_PREP) || d.K != K || d.V != V || param_ab;
     static thread_local int attr_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1720,8 +1771,10 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
             TRY(tc_launch_chunk_prep(pl, d, q, k, v, a, b, gk, scale, ws, save_bwd, st));
         } else {
             PrepP pp{(bp)q, (bp)k, (bp)v, (bp)a, (bp)b, gk, U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc),
-                     F(pl.E), (__nv_bfloat16*)(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status, d.K, d.V, chunk_tab};
-            launch(prep_hat_kernel, dim3(G), dim3(128), 0, st, pp);
+                     F(pl.E), (__nv_bfloat16*)(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status, d.K, d.V, chunk_tab,
+                     param_ab ? (bp)a : nullptr};
+            if (param_ab) launch(prep_hat_kernel<true>, dim3(G), dim3(128), 0, st, pp);
+            else launch(prep_hat_kernel<false>, dim3(G), dim3(128), 0, st, pp);
             HDLA_CHECK_LAUNCH("prep_hat_kernel");
             GramP gp{U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Aqk), U4(pl.Aqb), U4(pl.Aak), U4(pl.Aab), status};
             launch(gram_tc_kernel, dim3(G), dim3(128), 98304 + 1024, st, gp);
@@ -1840,6 +1893,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         TRY(tc_chunk_fwd(df, q, k, v, a, b, gk, scale, h0, nullptr, nullptr, ws, make_tc_plan(df).total, false, st));
     }
     const TcPlan pl = make_tc_plan(d);
+    const bool param_ab = (d.flags & HDLA_FLAG_PARAM_AB) != 0;
     auto U4 = [&](size_t off) { return reinterpret_cast<uint4*>(ws + off); };
     auto F = [&](size_t off) { return reinterpret_cast<float*>(ws + off); };
     int* status = reinterpret_cast<int*>(ws + pl.status);
@@ -1930,11 +1984,15 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     // --- everything else: hat-operand gradients, dv, un-gating, dgk
     GradP gp{U4(pl.Hs), U4(pl.Bh), U4(pl.dOc), U4(pl.Kh), U4(pl.dAqb), U4(pl.dAqk), U4(pl.DE), U4(pl.dP), U4(pl.Aak),
              U4(pl.Aqk), U4(pl.dW), U4(pl.M), U4(pl.dAab), U4(pl.dAak), U4(pl.V2), U4(pl.Ah), U4(pl.Qh), U4(pl.Vc),
-             (bp)(ws + pl.ghat), F(pl.E), F(pl.dgl), (bp)dq, (bp)dk, (bp)dv, (bp)da, (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype,
+             (bp)(ws + pl.ghat), F(pl.E), F(pl.dgl), (bp)dq, (bp)dk, (bp)dv, param_ab ? (bp)(ws + pl.dab) : (bp)da,
+             param_ab ? (bp)(ws + pl.dab + pl.dab_half) : (bp)db, dgk, scale, d.T, d.H, pl.NT, d.gk_dtype,
              status, (long long)G, d.K, d.V, chunk_tab};
     const unsigned grad_grid = G < (unsigned)sm_count() ? G : (unsigned)sm_count();    // one persistent CTA per SM
     launch(grad_tc_kernel, dim3(grad_grid), dim3(544), kGradSmem, st, gp);
     HDLA_CHECK_LAUNCH("grad_tc_kernel");
+    if (param_ab)      // da, db -> dbeta (through the `da` argument), and their shares of dk and dgk = dlog_f added in place
+        return param_ab_launch(true, a, k, gk, ws + pl.dab, ws + pl.dab + pl.dab_half, da, dk, dgk, d.B, d.T, d.H, d.K,
+                               d.dtype, d.gk_dtype, 1, st);
     return HDLA_OK;
 }
 

@@ -22,6 +22,8 @@ struct AbP {
     void *dbeta, *dk, *dlog_f;         // backward outputs
     long long rows;                    // B*T*H
     int T, H, K, dt;
+    int gdt;                           // dtype of log_f and dlog_f (the operator's gk may be fp32 next to bf16 tensors)
+    int accumulate;                    // backward: add to what dk and dlog_f already hold (the operator's own shares)
 };
 
 __device__ __forceinline__ void row_index(const AbP& p, long long row, size_t& in_off, size_t& o1, size_t& o2) {
@@ -43,12 +45,12 @@ __global__ void __launch_bounds__(256) param_ab_fwd_kernel(AbP p) {
     float s = 0.f;
     for (int c = lane; c < p.K; c += 32) {
         const float kv = ld_elem(p.k, in + c, p.dt);
-        s += kv * (-beta * __expf(ld_elem(p.log_f, in + c, p.dt)) * kv);
+        s += kv * (-beta * __expf(ld_elem(p.log_f, in + c, p.gdt)) * kv);
     }
     s = warp_sum(s);
     for (int c = lane; c < p.K; c += 32) {
         const float kv = ld_elem(p.k, in + c, p.dt);
-        const float ef = __expf(ld_elem(p.log_f, in + c, p.dt));
+        const float ef = __expf(ld_elem(p.log_f, in + c, p.gdt));
         const float a1 = -beta * kv, at2 = -beta * ef * kv;
         st_elem(p.a, o1 + c, p.dt, a1);
         st_elem(p.a, o2 + c, p.dt, at2 + a1 * s);
@@ -68,7 +70,7 @@ __global__ void __launch_bounds__(256) param_ab_bwd_kernel(AbP p) {
     float s = 0.f, ds = 0.f;
     for (int c = lane; c < p.K; c += 32) {
         const float kv = ld_elem(p.k, in + c, p.dt);
-        const float ef = __expf(ld_elem(p.log_f, in + c, p.dt));
+        const float ef = __expf(ld_elem(p.log_f, in + c, p.gdt));
         s += kv * (-beta * ef * kv);
         ds += (-beta * kv) * ld_elem(p.a, o2 + c, p.dt);
     }
@@ -77,7 +79,7 @@ __global__ void __launch_bounds__(256) param_ab_bwd_kernel(AbP p) {
     float dbeta = 0.f;
     for (int c = lane; c < p.K; c += 32) {
         const float kv = ld_elem(p.k, in + c, p.dt);
-        const float ef = __expf(ld_elem(p.log_f, in + c, p.dt));
+        const float ef = __expf(ld_elem(p.log_f, in + c, p.gdt));
         const float da1 = ld_elem(p.a, o1 + c, p.dt), da2 = ld_elem(p.a, o2 + c, p.dt);
         const float db1 = ld_elem(p.b, o1 + c, p.dt), db2 = ld_elem(p.b, o2 + c, p.dt);
         const float at2 = -beta * ef * kv;
@@ -89,8 +91,13 @@ __global__ void __launch_bounds__(256) param_ab_bwd_kernel(AbP p) {
         dk += ef * db1 + db2;                        // b1 = ef k, b2 = k
         const float def = -beta * kv * dat2 + kv * db1;
         dbeta += -ef * kv * dat2 - kv * da1t;
+        float dlf = def * ef;
+        if (p.accumulate) {
+            dk += ld_elem(p.dk, in + c, p.dt);
+            dlf += ld_elem(p.dlog_f, in + c, p.gdt);
+        }
         st_elem(p.dk, in + c, p.dt, dk);
-        st_elem(p.dlog_f, in + c, p.dt, def * ef);
+        st_elem(p.dlog_f, in + c, p.gdt, dlf);
     }
     dbeta = warp_sum(dbeta);
     if (lane == 0) st_elem(p.dbeta, (size_t)row, p.dt, dbeta);
@@ -120,7 +127,7 @@ __global__ void __launch_bounds__(256) param_ab_fwd_vec_kernel(AbP p) {
         const int pc = l + j * kAbLanes;
         if (live && pc < npiece) {
             ld_elem8(p.k, in + pc * 8, p.dt, kv[j]);
-            ld_elem8(p.log_f, in + pc * 8, p.dt, ef[j]);
+            ld_elem8(p.log_f, in + pc * 8, p.gdt, ef[j]);
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 ef[j][e] = __expf(ef[j][e]);
@@ -163,7 +170,7 @@ __global__ void __launch_bounds__(256) param_ab_bwd_vec_kernel(AbP p) {
         const int pc = l + j * kAbLanes;
         if (live && pc < npiece) {
             ld_elem8(p.k, in + pc * 8, p.dt, kv[j]);
-            ld_elem8(p.log_f, in + pc * 8, p.dt, ef[j]);
+            ld_elem8(p.log_f, in + pc * 8, p.gdt, ef[j]);
             ld_elem8(p.a, o1 + pc * 8, p.dt, da1[j]);
             ld_elem8(p.a, o2 + pc * 8, p.dt, da2[j]);
             ld_elem8(p.b, o1 + pc * 8, p.dt, db1[j]);
@@ -183,7 +190,13 @@ __global__ void __launch_bounds__(256) param_ab_bwd_vec_kernel(AbP p) {
     for (int j = 0; j < PIECES; ++j) {
         const int pc = l + j * kAbLanes;
         if (live && pc < npiece) {
-            float dk[8], dlf[8];
+            float dk[8], dlf[8], dk0[8], dlf0[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dk0[e] = dlf0[e] = 0.f;
+            if (p.accumulate) {
+                ld_elem8(p.dk, in + pc * 8, p.dt, dk0);
+                ld_elem8(p.dlog_f, in + pc * 8, p.gdt, dlf0);
+            }
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const float k = kv[j][e], f = ef[j][e];
@@ -194,12 +207,12 @@ __global__ void __launch_bounds__(256) param_ab_bwd_vec_kernel(AbP p) {
                 g += -beta * f * dat2;                       // at2 = -beta ef k
                 g += -beta * da1t;                           // a1 = -beta k
                 g += f * db1[j][e] + db2[j][e];              // b1 = ef k, b2 = k
-                dk[e] = g;
-                dlf[e] = (-beta * k * dat2 + k * db1[j][e]) * f;
+                dk[e] = g + dk0[e];
+                dlf[e] = (-beta * k * dat2 + k * db1[j][e]) * f + dlf0[e];
                 dbeta += -f * k * dat2 - k * da1t;
             }
             st_elem8(p.dk, in + pc * 8, p.dt, dk);
-            st_elem8(p.dlog_f, in + pc * 8, p.dt, dlf);
+            st_elem8(p.dlog_f, in + pc * 8, p.gdt, dlf);
         }
     }
     dbeta = sub_sum(dbeta);
@@ -209,8 +222,9 @@ __global__ void __launch_bounds__(256) param_ab_bwd_vec_kernel(AbP p) {
 }  // namespace
 
 int param_ab_launch(bool backward, const void* beta, const void* k, const void* log_f, void* a, void* b, void* dbeta,
-                    void* dk, void* dlog_f, int B, int T, int H, int K, int dt, cudaStream_t st) {
-    AbP p{beta, k, log_f, a, b, dbeta, dk, dlog_f, (long long)B * T * H, T, H, K, dt};
+                    void* dk, void* dlog_f, int B, int T, int H, int K, int dt, int gdt, int accumulate,
+                    cudaStream_t st) {
+    AbP p{beta, k, log_f, a, b, dbeta, dk, dlog_f, (long long)B * T * H, T, H, K, dt, gdt, accumulate};
     bool aligned = true;
     for (const void* q : {k, log_f, (const void*)a, (const void*)b, (const void*)dk, (const void*)dlog_f})
         aligned = aligned && reinterpret_cast<uintptr_t>(q) % 16 == 0;

@@ -24,6 +24,7 @@ struct TcPlan {
     int lead_real;                     // the first segment in scan order is scanned for real in the first pass
     size_t Tseg, Fseg, Sin;            // per (b, h, segment): transition [K,K], state from zero [K,V], entering state [K,V]
     size_t dOc, dAqk, dAqb, DV2, DE, dgl, dW, dP, dAak, dAab;
+    size_t dab, dab_half;              // in-operator a/b parametrisation: da then db, dab_half bytes each
     size_t total_fwd, total;
     int nseq;                          // sequences of a packed variable-length batch, 0 otherwise
     size_t chunk_tab, seq_tab;         // int2 per chunk: (first token, tokens);  int2 per sequence: (first chunk, chunks)
@@ -65,7 +66,8 @@ inline TcPlan make_tc_plan(const HdlaDims& d) {
     // forward region: what the scan and the output kernel read.  The fused preparation kernel (HDLA_FLAG_FUSED_PREP)
     // keeps Aab on chip and writes Ah, Aak, M, P and the un-gating factors only for a backward pass, so with it
     // those live in the backward region; the four-kernel preparation passes them from kernel to kernel.
-    const bool fused = (d.flags & HDLA_FLAG_FUSED_PREP) != 0 && d.K == K && d.V == V;    // (it needs full head dims)
+    // (it needs full head dims and does not form a and b itself)
+    const bool fused = (d.flags & HDLA_FLAG_FUSED_PREP) != 0 && d.K == K && d.V == V && !(d.flags & HDLA_FLAG_PARAM_AB);
     p.Qh = take(16384); p.Kh = take(16384); p.Bh = take(32768); p.Vc = take(16384);
     p.E = take(K * 4);
     p.Aqk = take(8192); p.Aqb = take(16384);
@@ -111,6 +113,10 @@ inline TcPlan make_tc_plan(const HdlaDims& d) {
     }
     p.dOc = take(16384); p.dAqk = take(8192); p.dAqb = take(16384); p.DV2 = take(32768); p.DE = take(32768);
     p.dgl = take(K * 4); p.dW = take(32768); p.dP = take(32768); p.dAak = take(16384); p.dAab = take(32768);
+    // in-operator a/b parametrisation: da and db, each [B, 2T, H, K] bf16 in the public layout, stay here for the
+    // parametrisation's backward kernel
+    p.dab_half = (((size_t)d.B * d.T * R * d.H * d.K * 2 + 255) / 256) * 256;
+    p.dab = off; off += (d.flags & HDLA_FLAG_PARAM_AB) ? 2 * p.dab_half : 0;
     p.total = off;
     return p;
 }

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define HDLA_VERSION 101
+#define HDLA_VERSION 102
 
 #if defined(__GNUC__)
 #define HDLA_API __attribute__((visibility("default")))
@@ -56,6 +56,19 @@ extern "C" {
                                        but runs about 5 % slower on large problems (two CTAs of four warps per SM do
                                        not hide its latencies); the workspace layout depends on it, so a forward
                                        and its backward must agree on the flag.                                   */
+
+#define HDLA_FLAG_PARAM_AB      8   /* bf16 tensor-core pipeline: the layer's a/b parametrisation
+                                       (HRDPLR/hdla_custom.py:19-43, called at :290) happens inside the operator.
+                                       Argument `a` then points to beta [B,T,H] (dtype of q), `b` is ignored (may
+                                       be null) and gk is the layer's log_f; the preparation kernel forms
+                                         a_{t,1} = -beta k,  a_{t,2} = -beta k (e^{log_f} + s),  s = -beta sum_K e^{log_f} k^2,
+                                         b_{t,1} = e^{log_f} k,  b_{t,2} = k
+                                       in fp32 on the way to its operand tiles, so a and b never exist in memory.
+                                       hdla_chunk_bwd with the flag writes dbeta [B,T,H] through `da`, ignores `db`,
+                                       and dk and dgk (= dlog_f) contain the parametrisation's share (its backward
+                                       runs as one more kernel over gradients kept in the workspace).  A forward
+                                       and its backward must agree on the flag; problems outside the tensor-core
+                                       pipeline report HDLA_ERR_UNSUPPORTED (use hdla_param_ab_fwd/_bwd there).   */
 
 /* Phase selector (bits 4..7 of HdlaDims.flags), for callers that split a sequence over devices
  * (context parallelism).  Only the inter-chunk scan depends on the incoming state, so a call can be cut:

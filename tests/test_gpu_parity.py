@@ -527,6 +527,66 @@ def _param_ab_torch(beta, k, log_f):
     return a, b
 
 
+def _layer_inputs(B, T, H, K, V, seed, gk_div):
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s_: torch.randn(*s_, generator=g)
+    x = dict(q=torch.nn.functional.normalize(rn(B, T, H, K), dim=-1), k=torch.nn.functional.normalize(rn(B, T, H, K), dim=-1),
+             v=rn(B, T, H, V), beta=2 * torch.sigmoid(rn(B, T, H, 1)),
+             log_f=torch.nn.functional.logsigmoid(rn(B, T, H, K)) / gk_div, do=rn(B, T, H, V),
+             h0=0.2 * rn(B, H, K, V), dht=rn(B, H, K, V))
+    return x
+
+
+@pytest.mark.parametrize("B,T,H,K,V,fdt,gk_div", [(2, 300, 2, 128, 128, torch.bfloat16, 16.0),
+                                                  (1, 640, 3, 128, 128, torch.float32, 1.0),
+                                                  (2, 200, 2, 64, 32, torch.bfloat16, 4.0)])
+def test_chunk_hdla_parametrisation_inside_the_operator(dev, B, T, H, K, V, fdt, gk_div):
+    """`chunk_hdla_delta_rule(q, k, v, beta, log_f)` -- a and b formed inside the chunk-preparation kernel, their
+    backward folded into dk, dlog_f, dbeta by the library -- against the fp64 oracle fed with the a, b of the
+    reference's parameterize_a_b (HRDPLR/hdla_custom.py:19-43, :290-309), and against the two-call route on the GPU.
+    Ragged tails, initial state, dht, log_f in bf16 and fp32, head dims below 128, the layer's undivided decay."""
+    from hdla_impl_b200.layer_ops import chunk_hdla_delta_rule, parameterize_a_b
+    import hdla_impl_b200 as Hm
+    from hdla_impl_b200 import _lib
+    x = _layer_inputs(B, T, H, K, V, seed=31, gk_div=gk_div)
+    bf = torch.bfloat16
+    dts = dict(q=bf, k=bf, v=bf, beta=bf, log_f=fdt)
+    names = ["q", "k", "v", "beta", "log_f"]
+    # oracle in fp64 on the values the device sees
+    rl = {n: x[n].to(dts[n]).double().requires_grad_(True) for n in names}
+    h0r = x["h0"].double().requires_grad_(True)
+    ra, rb = _param_ab_torch(rl["beta"], rl["k"], rl["log_f"])
+    ro, rht = orc.chunked_ref(rl["q"], rl["k"], rl["v"], ra, rb, rl["log_f"], 2, 1.0, h0r, True, 64)
+    rg = torch.autograd.grad((ro * x["do"].to(bf).double()).sum() + (rht * x["dht"].double()).sum(),
+                             [rl[n] for n in names] + [h0r])
+    ref = dict(o=ro, ht=rht, **{"d" + n: g_ for n, g_ in zip(names + ["h0"], rg)})
+
+    def run(fn):
+        lv = {n: x[n].to(dts[n]).to(dev).requires_grad_(True) for n in names}
+        h0 = x["h0"].to(dev).requires_grad_(True)
+        o, ht = fn(lv, h0)
+        gr = torch.autograd.grad((o.float() * x["do"].to(bf).to(dev).float()).sum() + (ht * x["dht"].to(dev)).sum(),
+                                 [lv[n] for n in names] + [h0])
+        return dict(o=o, ht=ht, **{"d" + n: g_ for n, g_ in zip(names + ["h0"], gr)})
+
+    n0 = _lib.kernel_launches()
+    got = run(lambda lv, h0: chunk_hdla_delta_rule(lv["q"], lv["k"], lv["v"], lv["beta"], lv["log_f"], scale=1.0,
+                                                   initial_state=h0, output_final_state=True))
+    launches = _lib.kernel_launches() - n0
+    assert got["dbeta"].shape == x["beta"].shape and got["dlog_f"].dtype == fdt
+    assert_close(got, ref, 2e-2, "in-operator parametrisation")
+    if T // 64 < 8:                  # one-level scans: the ten operator kernels and the parametrisation's backward
+        assert launches == 11, launches
+
+    def two_calls(lv, h0):
+        a, b = parameterize_a_b(lv["beta"], lv["k"], lv["log_f"])
+        return Hm.chunk_hrdplr_delta_rule(lv["q"], lv["k"], lv["v"], a, b, lv["log_f"], 2, scale=1.0,
+                                          initial_state=h0, output_final_state=True, chunk_size=64)
+    if fdt == bf:
+        assert_close(run(two_calls), ref, 2e-2, "two-call route")
+    Hm.check_status(dev, wait=True)
+
+
 @pytest.mark.parametrize("K", [96, 128, 200, 100])   # one piece per lane, full rows, two pieces, scalar kernels
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
 def test_parameterize_a_b_forward_backward(dev, dtype, tol, K):

@@ -122,3 +122,20 @@ def test_tensor_core_pipeline_selection():
     assert uses(2, 256, 2, 128, 128, 2, 64, 0, 0, 0) == 0         # fp32 inputs
     assert uses(2, 256, 2, 128, 128, 2, 64, 1, 0, _lib.FLAG_FORCE_SIMT) == 0
     assert uses(2, 256, 2, 64, 64, 2, 64, 1, 0, _lib.PHASE_PRE) == 0      # phased calls need the full 128 x 128
+
+
+def test_in_operator_parametrisation_flag_is_sized_and_gated_on_the_host():
+    """HDLA_FLAG_PARAM_AB: the backward workspace grows by the two gradient tensors [B, 2T, H, K] bf16 that stay inside
+    the library, the forward workspace does not change, and problems outside the tensor-core pipeline are refused."""
+    lib = _lib.load()
+    B, T, H, K = 2, 256, 2, 128
+    plain = _lib.HdlaDims(B, T, H, K, 128, 2, 64, 1, 0, 0)
+    fused = _lib.HdlaDims(B, T, H, K, 128, 2, 64, 1, 0, _lib.FLAG_PARAM_AB)
+    assert lib.hdla_chunk_workspace_bytes(C.byref(fused), 0) == lib.hdla_chunk_workspace_bytes(C.byref(plain), 0)
+    grow = lib.hdla_chunk_workspace_bytes(C.byref(fused), 1) - lib.hdla_chunk_workspace_bytes(C.byref(plain), 1)
+    assert grow == 2 * B * 2 * T * H * K * 2
+    fp32 = _lib.HdlaDims(B, T, H, K, 128, 2, 64, 0, 0, _lib.FLAG_PARAM_AB)
+    assert lib.hdla_chunk_workspace_bytes(C.byref(fp32), 1) == 0 and "HDLA_FLAG_PARAM_AB" in _lib.last_error()
+    # with the one-kernel preparation requested as well, the four-kernel layout is planned (that kernel reads a and b)
+    both = _lib.HdlaDims(B, T, H, K, 128, 2, 64, 1, 0, _lib.FLAG_PARAM_AB | _lib.FLAG_FUSED_PREP)
+    assert lib.hdla_chunk_workspace_bytes(C.byref(both), 1) == lib.hdla_chunk_workspace_bytes(C.byref(fused), 1)
