@@ -709,9 +709,23 @@ def bench_layer_call(dev, steps=10):
         return e0.elapsed_time(e1) / steps
 
     t2, t1, tn = timed(two_calls), timed(one_call), timed(norm)
+    # the stand-alone layer kernels by themselves: algorithmic bytes (every element read or written once) / time
+    es, n_ab, n_ng = 2, B * T * H * K, B * T * H * V
+    a, b = parameterize_a_b(beta, k, log_f)
+    ga, gb = torch.randn_like(a), torch.randn_like(b)
+    o_n = rms_norm_fused_gate(x, gate, w, 1e-5)
+    with torch.no_grad():
+        t_abf = timed(lambda: parameterize_a_b(beta, k, log_f))
+        t_ngf = timed(lambda: rms_norm_fused_gate(x, gate, w, 1e-5))
+    t_abb = timed(lambda: torch.autograd.grad([a, b], [beta, k, log_f], [ga, gb], retain_graph=True))
+    t_ngb = timed(lambda: torch.autograd.grad(o_n, [x, gate, w], dn, retain_graph=True))
+    peak = load_peaks()[0]["hbm_gbs"]
+    kern = lambda ms, elems: {"ms": ms, "GBps": elems * es / ms / 1e6, "frac_of_hbm_peak": elems * es / ms / 1e6 / peak}
     return {"workload": "cfg1 shape as the layer calls the operator (q, k, v, beta, log_f; scale 1), bf16, fwd+bwd",
             "two_calls_ms": t2, "one_call_ms": t1, "norm_gate_fwd_bwd_ms": tn,
-            "one_call_tokens_per_s": B * T / (t1 / 1e3), "steps": steps}
+            "one_call_tokens_per_s": B * T / (t1 / 1e3), "steps": steps,
+            "kernels": {"param_ab_fwd": kern(t_abf, 6 * n_ab), "param_ab_bwd": kern(t_abb, 8 * n_ab),
+                        "norm_gate_fwd": kern(t_ngf, 3 * n_ng), "norm_gate_bwd": kern(t_ngb, 5 * n_ng)}}
 
 
 def run_decode(args, rank, world, local_rank):

@@ -17,6 +17,7 @@ FLAG_WS_HOLDS_FWD = 1
 FLAG_FORCE_SIMT = 2
 FLAG_FUSED_PREP = 4
 FLAG_PARAM_AB = 8
+FLAG_NORM_K = 256
 PHASE_ALL, PHASE_PRE, PHASE_TRANSITION, PHASE_STATE, PHASE_POST = 0x00, 0x10, 0x20, 0x30, 0x40
 
 EXPORTS = (

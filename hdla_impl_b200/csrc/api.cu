@@ -72,6 +72,10 @@ size_t hdla_chunk_workspace_bytes(const HdlaDims* dims, int with_backward) {
                                    "(bf16, chunk 64, R=2, K and V multiples of 8 up to 128)");
         return 0;
     }
+    if ((dims->flags & HDLA_FLAG_NORM_K) && !(dims->flags & HDLA_FLAG_PARAM_AB)) {
+        fail(HDLA_ERR_INVALID, "HDLA_FLAG_NORM_K needs HDLA_FLAG_PARAM_AB");
+        return 0;
+    }
     if ((dims->flags & HDLA_FLAG_PARAM_AB) && !tc_supported(*dims)) {
         fail(HDLA_ERR_UNSUPPORTED, "the in-operator a/b parametrisation (HDLA_FLAG_PARAM_AB) needs the bf16 tensor-core "
                                    "pipeline (bf16, chunk 64, R=2, K and V multiples of 8 up to 128)");
@@ -170,7 +174,7 @@ int hdla_param_ab_fwd(const void* beta, const void* k, const void* log_f, void* 
     if (B <= 0 || T <= 0 || H <= 0 || K <= 0) return fail(HDLA_ERR_INVALID, "param_ab_fwd: non-positive dimension");
     if (dtype != HDLA_F32 && dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", dtype);
     begin_call(static_cast<cudaStream_t>(cuda_stream));
-    return param_ab_launch(false, beta, k, log_f, a, b, nullptr, nullptr, nullptr, B, T, H, K, dtype, dtype, 0,
+    return param_ab_launch(false, beta, k, log_f, a, b, nullptr, nullptr, nullptr, B, T, H, K, dtype, dtype, 0, 0,
                            static_cast<cudaStream_t>(cuda_stream));
 }
 
@@ -183,7 +187,7 @@ int hdla_param_ab_bwd(const void* beta, const void* k, const void* log_f, const 
     if (dtype != HDLA_F32 && dtype != HDLA_BF16) return fail(HDLA_ERR_UNSUPPORTED, "dtype %d", dtype);
     begin_call(static_cast<cudaStream_t>(cuda_stream));
     return param_ab_launch(true, beta, k, log_f, const_cast<void*>(da), const_cast<void*>(db), dbeta, dk, dlog_f, B, T,
-                           H, K, dtype, dtype, 0, static_cast<cudaStream_t>(cuda_stream));
+                           H, K, dtype, dtype, 0, 0, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int hdla_norm_gate_fwd(const void* x, const void* gate, const void* weight, void* o, int64_t rows, int32_t D,

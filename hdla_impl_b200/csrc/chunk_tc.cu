@@ -43,6 +43,7 @@ struct PrepP {
     int Kd, Vd;                           // head dims of the public tensors (multiples of 8, <= 128); the tiles are padded with zeros
     const int2* chunk_tab;                // variable-length batches: (first token, tokens) per chunk, else null
     const __nv_bfloat16* beta;            // in-operator a/b parametrisation: [B,T,H]; a and b are not read, gk is log_f
+    int norm_k;                           // ... with k normalised on the way: k <- k / sqrt(sum_K k^2 + kNormEps)
 };
 
 // the seven 16-byte input pieces one thread handles per step: (row r, column group kc) of q, k, v, a0, a1, b0, b1
@@ -76,12 +77,14 @@ __device__ __forceinline__ PrepIn prep_load(const PrepP& p, int b, int h, int t0
 // AB: the layer's a/b parametrisation (HRDPLR/hdla_custom.py:19-43) on the way:  with ef = e^{log_f} (log_f = gk),
 //   a0 = -beta k,  a1 = a0 (ef + s),  s = -beta sum_K ef k^2,  b0 = ef k,  b1 = k      (rows 2t, 2t+1 of a / b)
 // s needs whole rows: the cumulative-sum phase, where a warp holds 16 complete rows of log_f, also loads those rows
-// of k and reduces ef k^2 over the warp; ef of a piece in the hat loop is e^{gi - ge}.
+// of k and reduces ef k^2 over the warp; ef of a piece in the hat loop is e^{gi - ge}.  With norm_k the layer's
+// l2_norm of k (HRDPLR/hdla_custom.py:248, normalizations/l2_norm.py:4-14) happens here too: the same phase reduces
+// k^2, and every use of k below is k / sqrt(sum_K k^2 + eps).
 template <bool AB>
 __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
     __shared__ float gis[C][K + 4];
     __shared__ float tot[4][K];
-    __shared__ float2 beta_s[AB ? C : 1];           // (beta, s) per row
+    __shared__ float4 beta_s[AB ? C : 1];           // (beta, s, 1 / |k| or 1) per row
     const long long g = blockIdx.x;
     const int bh = (int)(g / p.NT), n = (int)(g % p.NT);
     const int b = bh / p.H, h = bh % p.H;
@@ -123,18 +126,23 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
                 kraw[i] = i < nrow ? __ldg(reinterpret_cast<const uint2*>(ksrc + i * rstride)) : make_uint2(0u, 0u);
             const int myrow = warp * 16 + (lane & 15);
             const float beta = myrow < valid ? __bfloat162float(p.beta[((size_t)b * p.T + t0 + myrow) * p.H + h]) : 0.f;
-            float mine = 0.f;
+            float mine = 0.f, mine2 = 0.f;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const float k0 = __uint_as_float(kraw[i].x << 16), k1 = __uint_as_float(kraw[i].x & 0xffff0000u);
                 const float k2 = __uint_as_float(kraw[i].y << 16), k3 = __uint_as_float(kraw[i].y & 0xffff0000u);
                 float part = __expf(x[i].x) * k0 * k0 + __expf(x[i].y) * k1 * k1 + __expf(x[i].z) * k2 * k2 +
                              __expf(x[i].w) * k3 * k3;
+                float sq = k0 * k0 + k1 * k1 + k2 * k2 + k3 * k3;
 #pragma unroll
-                for (int d = 16; d > 0; d >>= 1) part += __shfl_xor_sync(0xffffffffu, part, d);
-                if ((lane & 15) == i) mine = part;
+                for (int d = 16; d > 0; d >>= 1) {
+                    part += __shfl_xor_sync(0xffffffffu, part, d);
+                    sq += __shfl_xor_sync(0xffffffffu, sq, d);
+                }
+                if ((lane & 15) == i) { mine = part; mine2 = sq; }
             }
-            if (lane < 16) beta_s[myrow] = make_float2(beta, -beta * mine);
+            const float rn = p.norm_k ? rsqrtf(mine2 + kNormEps) : 1.f;
+            if (lane < 16) beta_s[myrow] = make_float4(beta, -beta * mine * rn * rn, rn, 0.f);
         }
         float4 run = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -205,12 +213,17 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
         for (int j = 0; j < 8; ++j) y[j] = x[j] * p.scale * ep[j];
         p.Qh[(size_t)g * CH64 + kc * 64 + r] = t8::pack8(y);
         t8::unpack8(cur.k, x);
+        if (AB) {
+            const float rn = beta_s[r].z;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) x[j] *= rn;
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
         p.Kh[(size_t)g * CH64 + kc * 64 + r] = t8::pack8(y);
         p.Vc[(size_t)g * CH64 + kc * 64 + r] = cur.v;
         if (AB) {   // x still holds this piece of k
-            const float2 bs = beta_s[r];
+            const float4 bs = beta_s[r];
             float a0[8], z[8];
             uint4 c0, c1;
 #pragma unroll
@@ -1772,7 +1785,7 @@ int tc_chunk_fwd(const HdlaDims& d, const void* q, const void* k, const void* v,
         } else {
             PrepP pp{(bp)q, (bp)k, (bp)v, (bp)a, (bp)b, gk, U4(pl.Qh), U4(pl.Kh), U4(pl.Ah), U4(pl.Bh), U4(pl.Vc),
                      F(pl.E), (__nv_bfloat16*)(ws + pl.ghat), scale, d.T, d.H, pl.NT, d.gk_dtype, status, d.K, d.V, chunk_tab,
-                     param_ab ? (bp)a : nullptr};
+                     param_ab ? (bp)a : nullptr, (d.flags & HDLA_FLAG_NORM_K) ? 1 : 0};
             if (param_ab) launch(prep_hat_kernel<true>, dim3(G), dim3(128), 0, st, pp);
             else launch(prep_hat_kernel<false>, dim3(G), dim3(128), 0, st, pp);
             HDLA_CHECK_LAUNCH("prep_hat_kernel");
@@ -1992,7 +2005,7 @@ int tc_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* v,
     HDLA_CHECK_LAUNCH("grad_tc_kernel");
     if (param_ab)      // da, db -> dbeta (through the `da` argument), and their shares of dk and dgk = dlog_f added in place
         return param_ab_launch(true, a, k, gk, ws + pl.dab, ws + pl.dab + pl.dab_half, da, dk, dgk, d.B, d.T, d.H, d.K,
-                               d.dtype, d.gk_dtype, 1, st);
+                               d.dtype, d.gk_dtype, 1, (d.flags & HDLA_FLAG_NORM_K) ? 1 : 0, st);
     return HDLA_OK;
 }
 

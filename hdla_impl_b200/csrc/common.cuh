@@ -105,8 +105,11 @@ int simt_chunk_bwd(const HdlaDims& d, const void* q, const void* k, const void* 
                    void* dk, void* dv, void* da, void* db, void* dgk, float* dh0, float* ws, cudaStream_t st);
 
 int param_ab_launch(bool backward, const void* beta, const void* k, const void* log_f, void* a, void* b, void* dbeta,
-                    void* dk, void* dlog_f, int B, int T, int H, int K, int dt, int gdt, int accumulate,
+                    void* dk, void* dlog_f, int B, int T, int H, int K, int dt, int gdt, int accumulate, int norm_k,
                     cudaStream_t st);
+
+// eps of the layer's l2_norm of k (HRDPLR/normalizations/l2_norm.py:4): k / sqrt(sum_K k^2 + eps)
+constexpr float kNormEps = 1e-5f;
 
 int norm_gate_launch(bool backward, const void* x, const void* gate, const void* weight, const void* d_o, void* o,
                      void* dx, void* dgate, float* dweight, long long rows, int D, float eps, int dt, cudaStream_t st);

@@ -24,6 +24,8 @@ struct AbP {
     int T, H, K, dt;
     int gdt;                           // dtype of log_f and dlog_f (the operator's gk may be fp32 next to bf16 tensors)
     int accumulate;                    // backward: add to what dk and dlog_f already hold (the operator's own shares)
+    int norm_k;                        // backward (vector kernel): k was normalised on the way in, k / sqrt(sum k^2 + eps);
+                                       // everything is taken at the normalised k and dk goes back through the norm
 };
 
 __device__ __forceinline__ void row_index(const AbP& p, long long row, size_t& in_off, size_t& o1, size_t& o2) {
@@ -164,12 +166,30 @@ __global__ void __launch_bounds__(256) param_ab_bwd_vec_kernel(AbP p) {
     if (live) row_index(p, row, in, o1, o2);
     const float beta = live ? ld_elem(p.beta, (size_t)row, p.dt) : 0.f;
     float kv[PIECES][8], ef[PIECES][8], da1[PIECES][8], da2[PIECES][8], db1[PIECES][8], db2[PIECES][8];
-    float s = 0.f, ds = 0.f;
+    float s = 0.f, ds = 0.f, rn = 1.f;
+#pragma unroll
+    for (int j = 0; j < PIECES; ++j) {
+        const int pc = l + j * kAbLanes;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) kv[j][e] = 0.f;
+        if (live && pc < npiece) ld_elem8(p.k, in + pc * 8, p.dt, kv[j]);
+    }
+    if (p.norm_k) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < PIECES; ++j)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(kv[j][e], kv[j][e], ss);
+        rn = rsqrtf(sub_sum(ss) + kNormEps);
+#pragma unroll
+        for (int j = 0; j < PIECES; ++j)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) kv[j][e] *= rn;
+    }
 #pragma unroll
     for (int j = 0; j < PIECES; ++j) {
         const int pc = l + j * kAbLanes;
         if (live && pc < npiece) {
-            ld_elem8(p.k, in + pc * 8, p.dt, kv[j]);
             ld_elem8(p.log_f, in + pc * 8, p.gdt, ef[j]);
             ld_elem8(p.a, o1 + pc * 8, p.dt, da1[j]);
             ld_elem8(p.a, o2 + pc * 8, p.dt, da2[j]);
@@ -185,12 +205,15 @@ __global__ void __launch_bounds__(256) param_ab_bwd_vec_kernel(AbP p) {
     }
     s = sub_sum(s);
     ds = sub_sum(ds);
-    float dbeta = 0.f;
+    float dbeta = 0.f, kdk = 0.f;
+    float dk[PIECES][8];
 #pragma unroll
     for (int j = 0; j < PIECES; ++j) {
         const int pc = l + j * kAbLanes;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dk[j][e] = 0.f;
         if (live && pc < npiece) {
-            float dk[8], dlf[8], dk0[8], dlf0[8];
+            float dlf[8], dk0[8], dlf0[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) dk0[e] = dlf0[e] = 0.f;
             if (p.accumulate) {
@@ -207,12 +230,24 @@ __global__ void __launch_bounds__(256) param_ab_bwd_vec_kernel(AbP p) {
                 g += -beta * f * dat2;                       // at2 = -beta ef k
                 g += -beta * da1t;                           // a1 = -beta k
                 g += f * db1[j][e] + db2[j][e];              // b1 = ef k, b2 = k
-                dk[e] = g + dk0[e];
+                dk[j][e] = g + dk0[e];
+                kdk = fmaf(k, dk[j][e], kdk);
                 dlf[e] = (-beta * k * dat2 + k * db1[j][e]) * f + dlf0[e];
                 dbeta += -f * k * dat2 - k * da1t;
             }
-            st_elem8(p.dk, in + pc * 8, p.dt, dk);
             st_elem8(p.dlog_f, in + pc * 8, p.gdt, dlf);
+        }
+    }
+    if (p.norm_k) kdk = sub_sum(kdk);                        // k_n = k rn:  dk = rn (dk_n - k_n (k_n . dk_n))
+#pragma unroll
+    for (int j = 0; j < PIECES; ++j) {
+        const int pc = l + j * kAbLanes;
+        if (live && pc < npiece) {
+            if (p.norm_k) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) dk[j][e] = rn * (dk[j][e] - kv[j][e] * kdk);
+            }
+            st_elem8(p.dk, in + pc * 8, p.dt, dk[j]);
         }
     }
     dbeta = sub_sum(dbeta);
@@ -222,9 +257,9 @@ __global__ void __launch_bounds__(256) param_ab_bwd_vec_kernel(AbP p) {
 }  // namespace
 
 int param_ab_launch(bool backward, const void* beta, const void* k, const void* log_f, void* a, void* b, void* dbeta,
-                    void* dk, void* dlog_f, int B, int T, int H, int K, int dt, int gdt, int accumulate,
+                    void* dk, void* dlog_f, int B, int T, int H, int K, int dt, int gdt, int accumulate, int norm_k,
                     cudaStream_t st) {
-    AbP p{beta, k, log_f, a, b, dbeta, dk, dlog_f, (long long)B * T * H, T, H, K, dt, gdt, accumulate};
+    AbP p{beta, k, log_f, a, b, dbeta, dk, dlog_f, (long long)B * T * H, T, H, K, dt, gdt, accumulate, norm_k};
     bool aligned = true;
     for (const void* q : {k, log_f, (const void*)a, (const void*)b, (const void*)dk, (const void*)dlog_f})
         aligned = aligned && reinterpret_cast<uintptr_t>(q) % 16 == 0;
@@ -241,6 +276,7 @@ int param_ab_launch(bool backward, const void* beta, const void* k, const void* 
         HDLA_CHECK_LAUNCH(backward ? "param_ab_bwd_vec_kernel" : "param_ab_fwd_vec_kernel");
         return HDLA_OK;
     }
+    if (norm_k) return fail(HDLA_ERR_INVALID, "param_ab: the normalised-k form needs 16-byte aligned tensors and K a multiple of 8");
     const unsigned blocks = (unsigned)((p.rows + 7) / 8);
     if (backward) param_ab_bwd_kernel<<<blocks, 256, 0, st>>>(p);
     else param_ab_fwd_kernel<<<blocks, 256, 0, st>>>(p);

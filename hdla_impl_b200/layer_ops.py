@@ -73,7 +73,7 @@ class _ChunkHdla(torch.autograd.Function):
     @staticmethod
     @_op.contiguous
     @_op.autocast_custom_fwd
-    def forward(ctx, q, k, v, beta, log_f, scale, initial_state, output_final_state, cu_seqlens):
+    def forward(ctx, q, k, v, beta, log_f, scale, initial_state, output_final_state, cu_seqlens, normalize_k=False):
         dev = _lib.require_cuda(q, k, v, beta, log_f, initial_state)
         _op.check_status(dev)
         lib = _lib.load()
@@ -83,7 +83,8 @@ class _ChunkHdla(torch.autograd.Function):
         beta_c = beta.to(q.dtype).contiguous()
         keep = _op.save_workspace_default() and any(
             isinstance(t, torch.Tensor) and t.requires_grad for t in (q, k, v, beta, log_f, initial_state))
-        dims = _op._dims(q, v, beta_c, log_f, 2, 64, _lib.FLAG_PARAM_AB, cu_seqlens)
+        ctx.flags = _lib.FLAG_PARAM_AB | (_lib.FLAG_NORM_K if normalize_k else 0)
+        dims = _op._dims(q, v, beta_c, log_f, 2, 64, ctx.flags, cu_seqlens)
         h0 = None if initial_state is None else initial_state.to(torch.float32).contiguous()
         with torch.cuda.device(dev):
             ws = _op._alloc_ws(_op.workspace_bytes(dims, keep), dev)
@@ -114,7 +115,7 @@ class _ChunkHdla(torch.autograd.Function):
         _op.check_status(dev)
         lib = _lib.load()
         ws, ctx.ws = ctx.ws, None
-        flags = _lib.FLAG_PARAM_AB | (_lib.FLAG_WS_HOLDS_FWD if ws is not None else 0)
+        flags = ctx.flags | (_lib.FLAG_WS_HOLDS_FWD if ws is not None else 0)
         dims = _op._dims(q, v, beta, log_f, 2, 64, flags, ctx.cu_seqlens)
         h0 = None if initial_state is None else initial_state.to(torch.float32).contiguous()
         if do.dtype != q.dtype:
@@ -136,10 +137,11 @@ class _ChunkHdla(torch.autograd.Function):
         if dh0 is not None and initial_state.dtype != torch.float32:
             dh0 = dh0.to(initial_state.dtype)
         shape, dtype = ctx.beta_like
-        return dq, dk, dv, dbeta.view(shape).to(dtype), dlog_f, None, dh0, None, None
+        return dq, dk, dv, dbeta.view(shape).to(dtype), dlog_f, None, dh0, None, None, None
 
 
 _warned_two_call = False
+L2_NORM_EPS = 1e-5      # of the reference's l2_norm (HRDPLR/normalizations/l2_norm.py:4)
 
 
 @torch.compiler.disable
@@ -153,11 +155,14 @@ def chunk_hdla_delta_rule(
     initial_state: Optional[torch.Tensor] = None,
     output_final_state: bool = False,
     cu_seqlens=None,
+    normalize_k: bool = False,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """What the reference layer computes with ``a, b = parameterize_a_b(beta, k, log_f)`` followed by
     ``chunk_hrdplr_delta_rule(q, k, v, a, b, gk=log_f, RANK_AB=2, ...)`` (HRDPLR/hdla_custom.py:290-309), as one
-    operator call on the bf16 tensor-core pipeline.  Problems outside that pipeline (fp32, other head dims, decays
-    beyond its range) take the two calls."""
+    operator call on the bf16 tensor-core pipeline.  With ``normalize_k`` the layer's ``k = l2_norm(k)``
+    (HRDPLR/hdla_custom.py:248: ``k / sqrt(sum_K k^2 + 1e-5)``) happens inside the operator too and ``k`` is the
+    un-normalised tensor.  Problems outside that pipeline (fp32, other head dims, decays beyond its range) take
+    the separate calls."""
     global _warned_two_call
     B, T, H, K = q.shape
     if k.shape != q.shape or log_f.shape != q.shape or v.shape[:3] != q.shape[:3]:
@@ -172,13 +177,17 @@ def chunk_hdla_delta_rule(
                                     or any(y < x for x, y in zip(offsets, offsets[1:]))):
             raise ValueError(f"cu_seqlens {offsets} must rise from 0 to T={T} in a batch of one")
         try:
-            return _ChunkHdla.apply(q, k, v, beta, log_f, scale, initial_state, output_final_state, offsets)
+            return _ChunkHdla.apply(q, k, v, beta, log_f, scale, initial_state, output_final_state, offsets,
+                                    normalize_k)
         except _DecayOverflow:
             if not _warned_two_call:
                 _warned_two_call = True
                 warnings.warn("hdla_impl_b200: a chunk's total log decay exceeds what the bf16 tensor-core pipeline "
                               "represents; such calls take parameterize_a_b + the fp32 CUDA-core pipeline "
                               "(correct, much slower)", RuntimeWarning, stacklevel=2)
+    if normalize_k:
+        kf = k.float()
+        k = (kf * torch.rsqrt((kf * kf).sum(-1, keepdim=True) + L2_NORM_EPS)).to(k.dtype)
     a, b = parameterize_a_b(beta.reshape(B, T, H, 1), k, log_f)
     return _op.chunk_hrdplr_delta_rule(q, k, v, a, b, log_f, 2, scale=scale, initial_state=initial_state,
                                        output_final_state=output_final_state, chunk_size=64, cu_seqlens=cu_seqlens)

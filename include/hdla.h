@@ -70,6 +70,11 @@ extern "C" {
                                        and its backward must agree on the flag; problems outside the tensor-core
                                        pipeline report HDLA_ERR_UNSUPPORTED (use hdla_param_ab_fwd/_bwd there).   */
 
+#define HDLA_FLAG_NORM_K       256   /* with HDLA_FLAG_PARAM_AB: k arrives un-normalised and the layer's l2_norm of k
+                                       (HRDPLR/hdla_custom.py:248; k / sqrt(sum_K k^2 + 1e-5), normalizations/l2_norm.py:4)
+                                       happens in the preparation kernel too; backward's dk is the gradient of the
+                                       un-normalised k.                                                              */
+
 /* Phase selector (bits 4..7 of HdlaDims.flags), for callers that split a sequence over devices
  * (context parallelism).  Only the inter-chunk scan depends on the incoming state, so a call can be cut:
  *   PHASE_ALL         the whole forward / backward (default)

@@ -537,10 +537,12 @@ def _layer_inputs(B, T, H, K, V, seed, gk_div):
     return x
 
 
-@pytest.mark.parametrize("B,T,H,K,V,fdt,gk_div", [(2, 300, 2, 128, 128, torch.bfloat16, 16.0),
-                                                  (1, 640, 3, 128, 128, torch.float32, 1.0),
-                                                  (2, 200, 2, 64, 32, torch.bfloat16, 4.0)])
-def test_chunk_hdla_parametrisation_inside_the_operator(dev, B, T, H, K, V, fdt, gk_div):
+@pytest.mark.parametrize("B,T,H,K,V,fdt,gk_div,norm_k", [(2, 300, 2, 128, 128, torch.bfloat16, 16.0, False),
+                                                         (1, 640, 3, 128, 128, torch.float32, 1.0, False),
+                                                         (2, 200, 2, 64, 32, torch.bfloat16, 4.0, False),
+                                                         (2, 300, 2, 128, 128, torch.bfloat16, 8.0, True),
+                                                         (1, 200, 2, 96, 64, torch.float32, 4.0, True)])
+def test_chunk_hdla_parametrisation_inside_the_operator(dev, B, T, H, K, V, fdt, gk_div, norm_k):
     """`chunk_hdla_delta_rule(q, k, v, beta, log_f)` -- a and b formed inside the chunk-preparation kernel, their
     backward folded into dk, dlog_f, dbeta by the library -- against the fp64 oracle fed with the a, b of the
     reference's parameterize_a_b (HRDPLR/hdla_custom.py:19-43, :290-309), and against the two-call route on the GPU.
@@ -549,14 +551,17 @@ def test_chunk_hdla_parametrisation_inside_the_operator(dev, B, T, H, K, V, fdt,
     import hdla_impl_b200 as Hm
     from hdla_impl_b200 import _lib
     x = _layer_inputs(B, T, H, K, V, seed=31, gk_div=gk_div)
+    if norm_k:                       # the layer's l2_norm of k inside the operator too: feed rows of uneven length
+        x["k"] = x["k"] * (0.5 + 3 * torch.rand(B, T, H, 1, generator=torch.Generator().manual_seed(5)))
     bf = torch.bfloat16
     dts = dict(q=bf, k=bf, v=bf, beta=bf, log_f=fdt)
     names = ["q", "k", "v", "beta", "log_f"]
     # oracle in fp64 on the values the device sees
     rl = {n: x[n].to(dts[n]).double().requires_grad_(True) for n in names}
     h0r = x["h0"].double().requires_grad_(True)
-    ra, rb = _param_ab_torch(rl["beta"], rl["k"], rl["log_f"])
-    ro, rht = orc.chunked_ref(rl["q"], rl["k"], rl["v"], ra, rb, rl["log_f"], 2, 1.0, h0r, True, 64)
+    rk = rl["k"] / torch.sqrt((rl["k"] * rl["k"]).sum(-1, keepdim=True) + 1e-5) if norm_k else rl["k"]
+    ra, rb = _param_ab_torch(rl["beta"], rk, rl["log_f"])
+    ro, rht = orc.chunked_ref(rl["q"], rk, rl["v"], ra, rb, rl["log_f"], 2, 1.0, h0r, True, 64)
     rg = torch.autograd.grad((ro * x["do"].to(bf).double()).sum() + (rht * x["dht"].double()).sum(),
                              [rl[n] for n in names] + [h0r])
     ref = dict(o=ro, ht=rht, **{"d" + n: g_ for n, g_ in zip(names + ["h0"], rg)})
@@ -571,7 +576,7 @@ def test_chunk_hdla_parametrisation_inside_the_operator(dev, B, T, H, K, V, fdt,
 
     n0 = _lib.kernel_launches()
     got = run(lambda lv, h0: chunk_hdla_delta_rule(lv["q"], lv["k"], lv["v"], lv["beta"], lv["log_f"], scale=1.0,
-                                                   initial_state=h0, output_final_state=True))
+                                                   initial_state=h0, output_final_state=True, normalize_k=norm_k))
     launches = _lib.kernel_launches() - n0
     assert got["dbeta"].shape == x["beta"].shape and got["dlog_f"].dtype == fdt
     assert_close(got, ref, 2e-2, "in-operator parametrisation")
@@ -582,9 +587,44 @@ def test_chunk_hdla_parametrisation_inside_the_operator(dev, B, T, H, K, V, fdt,
         a, b = parameterize_a_b(lv["beta"], lv["k"], lv["log_f"])
         return Hm.chunk_hrdplr_delta_rule(lv["q"], lv["k"], lv["v"], a, b, lv["log_f"], 2, scale=1.0,
                                           initial_state=h0, output_final_state=True, chunk_size=64)
-    if fdt == bf:
+    if fdt == bf and not norm_k:
         assert_close(run(two_calls), ref, 2e-2, "two-call route")
     Hm.check_status(dev, wait=True)
+
+
+def test_chunk_hdla_packed_sequences_recompute_and_forward_only(dev, monkeypatch):
+    """The one-call layer operator on a packed variable-length batch equals its per-sequence calls; backward that
+    recomputes the forward (HDLA_RECOMPUTE=1) is bit-identical to backward on the saved workspace; a no-grad
+    forward (forward-only workspace) returns the same output."""
+    from hdla_impl_b200.layer_ops import chunk_hdla_delta_rule
+    H, K, V = 2, 128, 128
+    offs = [0, 200, 264, 598]
+    x = _layer_inputs(1, offs[-1], H, K, V, seed=33, gk_div=8.0)
+    bf = torch.bfloat16
+    names = ["q", "k", "v", "beta", "log_f"]
+    h0 = 0.2 * torch.randn(len(offs) - 1, H, K, V, generator=torch.Generator().manual_seed(1))
+
+    def run(cu, lo=0, hi=offs[-1], states=slice(None)):
+        lv = [x[n][:, lo:hi].to(bf).to(dev).requires_grad_(True) for n in names]
+        o, ht = chunk_hdla_delta_rule(*lv, scale=1.0, initial_state=h0[states].to(dev), output_final_state=True,
+                                      cu_seqlens=cu)
+        gr = torch.autograd.grad((o.float() * x["do"][:, lo:hi].to(dev)).sum() + ht.sum(), lv)
+        return [o, ht] + list(gr)
+
+    packed = run(offs)
+    monkeypatch.setenv("HDLA_RECOMPUTE", "1")
+    again = run(offs)
+    monkeypatch.delenv("HDLA_RECOMPUTE")
+    for a_, b_ in zip(packed, again):
+        assert torch.equal(a_, b_)
+    parts = [run(None, lo, hi, slice(i, i + 1)) for i, (lo, hi) in enumerate(zip(offs, offs[1:]))]
+    for j in range(len(packed)):
+        whole = torch.cat([p_[j] for p_ in parts], 0 if j == 1 else 1)
+        assert orc.rel_err(packed[j], whole) < 5e-3, j
+    with torch.no_grad():
+        lv = [x[n].to(bf).to(dev) for n in names]
+        o, ht = chunk_hdla_delta_rule(*lv, scale=1.0, initial_state=h0.to(dev), output_final_state=True, cu_seqlens=offs)
+    assert torch.equal(o, packed[0]) and torch.equal(ht, packed[1])
 
 
 @pytest.mark.parametrize("K", [96, 128, 200, 100])   # one piece per lane, full rows, two pieces, scalar kernels

@@ -139,3 +139,8 @@ def test_in_operator_parametrisation_flag_is_sized_and_gated_on_the_host():
     # with the one-kernel preparation requested as well, the four-kernel layout is planned (that kernel reads a and b)
     both = _lib.HdlaDims(B, T, H, K, 128, 2, 64, 1, 0, _lib.FLAG_PARAM_AB | _lib.FLAG_FUSED_PREP)
     assert lib.hdla_chunk_workspace_bytes(C.byref(both), 1) == lib.hdla_chunk_workspace_bytes(C.byref(fused), 1)
+    # normalising k inside the operator is part of the in-operator parametrisation
+    alone = _lib.HdlaDims(B, T, H, K, 128, 2, 64, 1, 0, _lib.FLAG_NORM_K)
+    assert lib.hdla_chunk_workspace_bytes(C.byref(alone), 1) == 0 and "HDLA_FLAG_PARAM_AB" in _lib.last_error()
+    with_norm = _lib.HdlaDims(B, T, H, K, 128, 2, 64, 1, 0, _lib.FLAG_PARAM_AB | _lib.FLAG_NORM_K)
+    assert lib.hdla_chunk_workspace_bytes(C.byref(with_norm), 1) == lib.hdla_chunk_workspace_bytes(C.byref(fused), 1)
