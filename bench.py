@@ -405,6 +405,7 @@ def run_ours(args, rank, world, local_rank):
                 secondary[name] = fn()
             except Exception as e:                       # noqa: BLE001
                 secondary[name] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+        record("host_link", lambda: bench_host_link(dev, world, barrier))
         if world > 1:
             record("cp_check", lambda: cp_parity_check(dev, rank, world))
             record("cfg3", lambda: bench_cfg3(dev, rank, world, barrier))
@@ -662,14 +663,55 @@ def bench_cfg0_gpu(dev, steps=20):
             "ms_per_step": ms, "value": B * T / (ms / 1e3), "unit": "tokens/s", "steps": steps}
 
 
-def bench_layer_call(dev, steps=10):
+def bench_host_link(dev, world, barrier, nbytes=256 << 20, reps=8):
+    """What the host link gives every rank while ALL ranks copy at once: pinned host <-> device copies of 256 MB,
+    one direction alone and both directions together.  The end-to-end figure of the line is bounded by the last
+    number (every step moves its inputs in and its gradients out); when the ranks' links share a host-side
+    bottleneck it does not grow with the number of GPUs, whatever the kernels do."""
+    import torch.distributed as dist
+    h_in = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    h_out = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    d_in = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    d_out = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def run(h2d, d2h):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        s_in.wait_stream(torch.cuda.current_stream(dev))
+        s_out.wait_stream(torch.cuda.current_stream(dev))
+        for _ in range(reps):
+            if h2d:
+                with torch.cuda.stream(s_in):
+                    d_in.copy_(h_in, non_blocking=True)
+            if d2h:
+                with torch.cuda.stream(s_out):
+                    h_out.copy_(d_out, non_blocking=True)
+        torch.cuda.current_stream(dev).wait_stream(s_in)
+        torch.cuda.current_stream(dev).wait_stream(s_out)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return reps * nbytes / (ms.item() / 1e3) / 1e9
+
+    run(True, True)                                       # warm-up
+    one_in, one_out, both = run(True, False), run(False, True), run(True, True)
+    return {"per_rank_GBps": {"h2d_alone": one_in, "d2h_alone": one_out, "each_way_when_both": both},
+            "all_ranks_GBps_each_way_when_both": both * world, "ranks_copying_at_once": world,
+            "bytes_per_copy": nbytes}
+
+
+def bench_layer_call(dev, steps=10, workload="cfg1"):
     """The operator as the reference layer calls it (HRDPLR/hdla_custom.py:290-345), at the cfg 1 shape, fwd+bwd:
     parameterize_a_b + chunk_hrdplr_delta_rule as two calls against chunk_hdla_delta_rule (a and b formed inside the
     chunk-preparation kernel), and the layer's norm x gate epilogue on the operator's output."""
     import torch.nn.functional as F
     import hdla_impl_b200 as HD
     from hdla_impl_b200.layer_ops import chunk_hdla_delta_rule, parameterize_a_b, rms_norm_fused_gate
-    B, T, H, K, V, C, _ = WORKLOADS["cfg1"]
+    B, T, H, K, V, C, _ = WORKLOADS[workload]
     g = torch.Generator().manual_seed(7)
     rn = lambda *s_: torch.randn(*s_, generator=g)
     bf = torch.bfloat16
@@ -721,7 +763,8 @@ def bench_layer_call(dev, steps=10):
     t_ngb = timed(lambda: torch.autograd.grad(o_n, [x, gate, w], dn, retain_graph=True))
     peak = load_peaks()[0]["hbm_gbs"]
     kern = lambda ms, elems: {"ms": ms, "GBps": elems * es / ms / 1e6, "frac_of_hbm_peak": elems * es / ms / 1e6 / peak}
-    return {"workload": "cfg1 shape as the layer calls the operator (q, k, v, beta, log_f; scale 1), bf16, fwd+bwd",
+    return {"workload": f"{workload} shape (B{B} T{T} H{H} K{K} V{V}) as the layer calls the operator (q, k, v, beta, "
+                        "log_f; scale 1), bf16, fwd+bwd",
             "two_calls_ms": t2, "one_call_ms": t1, "norm_gate_fwd_bwd_ms": tn,
             "one_call_tokens_per_s": B * T / (t1 / 1e3), "steps": steps,
             "kernels": {"param_ab_fwd": kern(t_abf, 6 * n_ab), "param_ab_bwd": kern(t_abb, 8 * n_ab),
@@ -839,11 +882,17 @@ def main():
     ap.add_argument("--scaling", default="strong", choices=["weak", "strong"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true")
+    ap.add_argument("--layer-call", action="store_true",
+                    help="only the layer-call measurement (secondary.layer_call of the default line) at --workload's shape")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.workload == "cfg2" and args.impl == "ours":
+    if args.layer_call:
+        dev = torch.device("cuda", local_rank)
+        torch.cuda.set_device(dev)
+        print(json.dumps({"layer_call": bench_layer_call(dev, max(args.steps, 1), args.workload)}))
+    elif args.workload == "cfg2" and args.impl == "ours":
         if args.steps == 20:
             args.steps = 128
         run_decode(args, rank, world, local_rank)
