@@ -157,72 +157,63 @@ __global__ void __launch_bounds__(256) param_ab_fwd_vec_kernel(AbP p) {
     }
 }
 
-template <int PIECES>
+// Every load of a row's piece sits in ONE conditional block together with the first use of its data, so that all of
+// them are in flight at once (a load whose result is merged with a default after its condition is waited for right
+// there, which would put the round trips to memory one behind the other).  The sums that need the normalised k are
+// taken at the raw k inside that block and scaled after the reductions: s = rn^2 s_raw, ds = rn ds_raw.
+template <int PIECES, bool ACC, int DT>
 __global__ void __launch_bounds__(256) param_ab_bwd_vec_kernel(AbP p) {
     const long long row = (long long)blockIdx.x * (256 / kAbLanes) + (threadIdx.x / kAbLanes);
     const bool live = row < p.rows;
     const int l = threadIdx.x % kAbLanes, npiece = p.K / 8;
     size_t in = 0, o1 = 0, o2 = 0;
     if (live) row_index(p, row, in, o1, o2);
-    const float beta = live ? ld_elem(p.beta, (size_t)row, p.dt) : 0.f;
+    const float beta = live ? ld_elem(p.beta, (size_t)row, DT) : 0.f;
     float kv[PIECES][8], ef[PIECES][8], da1[PIECES][8], da2[PIECES][8], db1[PIECES][8], db2[PIECES][8];
-    float s = 0.f, ds = 0.f, rn = 1.f;
-#pragma unroll
-    for (int j = 0; j < PIECES; ++j) {
-        const int pc = l + j * kAbLanes;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) kv[j][e] = 0.f;
-        if (live && pc < npiece) ld_elem8(p.k, in + pc * 8, p.dt, kv[j]);
-    }
-    if (p.norm_k) {
-        float ss = 0.f;
-#pragma unroll
-        for (int j = 0; j < PIECES; ++j)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) ss = fmaf(kv[j][e], kv[j][e], ss);
-        rn = rsqrtf(sub_sum(ss) + kNormEps);
-#pragma unroll
-        for (int j = 0; j < PIECES; ++j)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) kv[j][e] *= rn;
-    }
+    float dk0[PIECES][8], dlf0[PIECES][8];
+    float s = 0.f, ds = 0.f, ss = 0.f;
 #pragma unroll
     for (int j = 0; j < PIECES; ++j) {
         const int pc = l + j * kAbLanes;
         if (live && pc < npiece) {
+            ld_elem8(p.k, in + pc * 8, DT, kv[j]);
             ld_elem8(p.log_f, in + pc * 8, p.gdt, ef[j]);
-            ld_elem8(p.a, o1 + pc * 8, p.dt, da1[j]);
-            ld_elem8(p.a, o2 + pc * 8, p.dt, da2[j]);
-            ld_elem8(p.b, o1 + pc * 8, p.dt, db1[j]);
-            ld_elem8(p.b, o2 + pc * 8, p.dt, db2[j]);
+            ld_elem8(p.a, o1 + pc * 8, DT, da1[j]);
+            ld_elem8(p.a, o2 + pc * 8, DT, da2[j]);
+            ld_elem8(p.b, o1 + pc * 8, DT, db1[j]);
+            ld_elem8(p.b, o2 + pc * 8, DT, db2[j]);
+            if (ACC) {
+                ld_elem8(p.dk, in + pc * 8, DT, dk0[j]);
+                ld_elem8(p.dlog_f, in + pc * 8, p.gdt, dlf0[j]);
+            }
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 ef[j][e] = __expf(ef[j][e]);
                 s += kv[j][e] * (-beta * ef[j][e] * kv[j][e]);
                 ds += (-beta * kv[j][e]) * da2[j][e];
+                ss = fmaf(kv[j][e], kv[j][e], ss);
             }
         }
     }
     s = sub_sum(s);
     ds = sub_sum(ds);
+    float rn = 1.f;
+    if (p.norm_k) {
+        rn = rsqrtf(sub_sum(ss) + kNormEps);
+        s *= rn * rn;
+        ds *= rn;
+    }
     float dbeta = 0.f, kdk = 0.f;
     float dk[PIECES][8];
 #pragma unroll
     for (int j = 0; j < PIECES; ++j) {
         const int pc = l + j * kAbLanes;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) dk[j][e] = 0.f;
         if (live && pc < npiece) {
-            float dlf[8], dk0[8], dlf0[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) dk0[e] = dlf0[e] = 0.f;
-            if (p.accumulate) {
-                ld_elem8(p.dk, in + pc * 8, p.dt, dk0);
-                ld_elem8(p.dlog_f, in + pc * 8, p.gdt, dlf0);
-            }
+            float dlf[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                const float k = kv[j][e], f = ef[j][e];
+                const float k = kv[j][e] * rn, f = ef[j][e];
+                kv[j][e] = k;
                 const float at2 = -beta * f * k;
                 const float dat2 = da2[j][e] + k * ds;       // a2 = at2 + a1 s,  s = sum k at2
                 const float da1t = da1[j][e] + s * da2[j][e];
@@ -230,28 +221,29 @@ __global__ void __launch_bounds__(256) param_ab_bwd_vec_kernel(AbP p) {
                 g += -beta * f * dat2;                       // at2 = -beta ef k
                 g += -beta * da1t;                           // a1 = -beta k
                 g += f * db1[j][e] + db2[j][e];              // b1 = ef k, b2 = k
-                dk[j][e] = g + dk0[e];
+                dk[j][e] = ACC ? g + dk0[j][e] : g;
                 kdk = fmaf(k, dk[j][e], kdk);
-                dlf[e] = (-beta * k * dat2 + k * db1[j][e]) * f + dlf0[e];
+                dlf[e] = (-beta * k * dat2 + k * db1[j][e]) * f + (ACC ? dlf0[j][e] : 0.f);
                 dbeta += -f * k * dat2 - k * da1t;
             }
             st_elem8(p.dlog_f, in + pc * 8, p.gdt, dlf);
+            if (!p.norm_k) st_elem8(p.dk, in + pc * 8, DT, dk[j]);
         }
     }
-    if (p.norm_k) kdk = sub_sum(kdk);                        // k_n = k rn:  dk = rn (dk_n - k_n (k_n . dk_n))
+    if (p.norm_k) {                                          // k_n = k rn:  dk = rn (dk_n - k_n (k_n . dk_n))
+        kdk = sub_sum(kdk);
 #pragma unroll
-    for (int j = 0; j < PIECES; ++j) {
-        const int pc = l + j * kAbLanes;
-        if (live && pc < npiece) {
-            if (p.norm_k) {
+        for (int j = 0; j < PIECES; ++j) {
+            const int pc = l + j * kAbLanes;
+            if (live && pc < npiece) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) dk[j][e] = rn * (dk[j][e] - kv[j][e] * kdk);
+                st_elem8(p.dk, in + pc * 8, DT, dk[j]);
             }
-            st_elem8(p.dk, in + pc * 8, p.dt, dk[j]);
         }
     }
     dbeta = sub_sum(dbeta);
-    if (live && l == 0) st_elem(p.dbeta, (size_t)row, p.dt, dbeta);
+    if (live && l == 0) st_elem(p.dbeta, (size_t)row, DT, dbeta);
 }
 
 }  // namespace
@@ -267,8 +259,14 @@ int param_ab_launch(bool backward, const void* beta, const void* k, const void* 
         const unsigned blocks = (unsigned)((p.rows + 15) / 16);
         const bool wide = K > kAbLanes * 8;
         if (backward) {
-            if (wide) param_ab_bwd_vec_kernel<2><<<blocks, 256, 0, st>>>(p);
-            else param_ab_bwd_vec_kernel<1><<<blocks, 256, 0, st>>>(p);
+            void (*kern)(AbP) = nullptr;
+            if (dt == HDLA_BF16)
+                kern = wide ? (accumulate ? param_ab_bwd_vec_kernel<2, true, HDLA_BF16> : param_ab_bwd_vec_kernel<2, false, HDLA_BF16>)
+                            : (accumulate ? param_ab_bwd_vec_kernel<1, true, HDLA_BF16> : param_ab_bwd_vec_kernel<1, false, HDLA_BF16>);
+            else
+                kern = wide ? (accumulate ? param_ab_bwd_vec_kernel<2, true, HDLA_F32> : param_ab_bwd_vec_kernel<2, false, HDLA_F32>)
+                            : (accumulate ? param_ab_bwd_vec_kernel<1, true, HDLA_F32> : param_ab_bwd_vec_kernel<1, false, HDLA_F32>);
+            kern<<<blocks, 256, 0, st>>>(p);
         } else {
             if (wide) param_ab_fwd_vec_kernel<2><<<blocks, 256, 0, st>>>(p);
             else param_ab_fwd_vec_kernel<1><<<blocks, 256, 0, st>>>(p);
