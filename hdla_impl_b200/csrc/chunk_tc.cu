@@ -50,28 +50,33 @@ struct PrepP {
 // (with the in-operator a/b parametrisation only q, k, v are read)
 struct PrepIn { uint4 q, k, v, a0, a1, b0, b1; };
 
+// Unconditional: a position outside the chunk's tokens or the head's channels is read from a clamped one and
+// replaced by zeros where the data is used (a load inside a condition, merged with a default after it, can be waited
+// for where the condition ends, which would undo the request one step ahead).
 template <bool AB>
 __device__ __forceinline__ PrepIn prep_load(const PrepP& p, int b, int h, int t0, int valid, int blk, int lane) {
     const int r = (blk >> 2) * 8 + (lane & 7);
     const int kc = (blk & 3) * 4 + (lane >> 3);
     const uint4 zero = make_uint4(0, 0, 0, 0);
-    PrepIn x{zero, zero, zero, zero, zero, zero, zero};
-    if (r < valid && kc * 8 < p.Kd) {
-        const size_t src = (((size_t)b * p.T + t0 + r) * p.H + h) * p.Kd + kc * 8;
-        const size_t sa0 = (((size_t)b * p.T * R + (size_t)(t0 + r) * R) * p.H + h) * p.Kd + kc * 8;
-        const size_t sa1 = sa0 + (size_t)p.H * p.Kd;
-        x.q = __ldg(reinterpret_cast<const uint4*>(p.q + src));
-        x.k = __ldg(reinterpret_cast<const uint4*>(p.k + src));
-        if (!AB) {
-            x.a0 = __ldg(reinterpret_cast<const uint4*>(p.a + sa0));
-            x.a1 = __ldg(reinterpret_cast<const uint4*>(p.a + sa1));
-            x.b0 = __ldg(reinterpret_cast<const uint4*>(p.b + sa0));
-            x.b1 = __ldg(reinterpret_cast<const uint4*>(p.b + sa1));
-        }
+    const bool row_ok = r < valid, k_ok = row_ok && kc * 8 < p.Kd, v_ok = row_ok && kc * 8 < p.Vd;
+    const int rc = row_ok ? r : valid - 1;
+    const size_t tok = (size_t)b * p.T + t0 + rc;
+    const size_t src = (tok * p.H + h) * p.Kd + (k_ok ? kc * 8 : 0);
+    const size_t sa0 = ((tok * R) * p.H + h) * p.Kd + (k_ok ? kc * 8 : 0);
+    const size_t sa1 = sa0 + (size_t)p.H * p.Kd;
+    PrepIn x;
+    x.q = __ldg(reinterpret_cast<const uint4*>(p.q + src));
+    x.k = __ldg(reinterpret_cast<const uint4*>(p.k + src));
+    if (!AB) {
+        x.a0 = __ldg(reinterpret_cast<const uint4*>(p.a + sa0));
+        x.a1 = __ldg(reinterpret_cast<const uint4*>(p.a + sa1));
+        x.b0 = __ldg(reinterpret_cast<const uint4*>(p.b + sa0));
+        x.b1 = __ldg(reinterpret_cast<const uint4*>(p.b + sa1));
+    } else {
+        x.a0 = x.a1 = x.b0 = x.b1 = zero;
     }
-    if (r < valid && kc * 8 < p.Vd)
-        x.v = __ldg(reinterpret_cast<const uint4*>(p.v + (((size_t)b * p.T + t0 + r) * p.H + h) * p.Vd + kc * 8));
-    return x;
+    x.v = __ldg(reinterpret_cast<const uint4*>(p.v + (tok * p.H + h) * p.Vd + (v_ok ? kc * 8 : 0)));
+    return x;                    // (the caller masks what lies outside: prep_mask)
 }
 
 // AB: the layer's a/b parametrisation (HRDPLR/hdla_custom.py:19-43) on the way:  with ef = e^{log_f} (log_f = gk),
@@ -203,14 +208,16 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
             hf[0] = .5f * l0.x; hf[1] = .5f * l0.y; hf[2] = .5f * l0.z; hf[3] = .5f * l0.w;
             hf[4] = .5f * l1.x; hf[5] = .5f * l1.y; hf[6] = .5f * l1.z; hf[7] = .5f * l1.w;
         }
+        // positions outside the chunk's tokens or the head's channels hold clamped reads: their factors are zero
+        const float mk = (r < valid && kc * 8 < p.Kd) ? 1.f : 0.f;
         float x[8], y[8], ep[8], em[8], ea[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            ep[j] = __expf(gi[j] - hf[j]); em[j] = __frcp_rn(ep[j]); ea[j] = __expf(ge[j] - hf[j]);
+            ep[j] = __expf(gi[j] - hf[j]); em[j] = mk * __frcp_rn(ep[j]); ea[j] = mk * __expf(ge[j] - hf[j]);
         }
         t8::unpack8(cur.q, x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) y[j] = x[j] * p.scale * ep[j];
+        for (int j = 0; j < 8; ++j) y[j] = x[j] * (p.scale * mk) * ep[j];
         p.Qh[(size_t)g * CH64 + kc * 64 + r] = t8::pack8(y);
         t8::unpack8(cur.k, x);
         if (AB) {
@@ -221,7 +228,7 @@ __global__ void __launch_bounds__(128) prep_hat_kernel(PrepP p) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) y[j] = x[j] * em[j];
         p.Kh[(size_t)g * CH64 + kc * 64 + r] = t8::pack8(y);
-        p.Vc[(size_t)g * CH64 + kc * 64 + r] = cur.v;
+        p.Vc[(size_t)g * CH64 + kc * 64 + r] = (r < valid && kc * 8 < p.Vd) ? cur.v : make_uint4(0, 0, 0, 0);
         if (AB) {   // x still holds this piece of k
             const float4 bs = beta_s[r];
             float a0[8], z[8];
