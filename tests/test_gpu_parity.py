@@ -309,6 +309,29 @@ def test_bf16_head_dims_below_128_run_on_tensor_cores(dev, B, T, H, K, V):
     assert torch.equal(o2, got["o"]) and torch.equal(ht2, got["ht"])
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_bf16_random_shapes_against_oracle(dev, seed):
+    """Seeded random problems of the tensor-core pipeline (batch, ragged length, heads, head dims that are multiples
+    of 8 up to 128, decay strength, with or without initial state / final-state gradient, gk in bf16 or fp32):
+    forward + backward against the fp64 oracle, status words clean."""
+    import random
+    import hdla_impl_b200 as HD
+    rng = random.Random(1000 + seed)
+    B, H = rng.choice([1, 2, 3]), rng.choice([1, 2, 3])
+    T = rng.randint(33, 700)
+    K, V = 8 * rng.randint(1, 16), 8 * rng.randint(1, 16)
+    use_h0, use_dht = rng.random() < 0.6, rng.random() < 0.6
+    gk_div = rng.choice([1.0, 2.0, 8.0, 16.0])
+    x = make_inputs(B, T, H, K, V, R, seed=200 + seed, dtype=torch.bfloat16, gk_div=gk_div, h0_std=0.2, with_dht=True)
+    if rng.random() < 0.5:
+        x["gk"] = x["gk"].float()
+    scale = rng.choice([1.0, K ** -0.5])
+    got = run_chunk(x, dev, scale, 64, use_h0, use_dht, torch.bfloat16)
+    HD.check_status(dev, wait=True)
+    ref = oracle_chunk(x, scale, use_h0, use_dht, torch.bfloat16)
+    assert_close(got, ref, 2e-2, f"B{B} T{T} H{H} K{K} V{V} h0={use_h0} dht={use_dht} gk/{gk_div} {x['gk'].dtype}")
+
+
 def _varlen_case(dev, lens, H, K, V, dtype, tol, seed):
     """Packed sequences through chunk_hrdplr_delta_rule(cu_seqlens=...) against the oracle run per sequence."""
     import hdla_impl_b200 as HD
