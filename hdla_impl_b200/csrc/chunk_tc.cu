@@ -1216,11 +1216,19 @@ __global__ void __launch_bounds__(128) out_tc_kernel(OutP p) {
             float f[64];
             tmem_row64(t8::taddr(tmem, warp, hh * 64), f);
             if (tid < valid) {
+                // whole 32-byte sectors per lane (lanes are 4 KB apart) where the rows of o start on 32-byte
+                // boundaries, i.e. V is a multiple of 16; rows of V = 8, 24, 40, ... elements start on odd multiples
+                // of 16 bytes and take 16-byte stores
+                const bool rows_32B = p.Vd % 16 == 0;
 #pragma unroll
-                for (int cg = 0; cg < 8; cg += 2) {        // whole 32-byte sectors per lane (lanes are 4 KB apart)
+                for (int cg = 0; cg < 8; cg += 2) {
                     const int col = (hh * 8 + cg) * 8;
-                    if (col + 16 <= p.Vd) sm100::st_global_32B(dst + hh * 8 + cg, t8::pack8(f + cg * 8), t8::pack8(f + cg * 8 + 8));
-                    else if (col < p.Vd) dst[hh * 8 + cg] = t8::pack8(f + cg * 8);
+                    if (rows_32B && col + 16 <= p.Vd) {
+                        sm100::st_global_32B(dst + hh * 8 + cg, t8::pack8(f + cg * 8), t8::pack8(f + cg * 8 + 8));
+                    } else {
+                        if (col < p.Vd) dst[hh * 8 + cg] = t8::pack8(f + cg * 8);
+                        if (col + 8 < p.Vd) dst[hh * 8 + cg + 1] = t8::pack8(f + cg * 8 + 8);
+                    }
                 }
             }
         }

@@ -282,7 +282,9 @@ def test_bf16_tensor_core_path_at_reference_decay_strength(dev):
 
 
 @pytest.mark.parametrize("B,T,H,K,V", [(2, 512, 2, 64, 64), (1, 300, 3, 128, 64), (1, 256, 2, 64, 128),
-                                       (1, 200, 2, 96, 48), (1, 2100, 2, 64, 64)])
+                                       (1, 200, 2, 96, 48), (1, 2100, 2, 64, 64),
+                                       (2, 200, 2, 56, 40), (1, 130, 3, 120, 120), (1, 100, 2, 8, 8)])   # rows of V = 8 (mod 16)
+                                                                             # elements start on odd multiples of 16 bytes
 def test_bf16_head_dims_below_128_run_on_tensor_cores(dev, B, T, H, K, V):
     """The reference handles any K <= 256 and any V (HRDPLR/fwd_func.py:229-241).  Head dims below 128 (multiples
     of 8) run on the tcgen05 pipeline too, zero-padded to its 128-wide tiles: forward + backward with an initial
