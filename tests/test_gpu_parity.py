@@ -175,6 +175,33 @@ def test_recurrent_shapes_bf16_decode(dev, K, V):
     assert orc.rel_err(o, ro) < 2e-2 and orc.rel_err(S, rh) < 1e-4
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_recurrent_random_shapes_against_oracle(dev, seed):
+    """Seeded random problems of the recurrent path: any K up to 256, V a multiple of 4 up to 256, few tokens (state
+    staged in shared memory by bulk copies where it fits) or many (state in registers), forward or reverse, with or
+    without an initial state, fp32 or bf16."""
+    import random
+    import hdla_impl_b200 as H
+    rng = random.Random(2000 + seed)
+    B, Hh = rng.choice([1, 2, 3]), rng.choice([1, 2])
+    K, V = rng.randint(1, 256), 4 * rng.randint(1, 64)
+    T = rng.choice([1, 2, 5, 8, 9, 23])
+    dtype = rng.choice([torch.float32, torch.bfloat16])
+    reverse, use_h0 = rng.random() < 0.4, rng.random() < 0.7
+    x = make_inputs(B, T, Hh, K, V, R, seed=300 + seed, dtype=dtype, gk_div=2.0, h0_std=0.3)
+    args = [x[n].to(dev) for n in ("q", "k", "v", "a", "b", "gk")]
+    o, ht = H.fused_recurrent_dplr_delta_rule(*args, R, 0.5, x["h0"].to(dev) if use_h0 else None, True, reverse, None)
+    f = lambda n: x[n].double()
+    ro, rh = orc.recurrent_ref(f("q"), f("k"), f("v"), f("a"), f("b"), f("gk"), R, 0.5, x["h0"] if use_h0 else None,
+                               reverse=reverse)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    label = f"B{B} T{T} H{Hh} K{K} V{V} {dtype} reverse={reverse} h0={use_h0}"
+    assert orc.rel_err(o, ro) < tol, label
+    assert orc.rel_err(ht, rh) < (1e-4 if dtype == torch.float32 else 2e-2), label
+    from hdla_impl_b200.recurrent import check_recurrent_status
+    check_recurrent_status(dev)
+
+
 def test_recurrent_inplace_state(dev):
     import hdla_impl_b200 as H
     x = make_inputs(4, 1, 2, 64, 64, R, seed=10, h0_std=0.5)
