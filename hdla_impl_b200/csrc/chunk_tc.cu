@@ -693,13 +693,17 @@ __global__ void __launch_bounds__(256) scan_tc_kernel(ScanTcP p) {
     if (tid == 0) {
         const long long g = g0 + n_first;
         mbar_init(&ldA, 1); mbar_init(&ldB, 1); mbar_init(&barA, 1); mbar_init(&barB, 1); fence_mbar_init();
-        mbar_expect_tx(&ldA, 65536);
-        bulk_g2s(sA1, p.A1 + g * CH128, 32768, &ldA);
-        bulk_g2s(sADD, p.ADD + g * p.add_stride * CH128, 32768, &ldA);
-        mbar_expect_tx(&ldB, 65536);
-        bulk_g2s(sL1, p.L1 + g * p.r1_stride * CH64, 16384, &ldB);
-        bulk_g2s(sR1, p.R1 + g * p.r1_stride * CH64, 16384, &ldB);
-        bulk_g2s(sL2, p.L2 + g * CH128, 32768, &ldB);
+        // (an empty sequence of a packed batch has no chunk: nothing is requested -- nothing would wait for it and
+        //  the CTA must not leave with copies into its shared memory in flight -- and its final state is its initial one)
+        if (steps > 0) {
+            mbar_expect_tx(&ldA, 65536);
+            bulk_g2s(sA1, p.A1 + g * CH128, 32768, &ldA);
+            bulk_g2s(sADD, p.ADD + g * p.add_stride * CH128, 32768, &ldA);
+            mbar_expect_tx(&ldB, 65536);
+            bulk_g2s(sL1, p.L1 + g * p.r1_stride * CH64, 16384, &ldB);
+            bulk_g2s(sR1, p.R1 + g * p.r1_stride * CH64, 16384, &ldB);
+            bulk_g2s(sL2, p.L2 + g * CH128, 32768, &ldB);
+        }
     }
     float S[64];
     if (p.init_identity) {

@@ -361,6 +361,25 @@ def test_bf16_random_shapes_against_oracle(dev, seed):
     assert_close(got, ref, 2e-2, f"B{B} T{T} H{H} K{K} V{V} h0={use_h0} dht={use_dht} gk/{gk_div} {x['gk'].dtype}")
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_fp32_random_shapes_against_oracle(dev, seed):
+    """Seeded random problems of the fp32 pipeline: any head dims (odd ones included, as the reference takes any
+    K <= 256 and any V), ragged lengths, chunk 16 / 32 / 64, strong and weak decay: forward + backward, 1e-4."""
+    import random
+    rng = random.Random(3000 + seed)
+    B, H = rng.choice([1, 2]), rng.choice([1, 2, 3])
+    T = rng.randint(17, 300)
+    K, V = rng.randint(1, 160), rng.randint(1, 160)
+    chunk = rng.choice([16, 32, 64])
+    use_h0, use_dht = rng.random() < 0.6, rng.random() < 0.6
+    gk_div = rng.choice([1.0, 4.0, 16.0])
+    x = make_inputs(B, T, H, K, V, R, seed=400 + seed, gk_div=gk_div, h0_std=0.2, with_dht=True)
+    scale = rng.choice([1.0, K ** -0.5])
+    got = run_chunk(x, dev, scale, chunk, use_h0, use_dht, torch.float32)
+    ref = oracle_chunk(x, scale, use_h0, use_dht, torch.float32)
+    assert_close(got, ref, 1e-4, f"B{B} T{T} H{H} K{K} V{V} chunk {chunk} h0={use_h0} dht={use_dht} gk/{gk_div}")
+
+
 def _varlen_case(dev, lens, H, K, V, dtype, tol, seed):
     """Packed sequences through chunk_hrdplr_delta_rule(cu_seqlens=...) against the oracle run per sequence."""
     import hdla_impl_b200 as HD
@@ -423,6 +442,19 @@ def test_chunked_varlen_packed_sequences_on_tensor_cores(dev):
     assert torch.equal(o1, o[:, 264:597]) and torch.equal(ht1, ht[2:3])
     # head dims below 128 and an empty sequence in the middle
     _varlen_case(dev, [70, 0, 130], 3, 64, 64, torch.bfloat16, 2e-2, seed=63)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_chunked_varlen_random_batches(dev, seed):
+    """Seeded random packed batches on the tensor-core pipeline: two to six sequences of 0 .. 300 tokens (empty ones,
+    single tokens and exact chunk multiples included), random heads and head dims."""
+    import random
+    rng = random.Random(4000 + seed)
+    lens = [rng.choice([0, 1, 63, 64, 65, 128, rng.randint(2, 300)]) for _ in range(rng.randint(2, 6))]
+    if sum(lens) <= 32:
+        lens.append(100)
+    H, K, V = rng.choice([1, 2, 3]), 8 * rng.randint(1, 16), 8 * rng.randint(1, 16)
+    _varlen_case(dev, lens, H, K, V, torch.bfloat16, 2e-2, seed=500 + seed)
 
 
 def test_chunked_varlen_falls_back_to_per_sequence_calls(dev):
