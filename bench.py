@@ -365,7 +365,9 @@ def run_ours(args, rank, world, local_rank):
                     out_host[i] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
                 out_host[i].copy_(t, non_blocking=True)
         else:
-            chunk_fwd_bwd_from_host(host, out_host, R, dev, scale=scale, chunk_size=C, slice_batch=1, sync=False)
+            # slices of up to four batch elements: while the kernels of a slice run, the copies of its neighbours
+            # proceed at about half their rate (measured), so fewer and larger kernels cost the link less
+            chunk_fwd_bwd_from_host(host, out_host, R, dev, scale=scale, chunk_size=C, slice_batch=4, sync=False)
 
     with numa_local_to(dev):
         e2e_step()

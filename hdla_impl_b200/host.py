@@ -75,7 +75,7 @@ _OUT = ("o", "dq", "dk", "dv", "da", "db", "dgk")
 
 
 _copy_streams: Dict[int, tuple] = {}
-_stages: Dict[tuple, list] = {}      # (device index, slice shape key) -> [slot0, slot1], each dict(bufs=..., done=Event|None)
+_stages: Dict[tuple, dict] = {}      # (device index, slice shape key) -> dict(turn=int, slots=[slot0, slot1]), a slot = dict(bufs=..., done=Event|None)
 
 
 def _streams(dev: torch.device):
@@ -128,8 +128,9 @@ def chunk_fwd_bwd_from_host(host_in: Dict[str, torch.Tensor], host_out: Optional
     with torch.cuda.device(dev):
         for idx, (lo, hi) in enumerate(bounds):
             key = (dev.index, hi - lo) + tuple((n, tuple(host_in[n].shape[1:]), host_in[n].dtype) for n in names_in)
-            slots = _stages.setdefault(key, [dict(bufs=None, done=None), dict(bufs=None, done=None)])
-            slot = slots[idx & 1]                  # two sets of device input buffers, alternating
+            stage = _stages.setdefault(key, dict(turn=0, slots=[dict(bufs=None, done=None), dict(bufs=None, done=None)]))
+            slot = stage["slots"][stage["turn"] & 1]   # two sets of device input buffers, alternating from slice to
+            stage["turn"] += 1                         # slice ACROSS calls too (a call may be a single slice)
             with torch.cuda.stream(s_in):
                 if slot["done"] is not None:
                     s_in.wait_event(slot["done"])              # the kernels that last read these buffers are done
