@@ -380,6 +380,25 @@ def test_fp32_random_shapes_against_oracle(dev, seed):
     assert_close(got, ref, 1e-4, f"B{B} T{T} H{H} K{K} V{V} chunk {chunk} h0={use_h0} dht={use_dht} gk/{gk_div}")
 
 
+@pytest.mark.parametrize("seed", range(4))
+def test_bf16_random_long_sequences_two_level_scan(dev, seed):
+    """Seeded random long sequences with few (batch, head) pairs, where the scans run segment-parallel: random
+    length (ragged), pairs, head dims, initial state and final-state gradient, against the fp64 oracle."""
+    import random
+    import hdla_impl_b200 as HD
+    rng = random.Random(5000 + seed)
+    B, H = rng.choice([(1, 1), (1, 2), (2, 1), (1, 3), (2, 2)])
+    T = rng.randint(1500, 5000)
+    K, V = 8 * rng.randint(4, 16), 8 * rng.randint(4, 16)
+    use_h0, use_dht = rng.random() < 0.7, rng.random() < 0.7
+    x = make_inputs(B, T, H, K, V, R, seed=600 + seed, dtype=torch.bfloat16, gk_div=rng.choice([4.0, 16.0]),
+                    h0_std=0.2, with_dht=True)
+    got = run_chunk(x, dev, K ** -0.5, 64, use_h0, use_dht, torch.bfloat16)
+    HD.check_status(dev, wait=True)
+    ref = oracle_chunk(x, K ** -0.5, use_h0, use_dht, torch.bfloat16)
+    assert_close(got, ref, 2e-2, f"B{B} T{T} H{H} K{K} V{V} h0={use_h0} dht={use_dht}")
+
+
 def _varlen_case(dev, lens, H, K, V, dtype, tol, seed):
     """Packed sequences through chunk_hrdplr_delta_rule(cu_seqlens=...) against the oracle run per sequence."""
     import hdla_impl_b200 as HD
