@@ -90,6 +90,18 @@ def _compose(lib, dims, T, F, S0, pre, post, out, count, t_stride, f_stride, rev
     _lib.check(rc, "hdla_compose_states")
 
 
+def _all_gather_maps(out: torch.Tensor, mine: torch.Tensor, group) -> None:
+    """``out[r] = mine of rank r``.  NCCL groups gather on the device; a group whose backend cannot take CUDA tensors
+    (gloo: ranks that share one GPU in tests, or hosts without NCCL) is served through host memory."""
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(out, mine, group=group)
+        return
+    host = mine.detach().cpu()
+    parts = [torch.empty_like(host) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(parts, host, group=group)
+    out.copy_(torch.stack(parts).to(out.device, non_blocking=False))
+
+
 class _CPChunkFunction(torch.autograd.Function):
     """Context-parallel chunked operator on the CUDA library, with the scans of all ranks running
     concurrently.
@@ -147,7 +159,7 @@ class _CPChunkFunction(torch.autograd.Function):
             else:
                 pack[2].zero_()
             maps = torch.empty(world, 3, B, H, K, V, **f32)
-            dist.all_gather_into_tensor(maps, pack, group=group)
+            _all_gather_maps(maps, pack, group)
             # state entering this rank's slice: the maps of ranks 0 .. rank-1 applied to the initial state
             S = torch.empty(B, H, K, V, **f32)
             _compose(lib, mk(0), maps[0, 0], maps[0, 1], maps[0, 2], None, None, S, rank, 3 * B * H, 3 * B * H, 0, dev)
@@ -208,7 +220,7 @@ class _CPChunkFunction(torch.autograd.Function):
             else:
                 pack[1].zero_()
             gmaps = torch.empty(world, 2, B, H, K, V, **f32)
-            dist.all_gather_into_tensor(gmaps, pack, group=group)
+            _all_gather_maps(gmaps, pack, group)
             # gradient of the state leaving this rank: dht_rank + E_{rank+1}, with E_j = T_j^T (dht_j + E_{j+1}) + G_j
             # the gradient of the state entering rank j (E_world = 0)
             D = torch.empty(B, H, K, V, **f32)

@@ -15,12 +15,15 @@ def _free_port():
     s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
 
 
-def _worker(rank, world, port, T, out):
+def _worker(rank, world, port, T, out, one_gpu=False):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
-    dev = torch.device("cuda", rank)
+    dev = torch.device("cuda", 0 if one_gpu else rank)
     torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    if one_gpu:          # ranks sharing one GPU: the maps travel through the host (gloo); no kernel waits for another rank
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    else:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         import hdla_impl_b200 as H
         from hdla_impl_b200.context_parallel import cp_chunk_hrdplr_delta_rule
@@ -62,6 +65,8 @@ def _worker(rank, world, port, T, out):
         else:                                  # initial_state is used on rank 0 only: zero gradient elsewhere
             assert grads[6] is None or float(grads[6].abs().max()) == 0.0
         out[rank] = max(errs)
+        HD_check = H.check_status
+        HD_check(dev, wait=True)
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -76,3 +81,16 @@ def test_context_parallel_two_gpus_matches_one_gpu(T):
     mp.spawn(_worker, args=(2, _free_port(), T, out), nprocs=2, join=True)
     # the two paths round the boundary state differently (bf16 checkpoints): bf16 tolerance
     assert len(out) == 2 and max(out.values()) < 2e-2, dict(out)
+
+
+@pytest.mark.parametrize("world,T", [(2, 512), (3, 4096 + 64 * 3)])
+def test_context_parallel_ranks_sharing_one_gpu(world, T):
+    """The phased library calls, the composition of the gathered affine state maps and the protocol around them
+    (every rank's own final-state gradient, dh0 on rank 0 only) with all ranks as processes on ONE GPU: the maps are
+    gathered through the host, so no kernel of one rank ever waits for another rank's.  Same checks as on two GPUs."""
+    if torch.cuda.device_count() < 1:
+        pytest.skip("needs a GPU")
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), T, out, True), nprocs=world, join=True)
+    assert len(out) == world and max(out.values()) < 2e-2, dict(out)
