@@ -163,3 +163,26 @@ def test_context_parallel_peer_loss_is_an_error_not_a_hang():
     # rank 2 waits for a state that never comes; rank 0's send or its backward recv meets the closed peer
     assert out[2].startswith("error"), dict(out)
     assert out[0].startswith("error"), dict(out)
+
+
+def _gather_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from hdla_impl_b200.context_parallel import _all_gather_maps
+        mine = torch.full((3, 2, 4), float(rank + 1))
+        got = torch.zeros(world, 3, 2, 4)
+        _all_gather_maps(got, mine, None)
+        out[rank] = bool(all(torch.equal(got[r], torch.full((3, 2, 4), float(r + 1))) for r in range(world)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_state_map_gather_through_the_host_for_non_nccl_groups():
+    """The context-parallel path's one collective per direction, on a group whose backend cannot take device tensors:
+    every rank ends up with every rank's maps in rank order."""
+    world = 3
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_gather_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert len(out) == world and all(out.values())
