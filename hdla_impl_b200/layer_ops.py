@@ -59,7 +59,10 @@ class _ParamAB(torch.autograd.Function):
 
 
 def parameterize_a_b(beta: torch.Tensor, k: torch.Tensor, log_f: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``a, b`` of shape ``[B, 2T, H, K]`` (row ``2t + r``) from ``beta [B,T,H,1]``, ``k`` and ``log_f [B,T,H,K]``."""
+    """``a, b`` of shape ``[B, 2T, H, K]`` (row ``2t + r``) from ``beta [B,T,H,1]``, ``k`` and ``log_f [B,T,H,K]``.
+    ``beta`` may be a number (the layer uses the constant 2 when it has no beta projection, HRDPLR/hdla_custom.py:226)."""
+    if not torch.is_tensor(beta):
+        beta = k.new_full(tuple(k.shape[:3]) + (1,), float(beta))
     return _ParamAB.apply(beta, k, log_f)
 
 
@@ -149,7 +152,7 @@ def chunk_hdla_delta_rule(
     q: torch.Tensor,       # [B, T, H, K]
     k: torch.Tensor,       # [B, T, H, K]
     v: torch.Tensor,       # [B, T, H, V]
-    beta: torch.Tensor,    # [B, T, H, 1] or [B, T, H]
+    beta,                  # [B, T, H, 1] or [B, T, H] tensor, or a number
     log_f: torch.Tensor,   # [B, T, H, K]  log decay (the operator's gk)
     scale: Optional[float] = None,
     initial_state: Optional[torch.Tensor] = None,
@@ -165,6 +168,8 @@ def chunk_hdla_delta_rule(
     the separate calls."""
     global _warned_two_call
     B, T, H, K = q.shape
+    if not torch.is_tensor(beta):            # the layer's constant beta = 2 (no beta projection)
+        beta = q.new_full((B, T, H, 1), float(beta))
     if k.shape != q.shape or log_f.shape != q.shape or v.shape[:3] != q.shape[:3]:
         raise ValueError(f"k {tuple(k.shape)} and log_f {tuple(log_f.shape)} must match q {tuple(q.shape)}, v "
                          f"{tuple(v.shape)} must be [B, T, H, V]")

@@ -727,7 +727,11 @@ def test_chunk_hdla_packed_sequences_recompute_and_forward_only(dev, monkeypatch
     with torch.no_grad():
         lv = [x[n].to(bf).to(dev) for n in names]
         o, ht = chunk_hdla_delta_rule(*lv, scale=1.0, initial_state=h0.to(dev), output_final_state=True, cu_seqlens=offs)
-    assert torch.equal(o, packed[0]) and torch.equal(ht, packed[1])
+        assert torch.equal(o, packed[0]) and torch.equal(ht, packed[1])
+        # a constant beta (the layer without a beta projection uses 2) is the same as a tensor filled with it
+        o2, _ = chunk_hdla_delta_rule(lv[0], lv[1], lv[2], 2, lv[4], scale=1.0, cu_seqlens=offs)
+        o3, _ = chunk_hdla_delta_rule(lv[0], lv[1], lv[2], torch.full_like(lv[3], 2.0), lv[4], scale=1.0, cu_seqlens=offs)
+        assert torch.equal(o2, o3)
 
 
 @pytest.mark.parametrize("K", [96, 128, 200, 100])   # one piece per lane, full rows, two pieces, scalar kernels
