@@ -177,6 +177,10 @@ def chunk_hdla_delta_rule(
         raise ValueError(f"beta {tuple(beta.shape)} must be [B, T, H, 1] or [B, T, H]")
     scale = K ** -0.5 if scale is None else scale
     offsets = _op._seq_offsets(cu_seqlens)
+    n_states = B if offsets is None else len(offsets) - 1
+    if initial_state is not None and tuple(initial_state.shape) != (n_states, H, K, v.shape[-1]):
+        raise ValueError(f"initial_state {tuple(initial_state.shape)} must be [{n_states}, H, K, V] = "
+                         f"{(n_states, H, K, v.shape[-1])}")
     if _op._packed_supported(q, v, 2) and log_f.dtype in (torch.bfloat16, torch.float32):
         if offsets is not None and (q.shape[0] != 1 or offsets[0] != 0 or offsets[-1] != T
                                     or any(y < x for x, y in zip(offsets, offsets[1:]))):
