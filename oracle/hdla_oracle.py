@@ -319,6 +319,23 @@ def autograd_ref(fn, q, k, v, a, b, gk, h0, do, dht, dtype=torch.float64):
     names = ["dq", "dk", "dv", "da", "db", "dgk"] + (["dh0"] if h0l is not None else [])
     return o.detach(), (None if ht is None else ht.detach()), dict(zip(names, grads))
 
+# --------------------------------------------------------------------------------------
+# 4. the layer's a/b parametrisation (HRDPLR/hdla_custom.py:19-43, which computes a and b and returns nothing)
+# --------------------------------------------------------------------------------------
+def param_ab_ref(beta: torch.Tensor, k: torch.Tensor, log_f: torch.Tensor):
+    """``a, b`` of shape ``[B, 2T, H, K]`` (row ``2t + r``) as the reference's ``parameterize_a_b`` forms them:
+    a1 = -beta k (:24), a2 = at2 + a1 sum_K(k at2) with at2 = -beta e^{log_f} k (:25-33), b1 = e^{log_f} k, b2 = k
+    (:35-36), stacked rank-minor (:38-42).  Differentiable.  Pinned by tests/golden/param_ab_small.npz, whose a and b
+    were read out of the reference function's own frame."""
+    a_t1 = -beta * k
+    a_t2 = -beta * torch.exp(log_f) * k
+    a_2 = a_t2 + a_t1 * torch.sum(k * a_t2, dim=-1, keepdim=True)
+    b_1 = torch.exp(log_f) * k
+    B, T, H, K = k.shape
+    a = torch.stack([a_t1, a_2], dim=2).reshape(B, 2 * T, H, K)
+    b = torch.stack([b_1, k], dim=2).reshape(B, 2 * T, H, K)
+    return a, b
+
 
 def rel_err(x: torch.Tensor, ref: torch.Tensor) -> float:
     """max|x-ref| / max|ref|  -- the parity metric used everywhere."""

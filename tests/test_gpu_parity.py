@@ -619,15 +619,9 @@ def test_repeated_calls_are_bit_identical(dev, B, T, H):
 
 
 def _param_ab_torch(beta, k, log_f):
-    """Restatement of the reference's parameterize_a_b (HRDPLR/hdla_custom.py:19-43) with the missing return."""
-    a_t1 = -beta * k
-    a_t2 = -beta * torch.exp(log_f) * k
-    a_2 = a_t2 + a_t1 * torch.sum(k * a_t2, dim=-1, keepdim=True)
-    b_1 = torch.exp(log_f) * k
-    B, T, H, K = k.shape
-    a = torch.stack([a_t1, a_2], dim=2).reshape(B, 2 * T, H, K)
-    b = torch.stack([b_1, k], dim=2).reshape(B, 2 * T, H, K)
-    return a, b
+    """The oracle's restatement of the reference's parameterize_a_b (HRDPLR/hdla_custom.py:19-43), pinned by
+    tests/golden/param_ab_small.npz (tests/test_oracle.py)."""
+    return orc.param_ab_ref(beta, k, log_f)
 
 
 def _layer_inputs(B, T, H, K, V, seed, gk_div):
@@ -755,6 +749,18 @@ def test_parameterize_a_b_forward_backward(dev, dtype, tol, K):
     assert orc.rel_err(a, ra) < tol and orc.rel_err(b, rbb) < tol
     for got, ref, n in zip(gg, rg, ("dbeta", "dk", "dlog_f")):
         assert orc.rel_err(got, ref) < tol, n
+
+
+def test_parameterize_a_b_against_reference_golden(dev, golden_dir):
+    """The CUDA kernel against a and b computed by the reference's own function (read out of its frame by
+    tests/golden/make_param_ab_golden.py)."""
+    from hdla_impl_b200.layer_ops import parameterize_a_b
+    z = np.load(os.path.join(golden_dir, "param_ab_small.npz"))
+    beta, k, log_f = (torch.from_numpy(z[n]).float().to(dev) for n in ("beta", "k", "log_f"))
+    a, b = parameterize_a_b(beta, k, log_f)
+    ra, rb = orc.param_ab_ref(beta.double().cpu(), k.double().cpu(), log_f.double().cpu())   # on the fp32-rounded inputs
+    assert orc.rel_err(a, ra) < 1e-6 and orc.rel_err(b, rb) < 1e-6
+    assert orc.rel_err(a, torch.from_numpy(z["a"])) < 1e-5 and orc.rel_err(b, torch.from_numpy(z["b"])) < 1e-5
 
 
 def test_bf16_recompute_and_forward_only(dev, monkeypatch):

@@ -123,3 +123,13 @@ def test_installed_reference_matches_oracle():
     assert orc.rel_err(o, st["o_bthv"]) < 1e-10 and orc.rel_err(ht, st["ht"]) < 1e-10
     for t, n in zip(grads, ("dq", "dk", "dv", "da", "db", "dgk")):
         assert orc.rel_err(t, g[n]) < 1e-10, n
+
+
+def test_param_ab_restatement_matches_the_reference_function(golden_dir):
+    """``param_ab_ref`` against a and b computed by the reference's own ``parameterize_a_b`` (the function returns
+    nothing; the generator read them out of its frame: tests/golden/make_param_ab_golden.py)."""
+    z = np.load(os.path.join(golden_dir, "param_ab_small.npz"))
+    t = lambda n: torch.from_numpy(z[n])
+    a, b = orc.param_ab_ref(t("beta"), t("k"), t("log_f"))
+    assert a.shape == t("a").shape and b.shape == t("b").shape
+    assert orc.rel_err(a, t("a")) < 1e-14 and orc.rel_err(b, t("b")) < 1e-14
