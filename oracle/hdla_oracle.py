@@ -336,6 +336,16 @@ def param_ab_ref(beta: torch.Tensor, k: torch.Tensor, log_f: torch.Tensor):
     b = torch.stack([b_1, k], dim=2).reshape(B, 2 * T, H, K)
     return a, b
 
+def norm_gate_ref(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """The layer's output epilogue (HRDPLR/hdla_custom.py:341-345): ``normalize_torch``
+    (HRDPLR/normalizations/normalize/normalize/normalize_torch.py:65-79) as ``RMSNormFusedGate`` calls it -- sigmoid
+    gate applied before the norm (:65-68), no mean, one group, ``o = c y / sqrt(sum(y^2) + eps) * weight`` (:75-79) with
+    ``c = sqrt(D)`` (HRDPLR/normalizations/utils.py, rmsnorm).  Differentiable.  Pinned by
+    tests/golden/norm_gate_small.npz, which the reference function itself produced."""
+    y = x * torch.sigmoid(gate)
+    D = x.shape[-1]
+    return (D ** 0.5) * y / torch.sqrt((y * y).sum(-1, keepdim=True) + eps) * weight
+
 
 def rel_err(x: torch.Tensor, ref: torch.Tensor) -> float:
     """max|x-ref| / max|ref|  -- the parity metric used everywhere."""

@@ -763,6 +763,19 @@ def test_parameterize_a_b_against_reference_golden(dev, golden_dir):
     assert orc.rel_err(a, torch.from_numpy(z["a"])) < 1e-5 and orc.rel_err(b, torch.from_numpy(z["b"])) < 1e-5
 
 
+def test_rms_norm_fused_gate_against_reference_golden(dev, golden_dir):
+    """The CUDA kernels against o, dx, dgate, dweight computed by the reference's own normalize_torch
+    (tests/golden/make_norm_gate_golden.py)."""
+    from hdla_impl_b200.layer_ops import rms_norm_fused_gate
+    z = np.load(os.path.join(golden_dir, "norm_gate_small.npz"))
+    x, gate, w = (torch.from_numpy(z[n]).to(dev).requires_grad_(True) for n in ("x", "gate", "weight"))
+    o = rms_norm_fused_gate(x, gate, w, float(z["eps"]))
+    grads = torch.autograd.grad((o * torch.from_numpy(z["d_o"]).to(dev)).sum(), [x, gate, w])
+    assert orc.rel_err(o, torch.from_numpy(z["o"])) < 1e-5
+    for got, n in zip(grads, ("dx", "dgate", "dweight")):
+        assert orc.rel_err(got, torch.from_numpy(z[n])) < 1e-5, n
+
+
 def test_bf16_recompute_and_forward_only(dev, monkeypatch):
     """Tensor-core path: backward that recomputes the forward (HDLA_RECOMPUTE=1, the reference's behaviour) gives
     the same gradients as backward on the saved workspace; a no-grad forward uses the forward-only workspace."""
@@ -791,8 +804,7 @@ def test_rms_norm_fused_gate_forward_backward(dev, dtype, tol, rows, D):
     w, go = 1 + 0.1 * torch.randn(D, generator=g), torch.randn(3, rows, D, generator=g)
     rd = lambda t: t.to(dtype).double().requires_grad_(True)
     rx, rg, rw = rd(x), rd(gate), rd(w)
-    y = rx * torch.sigmoid(rg)
-    ro = (D ** 0.5) * y / torch.sqrt((y * y).sum(-1, keepdim=True) + eps) * rw
+    ro = orc.norm_gate_ref(rx, rg, rw, eps)
     rgrads = torch.autograd.grad((ro * go.to(dtype).double()).sum(), [rx, rg, rw])
     dx, dg, dw = (t.to(dtype).to(dev).requires_grad_(True) for t in (x, gate, w))
     o = rms_norm_fused_gate(dx, dg, dw, eps)

@@ -133,3 +133,15 @@ def test_param_ab_restatement_matches_the_reference_function(golden_dir):
     a, b = orc.param_ab_ref(t("beta"), t("k"), t("log_f"))
     assert a.shape == t("a").shape and b.shape == t("b").shape
     assert orc.rel_err(a, t("a")) < 1e-14 and orc.rel_err(b, t("b")) < 1e-14
+
+
+def test_norm_gate_restatement_matches_the_reference_function(golden_dir):
+    """``norm_gate_ref`` (forward and autograd gradients) against the reference's own ``normalize_torch`` called as the
+    layer's epilogue calls it (tests/golden/make_norm_gate_golden.py; the reference computes in fp32)."""
+    z = np.load(os.path.join(golden_dir, "norm_gate_small.npz"))
+    leaves = [torch.from_numpy(z[n]).double().requires_grad_(True) for n in ("x", "gate", "weight")]
+    o = orc.norm_gate_ref(*leaves, float(z["eps"]))
+    grads = torch.autograd.grad((o * torch.from_numpy(z["d_o"]).double()).sum(), leaves)
+    assert orc.rel_err(o, torch.from_numpy(z["o"])) < 1e-6
+    for got, n in zip(grads, ("dx", "dgate", "dweight")):
+        assert orc.rel_err(got, torch.from_numpy(z[n])) < 1e-5, n
