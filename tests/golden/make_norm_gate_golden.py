@@ -11,7 +11,8 @@ The module imports ``xopes.ops.act.act_torch`` (third-party package ``xopes``, n
 installed here); ``act_torch(x, "sigmoid")`` is the only use on this path and is stood in for by ``torch.sigmoid``.
 Everything else executed is the reference function's own source text, taken out of the file with ``ast`` and run on
 fp32 inputs (the function computes in fp32: ``x = x.float()``).  Outputs: o and, by autograd on the
-reference function, the gradients of x, gate and weight for a fixed dO.
+reference function, the gradients of x, gate and weight for a fixed dO; and ``l2``, the same function as the layer's
+``l2_norm`` calls it.
 """
 import ast
 import os
@@ -50,9 +51,12 @@ def main():
     o = fn(x, weight=w, gate=gate, gate_act="sigmoid", gate_pos="pre", c=D ** 0.5, eps=eps, use_mean=False,
            num_groups=1)
     dx, dg, dw = torch.autograd.grad((o * do).sum(), [x, gate, w])
+    # the layer's l2_norm of k (HRDPLR/normalizations/l2_norm.py:4-14): the same function with c = 1, eps = 1e-5, no
+    # weight, no gate
+    l2 = fn(x.detach(), weight=None, bias=None, residual=None, c=1, eps=1e-5, use_mean=False, num_groups=1)
     np.savez_compressed(os.path.join(HERE, "norm_gate_small.npz"), x=x.detach().numpy(), gate=gate.detach().numpy(),
                         weight=w.detach().numpy(), d_o=do.numpy(), eps=np.float64(eps), o=o.detach().numpy(),
-                        dx=dx.numpy(), dgate=dg.numpy(), dweight=dw.numpy())
+                        dx=dx.numpy(), dgate=dg.numpy(), dweight=dw.numpy(), l2=l2.numpy())
     print("o", tuple(o.shape), float(o.detach().abs().max()))
 
 

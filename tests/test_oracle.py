@@ -145,3 +145,11 @@ def test_norm_gate_restatement_matches_the_reference_function(golden_dir):
     assert orc.rel_err(o, torch.from_numpy(z["o"])) < 1e-6
     for got, n in zip(grads, ("dx", "dgate", "dweight")):
         assert orc.rel_err(got, torch.from_numpy(z[n])) < 1e-5, n
+
+
+def test_l2_norm_formula_matches_the_reference_function(golden_dir):
+    """k / sqrt(sum_K k^2 + 1e-5) -- what HDLA_FLAG_NORM_K computes inside the operator and what the tests feed the
+    oracle with -- against the reference's normalize_torch called as its l2_norm calls it."""
+    z = np.load(os.path.join(golden_dir, "norm_gate_small.npz"))
+    x = torch.from_numpy(z["x"]).double()
+    assert orc.rel_err(x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-5), torch.from_numpy(z["l2"])) < 1e-6
