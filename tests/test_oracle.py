@@ -125,6 +125,28 @@ def test_installed_reference_matches_oracle():
         assert orc.rel_err(t, g[n]) < 1e-10, n
 
 
+def test_oracle_scan_stage_matches_the_reference_scan_function():
+    """The state-scan stage of the staged oracle (state entering every chunk, v2, final state) against the
+    reference's own ``fwd_h_naive`` (HRDPLR/naive.py:11-73) fed with the oracle's stage operands; skipped where the
+    reference is not installed."""
+    import pytest
+    from oracle import ref_naive
+    if not ref_naive.available():
+        pytest.skip("oracle/_ref/naive.py is not installed")
+    from hdla_impl_b200.synthetic import make_inputs
+    B, T, H, K, V, R, C = 2, 64, 2, 16, 24, 2, 16
+    x = make_inputs(B, T, H, K, V, R, seed=13, gk_div=2.0, h0_std=0.5)
+    f = lambda n: x[n].double()
+    st = orc.staged_forward(f("q"), f("k"), f("v"), f("a"), f("b"), f("gk"), R, 1.0, x["h0"], C)
+    # chunk-major [B,H,NT,rows,D] -> the reference's [B, NT*rows, H, D]
+    flat = lambda t: t.permute(0, 2, 3, 1, 4).reshape(B, -1, H, t.shape[-1])
+    h_ref, ht_ref, v_new_ref = ref_naive.load().fwd_h_naive(flat(st["kg"]), f("v"), flat(st["bg"]), flat(st["w"]),
+                                                            flat(st["u"]), flat(st["gi"]), x["h0"].double(), C, R)
+    assert orc.rel_err(st["h"].permute(0, 2, 1, 3, 4), h_ref) < 1e-12          # [B,H,NT,K,V] vs [B,NT,H,K,V]
+    assert orc.rel_err(flat(st["v2"]), v_new_ref) < 1e-12
+    assert orc.rel_err(st["ht"], ht_ref) < 1e-12
+
+
 def test_param_ab_restatement_matches_the_reference_function(golden_dir):
     """``param_ab_ref`` against a and b computed by the reference's own ``parameterize_a_b`` (the function returns
     nothing; the generator read them out of its frame: tests/golden/make_param_ab_golden.py)."""
