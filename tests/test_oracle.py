@@ -175,3 +175,20 @@ def test_l2_norm_formula_matches_the_reference_function(golden_dir):
     z = np.load(os.path.join(golden_dir, "norm_gate_small.npz"))
     x = torch.from_numpy(z["x"]).double()
     assert orc.rel_err(x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-5), torch.from_numpy(z["l2"])) < 1e-6
+
+
+def test_oracle_score_matrices_match_the_reference_stage_test(golden_dir):
+    """The four intra-chunk score matrices of the staged oracle against the torch reference block of the reference's own
+    stage test, compute_A_ref_torch (test_fwd_A.py:10-62, called as at :203-214; tests/golden/make_stage_golden.py)."""
+    z = np.load(os.path.join(golden_dir, "stage_A_small.npz"))
+    t = lambda n: torch.from_numpy(z[n])
+    B, T, H, K = t("q").shape
+    C, R = int(z["chunk"]), 2
+    st = orc.staged_forward(t("q"), t("k"), torch.zeros(B, T, H, 4, dtype=torch.float64), t("a"), t("b"), t("gk"), R, 1.0,
+                            None, C)
+    for n in ("Aqk", "Aqb", "Aak", "Aab"):
+        mine = st[n].permute(0, 2, 3, 1, 4).reshape(t(n).shape)        # [B,H,NT,rows,cols] -> [B, NT*rows, H, cols]
+        assert orc.rel_err(mine, t(n)) < 1e-12, n
+    # the output stage: the reference's chunk_dplr_fwd_o_simple (test_fwd_o.py:9-94) on those score matrices
+    st = orc.staged_forward(t("q"), t("k"), t("v"), t("a"), t("b"), t("gk"), R, 1.0, t("h0"), C)
+    assert orc.rel_err(st["o_bthv"], t("o")) < 1e-12
