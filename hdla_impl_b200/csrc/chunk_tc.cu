@@ -1503,7 +1503,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         const __nv_bfloat16* ek = reinterpret_cast<const __nv_bfloat16*>(sb + (k >> 3) * 64) + (k & 7) + i_lo * 8;
         const __nv_bfloat16* ea = reinterpret_cast<const __nv_bfloat16*>(sB + (k >> 3) * 128) + (k & 7) + i_lo * 16;
         float run = 0.f;
-        float* dgk_loc = reinterpret_cast<float*>(sE) + (size_t)i_lo * K + k;    // [64][128] fp32 over the (consumed) dAab slot
+        float loc[16];                                    // this thread's dgk values before the other groups' totals
 #pragma unroll
         for (int hb = 3; hb >= 0; --hb) {                 // four tokens per accumulator read: fewer live registers
             uint32_t vq[4], vk[4], va[8], vb[8];
@@ -1530,7 +1530,7 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
                     p.db[base_ab + (size_t)(2 * jt + 1) * tok_stride] = __float2bfloat16_rn(em * db1);
                 }
                 run += d_gi + d_ge;
-                dgk_loc[jt * K] = run - d_ge + dgl;
+                loc[jt] = run - d_ge + dgl;
             }
         }
         if (tid == 0) TL(10);
@@ -1539,11 +1539,9 @@ __global__ void __launch_bounds__(544) grad_tc_kernel(GradP p) {
         if (tid == 0) TL(11);
         float add = 0.f;
         for (int w = 0; w < wg; ++w) add += group_total[w][k];
-#pragma unroll 4
-        for (int jj = 0; jj < 16; ++jj) {
-            const int t = t0 + i_lo + jj;
-            if (i_lo + jj < t_left && k_ok) st_elem(p.dgk, (((size_t)b * p.T + t) * p.H + h) * p.Kd + k, p.gdt, dgk_loc[jj * K] + add);
-        }
+#pragma unroll
+        for (int jj = 0; jj < 16; ++jj)
+            if (i_lo + jj < t_left && k_ok) st_elem(p.dgk, base_qk + (size_t)jj * tok_stride, p.gdt, loc[jj] + add);
     }
     // every thread is done with this tile's slots and accumulators before the next tile's first loads and products
     tc_fence_before();
